@@ -1,0 +1,424 @@
+/*
+ * qs3_moe.h -- C ABI of the sm_100a mixture-of-experts library (libqs3moe.so).
+ *
+ * Two groups of declarations live here:
+ *
+ *  1. The part of the qs3 ("quasar3") kernel boundary that its MoE layer goes
+ *     through. Struct layouts, enum values, symbol names and error behaviour
+ *     follow the upstream headers so that objects built from this library can
+ *     replace the upstream MoE/router objects at link time. Every such
+ *     declaration cites the upstream file:line it is layout-compatible with.
+ *
+ *  2. Additive entry points (prefix qs3_) that upstream does not have: NVFP4
+ *     weight preparation, a dense bf16 GEMM for the router / shared expert, a
+ *     whole-layer call (router logits -> top-k -> experts -> combine), and the
+ *     expert-parallel pack/unpack helpers. They never change an upstream
+ *     signature.
+ *
+ * Conventions (upstream qs_tensor.h:6-13, qsfi.h:14-18): strides are element
+ * strides; an optional tensor is absent when data == NULL; all work is
+ * enqueued on the stream owned by the context (or passed explicitly for the
+ * context-free qscu_ helpers) and nothing synchronises in release builds.
+ */
+#ifndef QS3_MOE_H
+#define QS3_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- status -- */
+
+#define QSFI_ERROR_MESSAGE_BYTES 512u /* upstream qs_info.h:10 */
+
+/* Checked builds add device-side validation plus one stream sync per validated
+ * call (upstream qs_info.h:12-18). The shipped library is a release build. */
+#ifndef QSFI_ENABLE_CHECKED_VALIDATION
+#define QSFI_ENABLE_CHECKED_VALIDATION 0
+#endif
+
+typedef enum { /* upstream qs_info.h:20-28 */
+    QSFI_STATUS_OK = 0,
+    QSFI_STATUS_INVALID_ARGUMENT = 1,
+    QSFI_STATUS_UNSUPPORTED = 2,
+    QSFI_STATUS_OUT_OF_MEMORY = 3,
+    QSFI_STATUS_CUDA_ERROR = 4,
+    QSFI_STATUS_BACKEND_ERROR = 5,
+    QSFI_STATUS_INTERNAL_ERROR = 6
+} qsfi_status;
+
+typedef enum { /* upstream qs_info.h:30-36 */
+    QSFI_ERROR_SOURCE_NONE = 0,
+    QSFI_ERROR_SOURCE_QSFI = 1,
+    QSFI_ERROR_SOURCE_CUDA = 2,
+    QSFI_ERROR_SOURCE_FLASHINFER = 3,
+    QSFI_ERROR_SOURCE_CUBLASLT = 4
+} qsfi_error_source;
+
+typedef struct { /* upstream qs_info.h:38-43 */
+    qsfi_status status;
+    qsfi_error_source source;
+    int32_t native_code;
+    char message[QSFI_ERROR_MESSAGE_BYTES];
+} qsfi_error_info;
+
+const char* qsfi_status_string(qsfi_status status); /* upstream qs_info.h:45 */
+
+/* --------------------------------------------------------------- tensors -- */
+
+typedef void* qsfi_cuda_stream; /* upstream qs_tensor.h:12 */
+typedef void* qsfi_device_ptr;  /* upstream qs_tensor.h:13 */
+
+typedef enum { /* upstream qs_tensor.h:15-29 */
+    QSFI_DTYPE_INVALID = 0,
+    QSFI_DTYPE_F32 = 1,
+    QSFI_DTYPE_F16 = 2,
+    QSFI_DTYPE_BF16 = 3,
+    QSFI_DTYPE_FP8_E4M3 = 4,
+    QSFI_DTYPE_FP8_E5M2 = 5,
+    QSFI_DTYPE_NVFP4_E2M1 = 6,
+    QSFI_DTYPE_MXFP4_E2M1 = 7,
+    QSFI_DTYPE_MXFP8_E4M3 = 8,
+    QSFI_DTYPE_I32 = 9,
+    QSFI_DTYPE_U32 = 10,
+    QSFI_DTYPE_I8 = 11,
+    QSFI_DTYPE_U8 = 12
+} qsfi_dtype;
+
+/* Rank-N strided views, upstream qs_tensor.h:31-50. */
+#define QS3_DECLARE_TENSOR(N)                                                                      \
+    typedef struct {                                                                               \
+        qsfi_device_ptr data;                                                                      \
+        qsfi_dtype dtype;                                                                          \
+        int64_t shape[N];                                                                          \
+        int64_t stride[N];                                                                         \
+    } qsfi_tensor##N
+QS3_DECLARE_TENSOR(1);
+QS3_DECLARE_TENSOR(2);
+QS3_DECLARE_TENSOR(3);
+#undef QS3_DECLARE_TENSOR
+
+/* --------------------------------------------------------------- context -- */
+
+typedef struct qsfi_context qsfi_context;   /* upstream qsfi.h:20 */
+typedef struct qsfi_moe_plan qsfi_moe_plan; /* upstream qsfi.h:23 */
+
+typedef struct { /* upstream qsfi.h:33-36 */
+    int32_t device_ordinal; /* < 0: whatever device is current at call time. */
+    qsfi_cuda_stream stream; /* NULL: the default stream. */
+} qsfi_context_desc;
+
+typedef struct { /* upstream qsfi.h:38-46 */
+    uint32_t target_sm;
+    uint32_t target_compute_capability_major;
+    uint32_t target_compute_capability_minor;
+    uint32_t assume_fp8;
+    uint32_t assume_fp4;
+    uint32_t assume_pdl;
+    uint32_t gemm_backend;
+} qsfi_build_config;
+
+typedef struct { /* upstream qsfi.h:48-51 */
+    uint32_t runtime_compute_capability_major;
+    uint32_t runtime_compute_capability_minor;
+} qsfi_context_info;
+
+/* Context life cycle and error read-back, upstream qsfi.h:268-288 and
+ * qsfi_context.cu:120-283. This build answers target_sm = 100 (CC 10.0). */
+qsfi_status qsfi_context_create(const qsfi_context_desc* desc, qsfi_context** out);
+void qsfi_context_destroy(qsfi_context* ctx);
+qsfi_status qsfi_context_set_stream(qsfi_context* ctx, qsfi_cuda_stream stream);
+qsfi_status qsfi_get_build_config(qsfi_build_config* out);
+qsfi_status qsfi_context_get_info(qsfi_context* ctx, qsfi_context_info* out);
+qsfi_status qsfi_context_validate_target(qsfi_context* ctx);
+qsfi_status qsfi_context_get_last_error(const qsfi_context* ctx, qsfi_error_info* out);
+void qsfi_context_clear_last_error(qsfi_context* ctx);
+
+/* ------------------------------------------------------------ MoE (qsfi) -- */
+
+typedef enum { /* upstream qsfi.h:211-215; the names keep upstream's spelling */
+    QSFI_MOE_BACKEND_FLASHINFER_STAGED_BF16 = 1,
+    QSFI_MOE_BACKEND_FLASHINFER_FUSED_BF16 = 2,
+    QSFI_MOE_BACKEND_FLASHINFER_NVFP4 = 3
+} qsfi_moe_backend;
+
+typedef enum { /* upstream qsfi.h:217-220 */
+    QSFI_MOE_ROUTE_PRECOMPUTED_TOPK = 0,
+    QSFI_MOE_ROUTE_ROUTER_LOGITS = 1
+} qsfi_moe_route_mode;
+
+typedef struct { /* upstream qsfi.h:222-236 */
+    qsfi_moe_backend backend;
+    qsfi_moe_route_mode route_mode;
+    uint32_t max_num_tokens;
+    uint32_t hidden_size;
+    uint32_t intermediate_size;
+    uint32_t num_experts;
+    uint32_t top_k;
+    uint32_t local_expert_offset; /* first global expert id owned by this rank */
+    uint32_t local_num_experts;
+    qsfi_dtype activation_dtype;
+    qsfi_dtype weight_dtype;
+    qsfi_dtype output_dtype;
+    uint32_t reserved0;
+} qsfi_moe_plan_desc;
+
+typedef struct { /* upstream qsfi.h:238-247 */
+    qsfi_tensor2 hidden;         /* bf16 [num_tokens, hidden] */
+    qsfi_tensor2 topk_ids;       /* i32  [num_tokens, top_k], GLOBAL expert ids */
+    qsfi_tensor2 topk_weights;   /* f32  [num_tokens, top_k], final per-route scale */
+    qsfi_tensor3 gate_up_weight; /* bf16 [local_experts, 2*inter, hidden]; rows [0,inter) gate */
+    qsfi_tensor3 down_weight;    /* bf16 [local_experts, hidden, inter] */
+    qsfi_tensor2 out;            /* bf16 [num_tokens, hidden] */
+    qsfi_tensor1 workspace;      /* u8/i8 [>= qsfi_moe_workspace_size] */
+    uint32_t num_tokens;
+} qsfi_moe_bf16_execute_desc;
+
+typedef struct { /* upstream qsfi.h:249-266 */
+    qsfi_tensor2 hidden_packed;         /* u8   [num_tokens, hidden/2], low nibble = even k */
+    qsfi_tensor2 hidden_scale;          /* e4m3 [num_tokens, hidden/16], row-major ("linear") */
+    qsfi_tensor2 topk_ids;              /* i32  [num_tokens, top_k] */
+    qsfi_tensor2 topk_weights;          /* f32  [num_tokens, top_k] */
+    qsfi_tensor3 gate_up_weight_packed; /* u8   [local_experts, 2*inter, hidden/2] */
+    qsfi_tensor3 gate_up_weight_scale;  /* e4m3 [local_experts, 2*inter, hidden/16], linear */
+    qsfi_tensor3 down_weight_packed;    /* u8   [local_experts, hidden, inter/2] */
+    qsfi_tensor3 down_weight_scale;     /* e4m3 [local_experts, hidden, inter/16], linear */
+    qsfi_tensor1 expert_output_scale;   /* optional f32 [local_experts]: down-GEMM output scale */
+    qsfi_tensor2 out;                   /* bf16 [num_tokens, hidden] */
+    qsfi_tensor1 workspace;             /* u8/i8 */
+    uint32_t num_tokens;
+} qsfi_moe_nvfp4_execute_desc;
+
+/* Plan and execute, upstream qsfi.h:333-344 (qsfi_moe.cu:730-821).
+ *
+ * Differences from upstream, all additive:
+ *  - an expert-parallel plan (partial local expert range) is accepted: routes to
+ *    non-local experts are skipped and `out` holds this rank's partial sum
+ *    (upstream rejects such plans, qsfi_moe.cu:160-166, although its kernels
+ *    already skip non-local routes, qsfi_moe.cu:340-343,379-381,484);
+ *  - qsfi_moe_execute_nvfp4 is implemented (upstream returns UNSUPPORTED,
+ *    qsfi_moe.cu:807-821) and qsfi_moe_workspace_size answers for NVFP4 plans;
+ *  - the order of rows inside one expert's segment is deterministic (stable in
+ *    route index); upstream's depends on atomics order (qsfi_moe.cu:378-382).
+ * The reported BF16 workspace size is never smaller than upstream's formula
+ * (qsfi_moe.cu:67-121), which the upstream Rust caller re-checks
+ * (src/ffi/qsfi.rs:472-516,539-587). */
+qsfi_status
+qsfi_moe_plan_create(qsfi_context* ctx, const qsfi_moe_plan_desc* desc, qsfi_moe_plan** out);
+void qsfi_moe_plan_destroy(qsfi_moe_plan* plan);
+qsfi_status qsfi_moe_workspace_size(
+    qsfi_context* ctx, const qsfi_moe_plan* plan, uint32_t num_tokens, size_t* device_bytes
+);
+qsfi_status qsfi_moe_execute_bf16(
+    qsfi_context* ctx, const qsfi_moe_plan* plan, const qsfi_moe_bf16_execute_desc* desc
+);
+qsfi_status qsfi_moe_execute_nvfp4(
+    qsfi_context* ctx, const qsfi_moe_plan* plan, const qsfi_moe_nvfp4_execute_desc* desc
+);
+
+/* ------------------------------------------------- router & glue (qscu) -- */
+
+typedef enum { /* upstream qscu.h:202 */
+    QSCU_ROUTER_SCORE_SOFTMAX = 0,
+    QSCU_ROUTER_SCORE_SIGMOID = 1
+} qscu_router_score;
+
+typedef struct { /* upstream qscu.h:246-256 */
+    qsfi_tensor2 logits;       /* bf16/f32 [num_tokens, num_experts] */
+    qsfi_tensor2 topk_ids;     /* i32 [num_tokens, top_k], descending score, ties by lower id */
+    qsfi_tensor2 topk_weights; /* f32 [num_tokens, top_k] */
+    uint32_t num_tokens;
+    uint32_t num_experts; /* <= 4096 */
+    uint32_t top_k;       /* <= 16 and <= num_experts */
+    qscu_router_score score;
+    uint32_t renormalize;
+    float routed_scaling_factor; /* finite, > 0 */
+} qscu_router_topk_desc;
+
+/* Softmax/sigmoid top-k routing, upstream qscu.h:278 (qscu.cu:894-971,1817-1857).
+ * One warp per token instead of upstream's one thread per token; the selection
+ * order, tie-break, NaN handling and renormalisation are upstream's. */
+qsfi_status qscu_router_topk(const qscu_router_topk_desc* desc, qsfi_cuda_stream stream);
+
+typedef struct { /* upstream qscu.h:27-33 */
+    qsfi_tensor2 gate;
+    qsfi_tensor2 up;
+    qsfi_tensor2 out;
+    uint32_t num_tokens;
+    uint32_t intermediate_size;
+} qscu_silu_and_mul_desc;
+
+/* out = silu(gate) * up on bf16 rows, upstream qscu.h:35 (qscu.cu:306-327). */
+qsfi_status qscu_silu_and_mul_bf16(const qscu_silu_and_mul_desc* desc, qsfi_cuda_stream stream);
+
+typedef struct { /* upstream qscu.h:42-48 */
+    qsfi_tensor2 gate_logits; /* bf16/f32 [num_tokens, 1] */
+    qsfi_tensor2 shared;      /* bf16 [num_tokens, hidden] */
+    qsfi_tensor2 out;         /* bf16 [num_tokens, hidden], updated in place */
+    uint32_t num_tokens;
+    uint32_t hidden_size;
+} qscu_qwen36_shared_expert_gate_add_desc;
+
+/* out += sigmoid(gate_logits[t]) * shared, upstream qscu.h:50-52 (qscu.cu:338-355). */
+qsfi_status qscu_qwen36_shared_expert_gate_add_bf16(
+    const qscu_qwen36_shared_expert_gate_add_desc* desc, qsfi_cuda_stream stream
+);
+
+/* ------------------------------------------------ dense bf16 GEMM (qscb) -- */
+
+typedef struct qscb_context qscb_context; /* upstream qscb.h:27 */
+
+typedef struct { /* upstream qscb.h:29-32 */
+    int32_t device_ordinal;
+    qsfi_cuda_stream stream;
+} qscb_context_desc;
+
+typedef struct { /* upstream qscb.h:34-45 */
+    qsfi_tensor2 x;      /* bf16 [rows, in_features], stride[1] == 1, padded rows allowed */
+    qsfi_tensor2 weight; /* bf16 [out_features, in_features] */
+    qsfi_tensor2 out;    /* bf16 or f32 [rows, out_features] */
+    uint32_t rows;
+    uint32_t in_features;
+    uint32_t out_features;
+    float alpha; /* 0 means 1 */
+    float beta;
+    qsfi_device_ptr workspace; /* unused by this build */
+    size_t workspace_bytes;
+} qscb_bf16_gemm_desc;
+
+/* out = alpha * x * weight^T + beta * out with f32 accumulation, upstream
+ * qscb.h:47-52 (qscb.cu:265-470). The router-logits GEMM and the shared-expert
+ * projections of the MoE layer go through this call (src/model.rs:2082-2090,
+ * 2184-2226). tcgen05 kind::f16 kernel; no cuBLASLt. */
+qsfi_status qscb_context_create(const qscb_context_desc* desc, qscb_context** out);
+void qscb_context_destroy(qscb_context* ctx);
+qsfi_status qscb_context_get_last_error(const qscb_context* ctx, qsfi_error_info* out);
+void qscb_context_clear_last_error(qscb_context* ctx);
+qsfi_status qscb_gemm_bf16(qscb_context* ctx, const qscb_bf16_gemm_desc* desc);
+
+/* ============================ additive entry points (no upstream symbol) == */
+
+/* Scale-factor tile layout used by the block-scaled tensor-core path
+ * ("tiled"): scales of a [rows, K] operand with one e4m3 scale per 16 elements
+ * are stored per (128-row block, 64-element k group) as a 512-byte tile,
+ *   byte = ((row_block * (K/64) + k_group) * 512) + (row % 32) * 16
+ *          + ((row / 32) % 4) * 4 + (k / 16) % 4,
+ * which is what one tcgen05.cp 32x128b.warpx4 moves into tensor memory. */
+
+/* Returns the number of bytes of the tiled scale buffer for a [rows, k] operand. */
+size_t qs3_nvfp4_tiled_scale_bytes(uint64_t rows, uint64_t k);
+
+typedef struct {
+    qsfi_tensor3 weight;        /* bf16 [experts, rows, k], contiguous */
+    qsfi_tensor3 packed;        /* u8 [experts, rows, k/2] out */
+    qsfi_tensor3 scale_linear;  /* optional e4m3 [experts, rows, k/16] out (declared ABI layout) */
+    qsfi_tensor1 scale_tiled;   /* optional u8 [experts * qs3_nvfp4_tiled_scale_bytes(rows,k)] out */
+    qsfi_tensor1 global_scale;  /* f32 [experts] out: amax / (6 * 448), 1 when amax == 0 */
+    uint32_t gated_rows;        /* != 0: rows = 2*inter (gate rows then up rows); the tiled scale
+                                   buffer then interleaves 64 gate rows with their 64 up rows per
+                                   128-row block, matching the gate_up GEMM tile */
+} qs3_nvfp4_quantize_weight_desc;
+
+/* Quantise bf16 expert weights to NVFP4 (e2m1 codes, one e4m3 scale per 16
+ * elements along k, one f32 scale per expert). Stands in for the quantised
+ * layout the upstream weight loader never produced (src/weight_loader.rs:33-66,
+ * AGENTS.md:45-47). */
+qsfi_status qs3_nvfp4_quantize_weight(qsfi_context* ctx, const qs3_nvfp4_quantize_weight_desc* desc);
+
+typedef struct {
+    qsfi_tensor2 x;            /* bf16 [rows, k] */
+    qsfi_tensor2 packed;       /* u8 [rows, k/2] out */
+    qsfi_tensor2 scale_linear; /* e4m3 [rows, k/16] out */
+    float global_scale;        /* 0 means 1 */
+    uint32_t rows;
+} qs3_nvfp4_quantize_act_desc;
+
+/* Quantise bf16 activation rows to the declared NVFP4 activation layout
+ * (hidden_packed / hidden_scale of qsfi_moe_nvfp4_execute_desc). */
+qsfi_status qs3_nvfp4_quantize_act(qsfi_context* ctx, const qs3_nvfp4_quantize_act_desc* desc);
+
+/* Re-tile declared-layout ("linear") weight scales into the tiled layout once,
+ * so that execute calls need not do it per call. */
+typedef struct {
+    qsfi_tensor3 scale_linear; /* e4m3 [experts, rows, k/16] */
+    qsfi_tensor1 scale_tiled;  /* u8 out */
+    uint32_t gated_rows;
+} qs3_nvfp4_tile_scales_desc;
+qsfi_status qs3_nvfp4_tile_scales(qsfi_context* ctx, const qs3_nvfp4_tile_scales_desc* desc);
+
+/* Whole MoE layer in one call: what upstream's execute_moe_mlp issues as five
+ * GEMM calls, a router call, a MoE call and two element-wise calls
+ * (src/model.rs:2072-2228), i.e. the QSFI_MOE_ROUTE_ROUTER_LOGITS mode upstream
+ * declares but rejects (qsfi_moe.cu:157-159). */
+typedef struct {
+    /* inputs */
+    qsfi_tensor2 hidden;        /* bf16 [num_tokens, hidden] */
+    qsfi_tensor2 router_weight; /* bf16 [num_experts, hidden] */
+    qsfi_tensor1 router_bias;   /* optional f32 [num_experts], added to the logits before top-k */
+    /* routed experts: bf16 plan -> *_weight bf16; NVFP4 plan -> packed + tiled scales */
+    qsfi_tensor3 gate_up_weight;       /* bf16 [E_local, 2I, H] or u8 [E_local, 2I, H/2] */
+    qsfi_tensor1 gate_up_scale_tiled;  /* NVFP4 only */
+    qsfi_tensor1 gate_up_global_scale; /* NVFP4 only, f32 [E_local] */
+    qsfi_tensor3 down_weight;          /* bf16 [E_local, H, I] or u8 [E_local, H, I/2] */
+    qsfi_tensor1 down_scale_tiled;     /* NVFP4 only */
+    qsfi_tensor1 down_global_scale;    /* NVFP4 only, f32 [E_local] */
+    /* optional shared expert (data == NULL on shared_gate_up_weight: none); same dtype family */
+    qsfi_tensor3 shared_gate_up_weight;       /* [1, 2*Is, H] (or packed) */
+    qsfi_tensor1 shared_gate_up_scale_tiled;
+    qsfi_tensor1 shared_gate_up_global_scale; /* f32 [1] */
+    qsfi_tensor3 shared_down_weight;          /* [1, H, Is] (or packed) */
+    qsfi_tensor1 shared_down_scale_tiled;
+    qsfi_tensor1 shared_down_global_scale;    /* f32 [1] */
+    qsfi_tensor2 shared_gate_weight;          /* bf16 [1, hidden]: sigmoid gate logit row */
+    uint32_t shared_intermediate_size;
+    /* routing parameters (upstream src/lib.rs:21-24 uses softmax, renormalise, 1.0) */
+    qscu_router_score score;
+    uint32_t renormalize;
+    float routed_scaling_factor;
+    float act_global_scale;  /* NVFP4: global scale of the hidden activations, 0 means 1 */
+    float act2_global_scale; /* NVFP4: global scale of the SwiGLU output, 0 means 1 */
+    /* outputs */
+    qsfi_tensor2 out;          /* bf16 [num_tokens, hidden] */
+    qsfi_tensor2 topk_ids;     /* optional i32 [num_tokens, top_k] out */
+    qsfi_tensor2 topk_weights; /* optional f32 [num_tokens, top_k] out */
+    qsfi_tensor2 router_logits; /* optional f32 [num_tokens, num_experts] out */
+    qsfi_tensor1 workspace;    /* u8 [>= qs3_moe_layer_workspace_size] */
+    uint32_t num_tokens;
+} qs3_moe_layer_desc;
+
+qsfi_status qs3_moe_layer_workspace_size(
+    qsfi_context* ctx, const qsfi_moe_plan* plan, uint32_t num_tokens,
+    uint32_t shared_intermediate_size, size_t* device_bytes
+);
+qsfi_status
+qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_layer_desc* desc);
+
+/* Routing tables of the last execute on this workspace, for parity checks:
+ * copies of counts[E_local], indptr[E_local+1], route_rows[T*K] (-1: not local),
+ * row_tokens[R_local], row_scales[R_local] (upstream qsfi_moe.cu:26-31). Device
+ * pointers into `workspace`; valid until the next execute on it. */
+typedef struct {
+    const int32_t* counts;
+    const int32_t* indptr;
+    const int32_t* route_rows;
+    const int32_t* row_tokens;
+    const float* row_scales;
+} qs3_moe_routing_view;
+qsfi_status qs3_moe_routing_tables(
+    qsfi_context* ctx, const qsfi_moe_plan* plan, uint32_t num_tokens, qsfi_device_ptr workspace,
+    qs3_moe_routing_view* out
+);
+
+/* Device-side error word of the tensor-core kernels: every wait inside them is
+ * bounded; a wait that runs out records where and the kernel returns. Reads
+ * (and clears) the word; synchronises the context's stream. 0 = no error. */
+qsfi_status qs3_moe_read_device_error(qsfi_context* ctx, uint32_t* code);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* QS3_MOE_H */

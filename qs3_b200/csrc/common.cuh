@@ -1,0 +1,183 @@
+// Internal declarations shared by the translation units of libqs3moe.so.
+#pragma once
+
+#include "../../include/qs3_moe.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+// Context object behind the opaque qsfi_context handle. Field order follows
+// upstream qsfi_internal.h:11-20 so that an object built against either
+// definition reads the same device ordinal, stream and error record.
+struct qsfi_context {
+    int32_t device_ordinal;
+    cudaStream_t stream;
+    void* float_workspace;
+    size_t float_workspace_bytes;
+    size_t int_workspace_bytes;
+    size_t host_int_workspace_bytes;
+    uint64_t scratch_generation;
+    qsfi_error_info last_error;
+};
+
+struct qsfi_moe_plan {
+    qsfi_moe_plan_desc desc;
+};
+
+namespace qs3 {
+
+constexpr size_t kWorkspaceAlign = 256;
+constexpr int kTileM = 128; // rows of one tensor-core tile; expert segments are padded to it
+
+// ---- error plumbing (upstream qsfi_context.cu:10-101) -------------------------
+void clear_error(qsfi_error_info* err);
+qsfi_status set_error(qsfi_context* ctx, qsfi_status status, qsfi_error_source source,
+                      int32_t native_code, const char* fmt, ...);
+qsfi_status set_invalid_arg(qsfi_context* ctx, const char* fmt, ...);
+qsfi_status set_unsupported(qsfi_context* ctx, const char* fmt, ...);
+qsfi_status set_cuda_error(qsfi_context* ctx, cudaError_t err, const char* op);
+qsfi_status activate_context(qsfi_context* ctx);
+qsfi_status status_from_cuda(cudaError_t err);
+
+// Device-side error word shared by the tensor-core kernels (one per device).
+uint32_t* device_error_word();
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+template <typename T> bool contiguous1(const T& t) { return t.stride[0] == 1; }
+template <typename T> bool contiguous2(const T& t)
+{
+    return t.stride[1] == 1 && t.stride[0] == t.shape[1];
+}
+template <typename T> bool contiguous3(const T& t)
+{
+    return t.stride[2] == 1 && t.stride[1] == t.shape[2]
+        && t.stride[0] == t.shape[1] * t.shape[2];
+}
+
+// ---- routing tables -------------------------------------------------------------
+// Everything the routed path derives from topk_ids, laid out in the workspace.
+struct RouteTables {
+    int32_t* counts;       // [E] routes per local expert
+    int32_t* indptr;       // [E+1] exclusive scan of counts
+    int32_t* pad_indptr;   // [E+1] exclusive scan of counts rounded up to kTileM
+    int32_t* route_rows;   // [R] dense row of a route (-1: expert not local)
+    int32_t* route_prows;  // [R] row in the padded layout (-1: expert not local)
+    int32_t* row_tokens;   // [R] token of a dense row
+    float* row_scales;     // [R] routing weight of a dense row
+    int32_t* tile_expert;  // [max_tiles]
+    int32_t* tile_row0;    // [max_tiles] first padded row of the tile
+    int32_t* tile_nrows;   // [max_tiles] valid rows in the tile
+    int32_t* total_tiles;  // [1]
+    int32_t* block_hist;   // [route_blocks * E] scratch of the counting sort
+    uint32_t max_tiles;
+    uint32_t max_pad_rows;
+    uint32_t route_blocks;
+};
+
+size_t route_tables_bytes(uint32_t routes, uint32_t experts);
+// Carves the tables out of `base` (may be NULL for sizing); returns bytes used.
+size_t route_tables_carve(char* base, uint32_t routes, uint32_t experts, RouteTables* out);
+// Counting sort of the routes by local expert, stable in route index.
+cudaError_t launch_route_sort(const int32_t* topk_ids, const float* topk_weights, uint32_t routes,
+                              uint32_t top_k, uint32_t local_offset, uint32_t experts,
+                              const RouteTables& rt, cudaStream_t stream);
+
+// ---- router -----------------------------------------------------------------------
+// `bias` (optional f32 [num_experts]) is added to the logits before scoring.
+cudaError_t launch_router_topk(const void* logits, int logits_bf16, const float* bias,
+                               int32_t* ids, float* weights, uint32_t num_tokens,
+                               uint32_t num_experts, uint32_t top_k, int sigmoid_score,
+                               int renormalize, float scaling, cudaStream_t stream);
+qsfi_status validate_router_desc(const qscu_router_topk_desc* d);
+
+// ---- permute / combine ----------------------------------------------------------
+cudaError_t launch_gather_bf16(const __nv_bfloat16* hidden, const int32_t* route_prows,
+                               uint32_t routes, uint32_t top_k, uint32_t hidden_size,
+                               __nv_bfloat16* expanded, cudaStream_t stream);
+
+struct CombineParams {
+    const int32_t* route_prows;   // [T*K]
+    const float* topk_weights;    // [T*K]
+    const __nv_bfloat16* expert_out; // [pad_rows, H]
+    __nv_bfloat16* out;           // [T, H]
+    uint32_t num_tokens, top_k, hidden_size;
+    // optional shared expert term: out += sigmoid(x . gate_w) * shared_out
+    const __nv_bfloat16* shared_out; // [T, H] or NULL
+    const __nv_bfloat16* hidden;     // [T, H] for the gate logit
+    const __nv_bfloat16* gate_w;     // [H]
+    int round_before_shared;         // 1: round the routed sum to bf16 first (upstream chain)
+};
+cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
+
+// ---- GEMMs ----------------------------------------------------------------------
+enum GemmEpilogue {
+    EPI_STORE_BF16 = 0,   // out = bf16(alpha * acc [+ beta * out])
+    EPI_STORE_F32 = 1,    // out = alpha * acc [+ beta * out] [+ bias[n]]
+    EPI_SWIGLU_BF16 = 2,  // out = bf16(silu(bf16(g)) * bf16(u))
+    EPI_SWIGLU_NVFP4 = 3  // out = nvfp4(silu(g) * u), packed + tiled scales
+};
+
+struct GemmProblem {
+    // A operand: [a_rows, k] row-major (bf16 elements or packed e2m1 bytes), pitch in BYTES
+    const void* a;
+    uint64_t a_rows;
+    uint64_t a_pitch_bytes;
+    const uint8_t* a_scale_tiled; // NVFP4 only
+    // B operand: [groups, b_rows, k]; b_rows = 2*n for gated problems
+    const void* b;
+    uint64_t b_pitch_bytes;
+    const uint8_t* b_scale_tiled; // NVFP4 only, per group qs3_nvfp4_tiled_scale_bytes(b_rows, k)
+    uint32_t groups;
+    uint32_t n; // output features (gated: intermediate size)
+    uint32_t k; // reduction length in elements
+    int nvfp4;
+    int gated;
+    int epilogue;
+    // tile tables (NULL: dense problem, tiles are consecutive 128-row blocks of A)
+    const int32_t* tile_expert;
+    const int32_t* tile_row0;
+    const int32_t* tile_nrows;
+    const int32_t* total_tiles;
+    uint32_t max_tiles;
+    // output
+    void* out;
+    uint64_t out_pitch_elems;   // elements (bytes for packed NVFP4 output)
+    uint8_t* out_scale_tiled;   // EPI_SWIGLU_NVFP4
+    float alpha;                // 0 means 1
+    float beta;
+    const float* group_scale;   // optional per-group multiplier on acc
+    const float* bias;          // optional f32 [n] (EPI_STORE_F32)
+    float out_global_scale;     // EPI_SWIGLU_NVFP4: global scale of the quantised output
+};
+// Chooses the tcgen05 kernel when the shape allows it and the plain CUDA-core
+// kernel otherwise (tiny or unaligned shapes; bf16 only).
+cudaError_t launch_gemm(const GemmProblem& p, cudaStream_t stream, const char** why_unsupported);
+bool gemm_tc_supported(const GemmProblem& p);
+
+// ---- NVFP4 ----------------------------------------------------------------------
+cudaError_t launch_nvfp4_gather_quantize(const __nv_bfloat16* hidden, const int32_t* route_prows,
+                                         uint32_t routes, uint32_t top_k, uint32_t hidden_size,
+                                         float global_scale, uint8_t* packed, uint8_t* scale_tiled,
+                                         cudaStream_t stream);
+cudaError_t launch_nvfp4_gather_packed(const uint8_t* hidden_packed, const uint8_t* hidden_scale,
+                                       const int32_t* route_prows, uint32_t routes, uint32_t top_k,
+                                       uint32_t hidden_size, uint8_t* packed, uint8_t* scale_tiled,
+                                       cudaStream_t stream);
+
+// ---- device helpers ---------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16)
+{
+    return __uint_as_float(bits16 << 16);
+}
+// upstream qscu.cu:253-256 / qsfi_moe.cu:461
+__device__ __forceinline__ float sigmoid_fast(float v) { return 1.0f / (1.0f + __expf(-v)); }
+#endif
+
+} // namespace qs3

@@ -1,0 +1,402 @@
+// Route permutation (histogram, scan, stable placement), token gather and the
+// weighted combine. Replaces upstream count_routes / prefix_sum / fill_route_rows /
+// scatter_hidden / finalize (qsfi_moe.cu:327-409,465-492).
+#include "common.cuh"
+
+namespace qs3 {
+
+namespace {
+
+constexpr int kSortWarps = 8;               // warps per block of the counting sort
+constexpr int kSortRounds = 4;              // 32-route rounds per warp
+constexpr int kSortChunk = kSortWarps * kSortRounds * 32; // routes per block (1024)
+
+__device__ __forceinline__ int local_expert(const int32_t* ids, uint32_t route, uint32_t routes,
+                                            uint32_t local_offset, uint32_t experts)
+{
+    if (route >= routes)
+        return -1;
+    const int local = ids[route] - static_cast<int>(local_offset);
+    return (local < 0 || local >= static_cast<int>(experts)) ? -1 : local;
+}
+
+// Per-warp histogram of the block's routes into s_hist[warp][expert] (u16: a warp
+// sees at most kSortRounds * 32 routes). Each warp owns a contiguous run of routes,
+// which is what makes the later placement stable.
+__device__ __forceinline__ void
+warp_histogram(const int32_t* ids, uint32_t routes, uint32_t local_offset, uint32_t experts,
+               uint16_t* s_hist)
+{
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t i = threadIdx.x; i < kSortWarps * experts; i += blockDim.x)
+        s_hist[i] = 0;
+    __syncthreads();
+    uint16_t* mine = s_hist + static_cast<size_t>(warp) * experts;
+    const uint32_t base = blockIdx.x * kSortChunk + warp * (kSortRounds * 32);
+#pragma unroll
+    for (int r = 0; r < kSortRounds; ++r) {
+        const int e = local_expert(ids, base + r * 32 + lane, routes, local_offset, experts);
+        const uint32_t peers = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && lane == static_cast<uint32_t>(__ffs(peers) - 1))
+            mine[e] += static_cast<uint16_t>(__popc(peers));
+        __syncwarp();
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kSortWarps * 32)
+route_hist_kernel(const int32_t* __restrict__ ids, uint32_t routes, uint32_t local_offset,
+                  uint32_t experts, int32_t* __restrict__ block_hist)
+{
+    extern __shared__ uint16_t s_hist[];
+    warp_histogram(ids, routes, local_offset, experts, s_hist);
+    for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
+        int total = 0;
+#pragma unroll
+        for (int w = 0; w < kSortWarps; ++w)
+            total += s_hist[static_cast<size_t>(w) * experts + e];
+        block_hist[static_cast<size_t>(blockIdx.x) * experts + e] = total;
+    }
+}
+
+// Single block: per expert, exclusive scan of the block histograms (column scan),
+// then exclusive scans over experts of the counts, of the counts padded to the
+// tile height, and of the tile counts; finally the tile table.
+__global__ void __launch_bounds__(1024)
+route_scan_kernel(int32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_t experts,
+                  RouteTables rt)
+{
+    __shared__ int s_warp[3][32];
+    __shared__ int s_carry[3];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x < 3)
+        s_carry[threadIdx.x] = 0;
+    __syncthreads();
+    for (uint32_t e0 = 0; e0 < experts; e0 += blockDim.x) {
+        const uint32_t e = e0 + threadIdx.x;
+        int count = 0;
+        if (e < experts) {
+            // loads are issued in independent batches so that their latencies overlap
+            constexpr uint32_t kBatch = 16;
+            for (uint32_t b0 = 0; b0 < num_blocks; b0 += kBatch) {
+                int v[kBatch];
+#pragma unroll
+                for (uint32_t j = 0; j < kBatch; ++j)
+                    v[j] = b0 + j < num_blocks
+                        ? block_hist[static_cast<size_t>(b0 + j) * experts + e]
+                        : 0;
+#pragma unroll
+                for (uint32_t j = 0; j < kBatch; ++j) {
+                    if (b0 + j < num_blocks)
+                        block_hist[static_cast<size_t>(b0 + j) * experts + e] = count;
+                    count += v[j];
+                }
+            }
+            rt.counts[e] = count;
+        }
+        const int tiles = (count + kTileM - 1) / kTileM;
+        int v[3] = { count, tiles * kTileM, tiles };
+        int incl[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            int x = v[j];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(0xffffffffu, x, o);
+                if (lane >= static_cast<uint32_t>(o))
+                    x += y;
+            }
+            incl[j] = x;
+            if (lane == 31)
+                s_warp[j][warp] = x;
+        }
+        __syncthreads();
+        if (warp == 0) {
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                int x = s_warp[j][lane];
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int y = __shfl_up_sync(0xffffffffu, x, o);
+                    if (lane >= static_cast<uint32_t>(o))
+                        x += y;
+                }
+                s_warp[j][lane] = x; // inclusive over warps
+            }
+        }
+        __syncthreads();
+        int excl[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j)
+            excl[j] = s_carry[j] + (warp > 0 ? s_warp[j][warp - 1] : 0) + incl[j] - v[j];
+        if (e < experts) {
+            rt.indptr[e] = excl[0];
+            rt.pad_indptr[e] = excl[1];
+            for (int m = 0; m < tiles; ++m) {
+                rt.tile_expert[excl[2] + m] = static_cast<int32_t>(e);
+                rt.tile_row0[excl[2] + m] = excl[1] + m * kTileM;
+                rt.tile_nrows[excl[2] + m] = min(kTileM, count - m * kTileM);
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+#pragma unroll
+            for (int j = 0; j < 3; ++j)
+                s_carry[j] += s_warp[j][31];
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        rt.indptr[experts] = s_carry[0];
+        rt.pad_indptr[experts] = s_carry[1];
+        *rt.total_tiles = s_carry[2];
+    }
+}
+
+// Placement: row of a route = segment start + routes of the same expert in earlier
+// blocks + in earlier warps of this block + earlier in this warp. Stable in route
+// index, so the permutation is reproducible (upstream's is atomics-ordered).
+__global__ void __launch_bounds__(kSortWarps * 32)
+route_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weights,
+                   uint32_t routes, uint32_t top_k, uint32_t local_offset, uint32_t experts,
+                   RouteTables rt)
+{
+    extern __shared__ uint16_t s_hist[];
+    warp_histogram(ids, routes, local_offset, experts, s_hist);
+    // exclusive prefix over the warps of the block, per expert
+    for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
+        int run = 0;
+#pragma unroll
+        for (int w = 0; w < kSortWarps; ++w) {
+            const size_t i = static_cast<size_t>(w) * experts + e;
+            const int v = s_hist[i];
+            s_hist[i] = static_cast<uint16_t>(run);
+            run += v;
+        }
+    }
+    __syncthreads();
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint16_t* mine = s_hist + static_cast<size_t>(warp) * experts;
+    const uint32_t base = blockIdx.x * kSortChunk + warp * (kSortRounds * 32);
+    const int32_t* block_off = rt.block_hist + static_cast<size_t>(blockIdx.x) * experts;
+#pragma unroll
+    for (int r = 0; r < kSortRounds; ++r) {
+        const uint32_t route = base + r * 32 + lane;
+        const int e = local_expert(ids, route, routes, local_offset, experts);
+        const uint32_t peers = __match_any_sync(0xffffffffu, e);
+        int in_block = 0;
+        if (e >= 0)
+            in_block = mine[e] + __popc(peers & ((1u << lane) - 1u));
+        __syncwarp();
+        if (e >= 0 && lane == static_cast<uint32_t>(__ffs(peers) - 1))
+            mine[e] += static_cast<uint16_t>(__popc(peers));
+        __syncwarp();
+        if (route < routes) {
+            if (e >= 0) {
+                const int off = block_off[e] + in_block;
+                const int row = rt.indptr[e] + off;
+                rt.route_rows[route] = row;
+                rt.route_prows[route] = rt.pad_indptr[e] + off;
+                rt.row_tokens[row] = static_cast<int32_t>(route / top_k);
+                rt.row_scales[row] = weights[route];
+            } else {
+                rt.route_rows[route] = -1;
+                rt.route_prows[route] = -1;
+            }
+        }
+    }
+}
+
+// expanded[prow, :] = hidden[route / top_k, :]; one warp per route, 16-byte copies.
+__global__ void __launch_bounds__(256)
+gather_bf16_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__ route_prows,
+                   uint32_t routes, uint32_t top_k, uint32_t vec_per_row,
+                   uint4* __restrict__ expanded)
+{
+    const uint32_t route = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (route >= routes)
+        return;
+    const int prow = route_prows[route];
+    if (prow < 0)
+        return;
+    const uint4* src = hidden + static_cast<size_t>(route / top_k) * vec_per_row;
+    uint4* dst = expanded + static_cast<size_t>(prow) * vec_per_row;
+    for (uint32_t i = threadIdx.x & 31; i < vec_per_row; i += 32)
+        dst[i] = src[i];
+}
+
+// out[t, :] = bf16(sum_k w[t,k] * f32(Y2[prow(t,k), :])) (+ shared-expert term).
+// One warp per token; k ascending and f32 accumulation as upstream finalize_kernel
+// (qsfi_moe.cu:465-492). Each lane owns 8-element chunks of the row.
+__global__ void __launch_bounds__(256) combine_kernel(CombineParams p)
+{
+    const uint32_t token = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const uint32_t lane = threadIdx.x & 31;
+    if (token >= p.num_tokens)
+        return;
+    const uint32_t vec_per_row = p.hidden_size / 8;
+
+    float gate = 0.0f;
+    if (p.shared_out != nullptr) {
+        // gate logit x . w_gate in f32 (upstream computes it as an N = 1 GEMM,
+        // src/model.rs:2218-2226)
+        const uint4* x = reinterpret_cast<const uint4*>(p.hidden) + static_cast<size_t>(token) * vec_per_row;
+        const uint4* w = reinterpret_cast<const uint4*>(p.gate_w);
+        float dot = 0.0f;
+        for (uint32_t i = lane; i < vec_per_row; i += 32) {
+            const uint4 xv = x[i], wv = w[i];
+            const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
+            const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                dot += bf16_bits_to_f32(xs[j] & 0xffffu) * bf16_bits_to_f32(ws[j] & 0xffffu);
+                dot += bf16_bits_to_f32(xs[j] >> 16) * bf16_bits_to_f32(ws[j] >> 16);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        gate = sigmoid_fast(dot);
+    }
+
+    // routing of this token: lane k holds route k
+    int my_row = -1;
+    float my_w = 0.0f;
+    if (lane < p.top_k) {
+        my_row = p.route_prows[static_cast<size_t>(token) * p.top_k + lane];
+        my_w = p.topk_weights[static_cast<size_t>(token) * p.top_k + lane];
+    }
+    const uint4* y2 = reinterpret_cast<const uint4*>(p.expert_out);
+    uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
+    for (uint32_t i = lane; i < vec_per_row; i += 32) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            acc[j] = 0.0f;
+        for (uint32_t k = 0; k < p.top_k; ++k) {
+            const int row = __shfl_sync(0xffffffffu, my_row, k);
+            const float w = __shfl_sync(0xffffffffu, my_w, k);
+            if (row < 0)
+                continue;
+            const uint4 v = y2[static_cast<size_t>(row) * vec_per_row + i];
+            const uint32_t vs[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[2 * j] += w * bf16_bits_to_f32(vs[j] & 0xffffu);
+                acc[2 * j + 1] += w * bf16_bits_to_f32(vs[j] >> 16);
+            }
+        }
+        if (p.shared_out != nullptr) {
+            const uint4 s = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
+            const uint32_t ss[4] = { s.x, s.y, s.z, s.w };
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float a0 = acc[2 * j], a1 = acc[2 * j + 1];
+                if (p.round_before_shared) { // upstream rounds the routed sum to bf16 first
+                    a0 = __bfloat162float(__float2bfloat16(a0));
+                    a1 = __bfloat162float(__float2bfloat16(a1));
+                }
+                acc[2 * j] = a0 + gate * bf16_bits_to_f32(ss[j] & 0xffffu);
+                acc[2 * j + 1] = a1 + gate * bf16_bits_to_f32(ss[j] >> 16);
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 r = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+            o[j] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+template <typename T> T* carve(char* base, size_t& offset, size_t count)
+{
+    offset = align_up(offset, kWorkspaceAlign);
+    T* p = base != nullptr ? reinterpret_cast<T*>(base + offset) : nullptr;
+    offset += count * sizeof(T);
+    return p;
+}
+
+} // namespace
+
+size_t route_tables_carve(char* base, uint32_t routes, uint32_t experts, RouteTables* out)
+{
+    RouteTables rt {};
+    size_t off = 0;
+    const uint64_t seg = routes < experts ? routes : experts; // experts that can hold a row
+    const uint64_t max_pad_rows = align_up(routes, kTileM) + seg * kTileM;
+    rt.max_pad_rows = static_cast<uint32_t>(max_pad_rows);
+    rt.max_tiles = static_cast<uint32_t>(max_pad_rows / kTileM);
+    rt.route_blocks = (routes + kSortChunk - 1) / kSortChunk;
+    rt.counts = carve<int32_t>(base, off, experts);
+    rt.indptr = carve<int32_t>(base, off, experts + 1);
+    rt.pad_indptr = carve<int32_t>(base, off, experts + 1);
+    rt.route_rows = carve<int32_t>(base, off, routes);
+    rt.route_prows = carve<int32_t>(base, off, routes);
+    rt.row_tokens = carve<int32_t>(base, off, routes);
+    rt.row_scales = carve<float>(base, off, routes);
+    rt.tile_expert = carve<int32_t>(base, off, rt.max_tiles);
+    rt.tile_row0 = carve<int32_t>(base, off, rt.max_tiles);
+    rt.tile_nrows = carve<int32_t>(base, off, rt.max_tiles);
+    rt.total_tiles = carve<int32_t>(base, off, 1);
+    rt.block_hist = carve<int32_t>(base, off, static_cast<size_t>(rt.route_blocks) * experts);
+    if (out != nullptr)
+        *out = rt;
+    return align_up(off, kWorkspaceAlign);
+}
+
+size_t route_tables_bytes(uint32_t routes, uint32_t experts)
+{
+    return route_tables_carve(nullptr, routes, experts, nullptr);
+}
+
+cudaError_t launch_route_sort(const int32_t* topk_ids, const float* topk_weights, uint32_t routes,
+                              uint32_t top_k, uint32_t local_offset, uint32_t experts,
+                              const RouteTables& rt, cudaStream_t stream)
+{
+    const size_t smem = static_cast<size_t>(kSortWarps) * experts * sizeof(uint16_t);
+    if (smem > 200 * 1024)
+        return cudaErrorInvalidValue;
+    if (smem > 48 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(route_hist_kernel,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem));
+        if (err == cudaSuccess)
+            err = cudaFuncSetAttribute(route_place_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+        if (err != cudaSuccess)
+            return err;
+    }
+    route_hist_kernel<<<rt.route_blocks, kSortWarps * 32, smem, stream>>>(
+        topk_ids, routes, local_offset, experts, rt.block_hist);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess)
+        return err;
+    route_scan_kernel<<<1, 1024, 0, stream>>>(rt.block_hist, rt.route_blocks, experts, rt);
+    err = cudaGetLastError();
+    if (err != cudaSuccess)
+        return err;
+    route_place_kernel<<<rt.route_blocks, kSortWarps * 32, smem, stream>>>(
+        topk_ids, topk_weights, routes, top_k, local_offset, experts, rt);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather_bf16(const __nv_bfloat16* hidden, const int32_t* route_prows,
+                               uint32_t routes, uint32_t top_k, uint32_t hidden_size,
+                               __nv_bfloat16* expanded, cudaStream_t stream)
+{
+    gather_bf16_kernel<<<(routes + 7) / 8, 256, 0, stream>>>(
+        reinterpret_cast<const uint4*>(hidden), route_prows, routes, top_k, hidden_size / 8,
+        reinterpret_cast<uint4*>(expanded));
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream)
+{
+    combine_kernel<<<(p.num_tokens + 7) / 8, 256, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+} // namespace qs3

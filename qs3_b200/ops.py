@@ -1,0 +1,429 @@
+"""Host-side operator layer over the C ABI, working on torch device tensors.
+
+Mirrors the operator descriptors of the upstream runtime
+(``src/runtime/kernels.rs:371-508,692-875``: ``RouterTopK``, ``MoeBf16PlanConfig``,
+``MoeBf16Execute``, ``Bf16Gemm``, ``SiluAndMulBf16``,
+``Qwen36SharedExpertGateAddBf16``) with the same argument meaning and the same
+error classes: a failing call raises :class:`Qs3Error` carrying the
+``qsfi_status`` and the context's last-error message, like the upstream
+``Status`` results. torch is used only to own device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import capi
+
+_STATUS_NAMES = {0: "Ok", 1: "InvalidArgument", 2: "Unsupported", 3: "OutOfMemory",
+                 4: "CudaError", 5: "BackendError", 6: "InternalError"}
+
+
+class Qs3Error(RuntimeError):
+    def __init__(self, status: int, message: str = ""):
+        self.status = status
+        self.message = message
+        super().__init__(f"{_STATUS_NAMES.get(status, status)}: {message}")
+
+
+_TORCH_DTYPES = {
+    torch.float32: capi.DTYPE_F32, torch.float16: capi.DTYPE_F16, torch.bfloat16: capi.DTYPE_BF16,
+    torch.int32: capi.DTYPE_I32, torch.int8: capi.DTYPE_I8, torch.uint8: capi.DTYPE_U8,
+    torch.float8_e4m3fn: capi.DTYPE_FP8_E4M3,
+}
+
+
+def _desc(t, rank, dtype=None):
+    """qsfi_tensorN view of a torch tensor (None -> absent optional tensor)."""
+    cls = {1: capi.Tensor1, 2: capi.Tensor2, 3: capi.Tensor3}[rank]
+    d = cls()
+    if t is None:
+        return d
+    if t.dim() != rank:
+        raise Qs3Error(capi.STATUS_INVALID_ARGUMENT, f"expected a rank-{rank} tensor, got {t.dim()}")
+    d.data = t.data_ptr()
+    d.dtype = dtype if dtype is not None else _TORCH_DTYPES.get(t.dtype, capi.DTYPE_INVALID)
+    for i in range(rank):
+        d.shape[i] = t.shape[i]
+        d.stride[i] = t.stride(i)
+    return d
+
+
+def _stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class Context:
+    """``qsfi_context``: device ordinal + stream + last-error record."""
+
+    def __init__(self, device: int | None = None, stream: int | None = None):
+        self._lib = capi.load()
+        if device is None:
+            device = torch.cuda.current_device()
+        self.device = device
+        desc = capi.ContextDesc(device, stream if stream is not None else _stream_ptr(device))
+        handle = C.c_void_p()
+        status = self._lib.qsfi_context_create(C.byref(desc), C.byref(handle))
+        if status != capi.STATUS_OK:
+            raise Qs3Error(status, "qsfi_context_create failed")
+        self.handle = handle
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self._lib.qsfi_context_destroy(self.handle)
+            self.handle = None
+
+    __del__ = close
+
+    def set_stream(self, stream_ptr: int):
+        self.check(self._lib.qsfi_context_set_stream(self.handle, C.c_void_p(stream_ptr)))
+
+    def use_current_stream(self):
+        self.set_stream(_stream_ptr(self.device))
+
+    def last_error(self) -> capi.ErrorInfo:
+        info = capi.ErrorInfo()
+        self._lib.qsfi_context_get_last_error(self.handle, C.byref(info))
+        return info
+
+    def check(self, status: int):
+        if status != capi.STATUS_OK:
+            raise Qs3Error(status, self.last_error().message.decode(errors="replace"))
+
+    def validate_target(self):
+        self.check(self._lib.qsfi_context_validate_target(self.handle))
+
+    def read_device_error(self) -> int:
+        code = C.c_uint32(0)
+        self.check(self._lib.qs3_moe_read_device_error(self.handle, C.byref(code)))
+        return code.value
+
+
+@dataclass
+class MoePlanConfig:
+    """Fields of ``qsfi_moe_plan_desc`` (upstream qsfi.h:222-236)."""
+    max_num_tokens: int
+    hidden_size: int
+    intermediate_size: int
+    num_experts: int
+    top_k: int
+    local_expert_offset: int = 0
+    local_num_experts: int | None = None
+    backend: int = capi.MOE_BACKEND_STAGED_BF16
+    route_mode: int = capi.MOE_ROUTE_PRECOMPUTED_TOPK
+    activation_dtype: int | None = None
+    weight_dtype: int | None = None
+    output_dtype: int = capi.DTYPE_BF16
+
+    def to_c(self) -> capi.MoePlanDesc:
+        nv = self.backend == capi.MOE_BACKEND_NVFP4
+        d = capi.MoePlanDesc()
+        d.backend = self.backend
+        d.route_mode = self.route_mode
+        d.max_num_tokens = self.max_num_tokens
+        d.hidden_size = self.hidden_size
+        d.intermediate_size = self.intermediate_size
+        d.num_experts = self.num_experts
+        d.top_k = self.top_k
+        d.local_expert_offset = self.local_expert_offset
+        d.local_num_experts = self.num_experts if self.local_num_experts is None else self.local_num_experts
+        default = capi.DTYPE_NVFP4_E2M1 if nv else capi.DTYPE_BF16
+        d.activation_dtype = default if self.activation_dtype is None else self.activation_dtype
+        d.weight_dtype = default if self.weight_dtype is None else self.weight_dtype
+        d.output_dtype = self.output_dtype
+        return d
+
+
+class MoePlan:
+    def __init__(self, ctx: Context, config: MoePlanConfig):
+        self.ctx = ctx
+        self.config = config
+        handle = C.c_void_p()
+        desc = config.to_c()
+        ctx.check(ctx._lib.qsfi_moe_plan_create(ctx.handle, C.byref(desc), C.byref(handle)))
+        self.handle = handle
+        self.desc = desc
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.ctx._lib.qsfi_moe_plan_destroy(self.handle)
+            self.handle = None
+
+    __del__ = close
+
+    def workspace_size(self, num_tokens: int) -> int:
+        n = C.c_size_t(0)
+        self.ctx.check(self.ctx._lib.qsfi_moe_workspace_size(self.ctx.handle, self.handle, num_tokens,
+                                                             C.byref(n)))
+        return n.value
+
+    def layer_workspace_size(self, num_tokens: int, shared_intermediate_size: int = 0) -> int:
+        n = C.c_size_t(0)
+        self.ctx.check(self.ctx._lib.qs3_moe_layer_workspace_size(
+            self.ctx.handle, self.handle, num_tokens, shared_intermediate_size, C.byref(n)))
+        return n.value
+
+    def routing_tables(self, workspace: torch.Tensor, num_tokens: int):
+        """counts, indptr, route_rows, row_tokens, row_scales of the last execute."""
+        view = capi.RoutingView()
+        self.ctx.check(self.ctx._lib.qs3_moe_routing_tables(
+            self.ctx.handle, self.handle, num_tokens, C.c_void_p(workspace.data_ptr()), C.byref(view)))
+        e = self.desc.local_num_experts
+        r = num_tokens * self.desc.top_k
+        base = workspace.data_ptr()
+
+        def grab(ptr, count, dtype):
+            off = ptr - base
+            return workspace[off:off + count * 4].view(dtype).clone()
+
+        torch.cuda.synchronize()
+        counts = grab(view.counts, e, torch.int32)
+        indptr = grab(view.indptr, e + 1, torch.int32)
+        route_rows = grab(view.route_rows, r, torch.int32)
+        n = int(indptr[-1].item())
+        row_tokens = grab(view.row_tokens, r, torch.int32)[:n]
+        row_scales = grab(view.row_scales, r, torch.float32)[:n]
+        return counts, indptr, route_rows, row_tokens, row_scales
+
+
+# ------------------------------------------------------------------ qscu ops ---
+
+def router_topk(logits, topk_ids, topk_weights, *, score=capi.ROUTER_SCORE_SOFTMAX, renormalize=True,
+                routed_scaling_factor=1.0, num_tokens=None, num_experts=None, top_k=None, stream=None):
+    """``qscu_router_topk`` (upstream qscu.h:278; builder src/runtime/kernels.rs:692-741)."""
+    lib = capi.load()
+    d = capi.RouterTopkDesc()
+    d.logits = _desc(logits, 2)
+    d.topk_ids = _desc(topk_ids, 2)
+    d.topk_weights = _desc(topk_weights, 2)
+    d.num_tokens = logits.shape[0] if num_tokens is None else num_tokens
+    d.num_experts = logits.shape[1] if num_experts is None else num_experts
+    d.top_k = topk_ids.shape[1] if top_k is None else top_k
+    d.score = score
+    d.renormalize = 1 if renormalize else 0
+    d.routed_scaling_factor = routed_scaling_factor
+    status = lib.qscu_router_topk(C.byref(d), C.c_void_p(_stream_ptr() if stream is None else stream))
+    if status != capi.STATUS_OK:
+        raise Qs3Error(status, "qscu_router_topk")
+
+
+def silu_and_mul_bf16(gate, up, out, stream=None):
+    """``qscu_silu_and_mul_bf16`` (upstream qscu.h:35)."""
+    lib = capi.load()
+    d = capi.SiluAndMulDesc()
+    d.gate = _desc(gate, 2)
+    d.up = _desc(up, 2)
+    d.out = _desc(out, 2)
+    d.num_tokens = out.shape[0]
+    d.intermediate_size = out.shape[1]
+    status = lib.qscu_silu_and_mul_bf16(C.byref(d), C.c_void_p(_stream_ptr() if stream is None else stream))
+    if status != capi.STATUS_OK:
+        raise Qs3Error(status, "qscu_silu_and_mul_bf16")
+
+
+def shared_expert_gate_add_bf16(gate_logits, shared, out, stream=None):
+    """``qscu_qwen36_shared_expert_gate_add_bf16`` (upstream qscu.h:50-52)."""
+    lib = capi.load()
+    d = capi.SharedExpertGateAddDesc()
+    d.gate_logits = _desc(gate_logits, 2)
+    d.shared = _desc(shared, 2)
+    d.out = _desc(out, 2)
+    d.num_tokens = out.shape[0]
+    d.hidden_size = out.shape[1]
+    status = lib.qscu_qwen36_shared_expert_gate_add_bf16(
+        C.byref(d), C.c_void_p(_stream_ptr() if stream is None else stream))
+    if status != capi.STATUS_OK:
+        raise Qs3Error(status, "qscu_qwen36_shared_expert_gate_add_bf16")
+
+
+# ------------------------------------------------------------------ qscb op ---
+
+class GemmContext:
+    """``qscb_context`` (upstream qscb.h:27-52)."""
+
+    def __init__(self, device: int | None = None, stream: int | None = None):
+        self._lib = capi.load()
+        if device is None:
+            device = torch.cuda.current_device()
+        desc = capi.QscbContextDesc(device, stream if stream is not None else _stream_ptr(device))
+        handle = C.c_void_p()
+        status = self._lib.qscb_context_create(C.byref(desc), C.byref(handle))
+        if status != capi.STATUS_OK:
+            raise Qs3Error(status, "qscb_context_create failed")
+        self.handle = handle
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self._lib.qscb_context_destroy(self.handle)
+            self.handle = None
+
+    __del__ = close
+
+    def gemm_bf16(self, x, weight, out, alpha=0.0, beta=0.0):
+        """out = alpha * x @ weight.T + beta * out (``qscb_gemm_bf16``)."""
+        d = capi.QscbGemmDesc()
+        d.x = _desc(x, 2)
+        d.weight = _desc(weight, 2)
+        d.out = _desc(out, 2)
+        d.rows = x.shape[0]
+        d.in_features = x.shape[1]
+        d.out_features = weight.shape[0]
+        d.alpha = alpha
+        d.beta = beta
+        status = self._lib.qscb_gemm_bf16(self.handle, C.byref(d))
+        if status != capi.STATUS_OK:
+            info = capi.ErrorInfo()
+            self._lib.qscb_context_get_last_error(self.handle, C.byref(info))
+            raise Qs3Error(status, info.message.decode(errors="replace"))
+
+
+# ------------------------------------------------------------------- MoE ops ---
+
+def moe_execute_bf16(plan: MoePlan, hidden, topk_ids, topk_weights, gate_up_weight, down_weight, out,
+                     workspace, num_tokens=None):
+    """``qsfi_moe_execute_bf16`` (upstream qsfi.h:339-341)."""
+    ctx = plan.ctx
+    d = capi.MoeBf16ExecuteDesc()
+    d.hidden = _desc(hidden, 2)
+    d.topk_ids = _desc(topk_ids, 2)
+    d.topk_weights = _desc(topk_weights, 2)
+    d.gate_up_weight = _desc(gate_up_weight, 3)
+    d.down_weight = _desc(down_weight, 3)
+    d.out = _desc(out, 2)
+    d.workspace = _desc(workspace, 1)
+    d.num_tokens = hidden.shape[0] if num_tokens is None else num_tokens
+    ctx.check(ctx._lib.qsfi_moe_execute_bf16(ctx.handle, plan.handle, C.byref(d)))
+
+
+def moe_execute_nvfp4(plan: MoePlan, hidden_packed, hidden_scale, topk_ids, topk_weights,
+                      gate_up_weight_packed, gate_up_weight_scale, down_weight_packed, down_weight_scale,
+                      out, workspace, expert_output_scale=None, num_tokens=None):
+    """``qsfi_moe_execute_nvfp4`` (upstream qsfi.h:342-344; declared layout qsfi.h:249-266)."""
+    ctx = plan.ctx
+    d = capi.MoeNvfp4ExecuteDesc()
+    d.hidden_packed = _desc(hidden_packed, 2)
+    d.hidden_scale = _desc(hidden_scale, 2, capi.DTYPE_FP8_E4M3)
+    d.topk_ids = _desc(topk_ids, 2)
+    d.topk_weights = _desc(topk_weights, 2)
+    d.gate_up_weight_packed = _desc(gate_up_weight_packed, 3)
+    d.gate_up_weight_scale = _desc(gate_up_weight_scale, 3, capi.DTYPE_FP8_E4M3)
+    d.down_weight_packed = _desc(down_weight_packed, 3)
+    d.down_weight_scale = _desc(down_weight_scale, 3, capi.DTYPE_FP8_E4M3)
+    d.expert_output_scale = _desc(expert_output_scale, 1)
+    d.out = _desc(out, 2)
+    d.workspace = _desc(workspace, 1)
+    d.num_tokens = hidden_packed.shape[0] if num_tokens is None else num_tokens
+    ctx.check(ctx._lib.qsfi_moe_execute_nvfp4(ctx.handle, plan.handle, C.byref(d)))
+
+
+@dataclass
+class Nvfp4Weight:
+    """Prepared NVFP4 weight: packed codes, linear and tiled scales, per-expert global scale."""
+    packed: torch.Tensor        # u8 [E, rows, k/2]
+    scale_linear: torch.Tensor  # u8 (e4m3 codes) [E, rows, k/16]
+    scale_tiled: torch.Tensor   # u8 [E * tiled_bytes]
+    global_scale: torch.Tensor  # f32 [E]
+
+
+def nvfp4_tiled_scale_bytes(rows: int, k: int) -> int:
+    return int(capi.load().qs3_nvfp4_tiled_scale_bytes(rows, k))
+
+
+def nvfp4_quantize_weight(ctx: Context, weight: torch.Tensor, gated: bool, linear: bool = True) -> Nvfp4Weight:
+    """``qs3_nvfp4_quantize_weight``: bf16 [E, rows, k] -> NVFP4."""
+    e, rows, k = weight.shape
+    dev = weight.device
+    packed = torch.empty((e, rows, k // 2), dtype=torch.uint8, device=dev)
+    sl = torch.empty((e, rows, k // 16), dtype=torch.uint8, device=dev) if linear else None
+    st = torch.zeros(e * nvfp4_tiled_scale_bytes(rows, k), dtype=torch.uint8, device=dev)
+    g = torch.empty(e, dtype=torch.float32, device=dev)
+    d = capi.Nvfp4QuantizeWeightDesc()
+    d.weight = _desc(weight, 3)
+    d.packed = _desc(packed, 3)
+    d.scale_linear = _desc(sl, 3, capi.DTYPE_FP8_E4M3)
+    d.scale_tiled = _desc(st, 1)
+    d.global_scale = _desc(g, 1)
+    d.gated_rows = 1 if gated else 0
+    ctx.check(ctx._lib.qs3_nvfp4_quantize_weight(ctx.handle, C.byref(d)))
+    return Nvfp4Weight(packed, sl, st, g)
+
+
+def nvfp4_quantize_act(ctx: Context, x: torch.Tensor, global_scale: float = 1.0):
+    """``qs3_nvfp4_quantize_act``: bf16 [rows, k] -> (packed u8 [rows, k/2], e4m3 codes [rows, k/16])."""
+    rows, k = x.shape
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((rows, k // 16), dtype=torch.uint8, device=x.device)
+    d = capi.Nvfp4QuantizeActDesc()
+    d.x = _desc(x, 2)
+    d.packed = _desc(packed, 2)
+    d.scale_linear = _desc(scale, 2, capi.DTYPE_FP8_E4M3)
+    d.global_scale = global_scale
+    d.rows = rows
+    ctx.check(ctx._lib.qs3_nvfp4_quantize_act(ctx.handle, C.byref(d)))
+    return packed, scale
+
+
+def nvfp4_tile_scales(ctx: Context, scale_linear: torch.Tensor, gated: bool) -> torch.Tensor:
+    """``qs3_nvfp4_tile_scales``: e4m3 codes [E, rows, k/16] -> tiled buffer."""
+    e, rows, kb = scale_linear.shape
+    st = torch.zeros(e * nvfp4_tiled_scale_bytes(rows, kb * 16), dtype=torch.uint8, device=scale_linear.device)
+    d = capi.Nvfp4TileScalesDesc()
+    d.scale_linear = _desc(scale_linear, 3, capi.DTYPE_FP8_E4M3)
+    d.scale_tiled = _desc(st, 1)
+    d.gated_rows = 1 if gated else 0
+    ctx.check(ctx._lib.qs3_nvfp4_tile_scales(ctx.handle, C.byref(d)))
+    return st
+
+
+@dataclass
+class SharedExpert:
+    """Shared-expert weights of one layer (upstream src/model.rs:963-968)."""
+    gate_up: object          # bf16 [1, 2*Is, H] tensor or Nvfp4Weight
+    down: object             # bf16 [1, H, Is] tensor or Nvfp4Weight
+    gate_weight: torch.Tensor  # bf16 [1, H]
+    intermediate_size: int
+
+
+def moe_layer_execute(plan: MoePlan, hidden, router_weight, gate_up, down, out, workspace, *,
+                      router_bias=None, shared: SharedExpert | None = None,
+                      score=capi.ROUTER_SCORE_SOFTMAX, renormalize=True, routed_scaling_factor=1.0,
+                      act_global_scale=1.0, act2_global_scale=1.0, topk_ids=None, topk_weights=None,
+                      router_logits=None, num_tokens=None):
+    """``qs3_moe_layer_execute``: the whole layer of upstream ``execute_moe_mlp``
+    (src/model.rs:2072-2228) in one call. ``gate_up`` / ``down`` are bf16 tensors for
+    a bf16 plan and :class:`Nvfp4Weight` for an NVFP4 plan."""
+    ctx = plan.ctx
+    d = capi.MoeLayerDesc()
+    d.hidden = _desc(hidden, 2)
+    d.router_weight = _desc(router_weight, 2)
+    d.router_bias = _desc(router_bias, 1)
+
+    def put(prefix, w):
+        if isinstance(w, Nvfp4Weight):
+            setattr(d, f"{prefix}_weight", _desc(w.packed, 3))
+            setattr(d, f"{prefix}_scale_tiled", _desc(w.scale_tiled, 1))
+            setattr(d, f"{prefix}_global_scale", _desc(w.global_scale, 1))
+        else:
+            setattr(d, f"{prefix}_weight", _desc(w, 3))
+
+    put("gate_up", gate_up)
+    put("down", down)
+    if shared is not None:
+        put("shared_gate_up", shared.gate_up)
+        put("shared_down", shared.down)
+        d.shared_gate_weight = _desc(shared.gate_weight, 2)
+        d.shared_intermediate_size = shared.intermediate_size
+    d.score = score
+    d.renormalize = 1 if renormalize else 0
+    d.routed_scaling_factor = routed_scaling_factor
+    d.act_global_scale = act_global_scale
+    d.act2_global_scale = act2_global_scale
+    d.out = _desc(out, 2)
+    d.topk_ids = _desc(topk_ids, 2)
+    d.topk_weights = _desc(topk_weights, 2)
+    d.router_logits = _desc(router_logits, 2)
+    d.workspace = _desc(workspace, 1)
+    d.num_tokens = hidden.shape[0] if num_tokens is None else num_tokens
+    ctx.check(ctx._lib.qs3_moe_layer_execute(ctx.handle, plan.handle, C.byref(d)))

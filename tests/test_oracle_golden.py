@@ -1,0 +1,154 @@
+"""Pins the CPU oracle against the known-answer cases of the upstream CUDA tests
+(tests/golden/reference_cases.json) before anything else trusts it."""
+import math
+
+import numpy as np
+
+from helpers import bf16, f32, moe_case_arrays, parse_floats
+
+
+def _router_case(oracle, case, logits_bf16=False):
+    logits = parse_floats(case["logits"]).reshape(case["num_tokens"], case["num_experts"])
+    if logits_bf16:
+        logits = f32(bf16(logits))
+    return logits, oracle.router_topk(logits, case["top_k"], case["score"], bool(case["renormalize"]),
+                                      case["scale"])
+
+
+def test_router_softmax_ties(oracle, golden):
+    case = golden["router_softmax_ties"]
+    logits, (ids, w) = _router_case(oracle, case)
+    assert ids.tolist() == case["expected_ids"]
+    # closed form: softmax over the row, renormalised over the selected three, times scale
+    for t in range(2):
+        p = np.exp(logits[t].astype(np.float64) - logits[t].max())
+        p /= p.sum()
+        sel = p[ids[t]]
+        want = sel / sel.sum() * case["scale"]
+        assert np.allclose(w[t], want, atol=case["weight_tolerance"])
+
+
+def test_router_sigmoid_bf16(oracle, golden):
+    case = golden["router_sigmoid_bf16"]
+    logits, (ids, w) = _router_case(oracle, case, logits_bf16=True)
+    assert ids.tolist() == case["expected_ids"]
+    want = case["scale"] / (1.0 + math.exp(-1.0))
+    assert np.allclose(w[0], [want, want], atol=case["weight_tolerance"])
+
+
+def test_router_nonfinite(oracle, golden):
+    case = golden["router_nonfinite"]
+    _, (ids, w) = _router_case(oracle, case)
+    assert ids.tolist() == case["expected_ids"]
+    assert np.all(np.isfinite(w))
+    assert np.allclose(w, case["expected_weights"], atol=case["weight_tolerance"])
+
+
+def test_router_unfilled_slots(oracle):
+    # only NaN / -inf logits: nothing qualifies, slots keep id = slot index and weight 0
+    # (upstream qscu.cu:945-949)
+    logits = np.array([[np.nan, -np.inf, np.nan, 1.0]], np.float32)
+    ids, w = oracle.router_topk(logits, 3, 0, True, 1.0)
+    assert ids.tolist() == [[3, 1, 2]]
+    assert w[0, 1] == 0.0 and w[0, 2] == 0.0
+
+
+def test_moe_known_answers(oracle, golden):
+    for name in ("moe_staged_grouped_gemm", "moe_top2_weighted_accumulation"):
+        case = golden[name]
+        hidden, ids, w, gate_up, down, expected = moe_case_arrays(case)
+        out = f32(oracle.moe_bf16(hidden, ids, w, gate_up, down))
+        assert np.max(np.abs(out - expected)) <= case["tolerance"], name
+        # everything the case does not name stays exactly zero
+        assert np.all(out[expected == 0.0] == 0.0), name
+
+
+def test_silu_and_mul(oracle, golden):
+    case = golden["silu_and_mul"]
+    gate, up = bf16(case["gate"]), bf16(case["up"])
+    out = f32(oracle.silu_and_mul_bf16(gate, up))
+    g, u = f32(gate).astype(np.float64), f32(up).astype(np.float64)
+    want = g / (1.0 + np.exp(-g)) * u
+    assert np.max(np.abs(out - want)) <= case["tolerance"]
+
+
+def test_shared_expert_gate_add(oracle, golden):
+    case = golden["shared_expert_gate_add"]
+    rows, hidden = case["rows"], case["hidden"]
+    shared = bf16(case["shared"]).reshape(rows, hidden)
+    out0 = bf16(case["out"]).reshape(rows, hidden)
+    for gate in (np.array(case["gate"], np.float32), f32(bf16(case["gate"]))):
+        out = f32(oracle.shared_gate_add_bf16(gate, shared, out0))
+        sig = 1.0 / (1.0 + np.exp(-gate.astype(np.float64)))
+        want = f32(out0) + sig[:, None] * f32(shared)
+        assert np.max(np.abs(out - want)) <= case["tolerance"]
+
+
+def test_route_sort_is_stable_and_consistent(oracle):
+    rng = np.random.default_rng(3)
+    t, k, e = 37, 4, 11
+    ids = rng.integers(0, e, size=(t, k), dtype=np.int32)
+    ids[0] = [2, 2, 2, 5]  # duplicate routes of one token accumulate (test.cu:1586)
+    w = rng.random((t, k), dtype=np.float32)
+    counts, indptr, route_rows, row_tokens, row_scales = oracle.route_sort(ids, w, 0, e)
+    assert counts.sum() == t * k and indptr[-1] == t * k
+    assert np.array_equal(counts, np.bincount(ids.ravel(), minlength=e))
+    order = np.argsort(ids.ravel(), kind="stable")
+    assert np.array_equal(route_rows[order], np.arange(t * k))
+    assert np.array_equal(row_tokens, order // k)
+    assert np.array_equal(row_scales, w.ravel()[order])
+    # expert-parallel view: only experts [4, 8) are local
+    counts2, indptr2, rows2, tok2, _ = oracle.route_sort(ids, w, 4, 4)
+    local = (ids.ravel() >= 4) & (ids.ravel() < 8)
+    assert counts2.sum() == local.sum() and np.all(rows2[~local] == -1)
+    assert np.array_equal(np.sort(rows2[local]), np.arange(local.sum()))
+
+
+def test_bf16_round_to_nearest_even(oracle):
+    # upstream src/model.rs:3000-3004: bits + 0x7FFF + lsb
+    cases = {1.0: 0x3F80, 1.00390625: 0x3F80, 1.01171875: 0x3F82, -2.5: 0xC020, 0.0: 0x0000}
+    for v, want in cases.items():
+        assert int(bf16([v])[0]) == want
+        assert oracle.lib().qs3o_f32_to_bf16(v) == want
+
+
+def test_fp4_fp8_codecs(oracle):
+    lib = oracle.lib()
+    # e2m1 grid and tie-to-even midpoints
+    grid = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+    for c, v in enumerate(grid):
+        assert lib.qs3o_e2m1_to_f32(c) == v and lib.qs3o_f32_to_e2m1(v) == c
+        assert lib.qs3o_f32_to_e2m1(-v) == (c | 8 if v != 0.0 else 8)
+    for mid, code in ((0.25, 0), (0.75, 2), (1.25, 2), (1.75, 4), (2.5, 4), (3.5, 6), (5.0, 6), (100.0, 7)):
+        assert lib.qs3o_f32_to_e2m1(mid) == code
+    # e4m3: exact round trip of every finite non-negative code, saturation, subnormals
+    for c in range(0x7F):
+        v = lib.qs3o_e4m3_to_f32(c)
+        assert lib.qs3o_f32_to_e4m3(v) == c
+    assert lib.qs3o_e4m3_to_f32(0x7E) == 448.0 and lib.qs3o_f32_to_e4m3(1e9) == 0x7E
+    assert lib.qs3o_e4m3_to_f32(0x01) == 2.0 ** -9 and lib.qs3o_f32_to_e4m3(2.0 ** -10) == 0
+    assert lib.qs3o_f32_to_e4m3(1.5 * 2.0 ** -9) == 2  # tie -> even
+
+
+def test_nvfp4_quantise_round_trip(oracle):
+    rng = np.random.default_rng(5)
+    x = bf16(rng.standard_normal((8, 64), dtype=np.float32))
+    packed, scale = oracle.nvfp4_quantize_act(x, 1.0)
+    deq = oracle.nvfp4_dequantize(packed, scale)
+    # block-wise error bound: half an e2m1 step (<= 1 at the top of the grid) times the scale
+    s = np.repeat(oracle.e4m3_to_f32(scale), 16, axis=-1)
+    assert np.all(np.abs(deq - f32(x)) <= s * 1.0 + 1e-6)
+    # exactly representable data survives: codes * power-of-two scale
+    y = np.tile(np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -6, -4, -3, -2, -1.5, -1, -.5, 0], np.float32), (1, 4))
+    p2, s2 = oracle.nvfp4_quantize_act(bf16(y), 1.0)
+    assert np.array_equal(oracle.nvfp4_dequantize(p2, s2), y)
+
+
+def test_tiled_scale_layout_is_a_bijection(oracle):
+    for rows, k, gated in ((256, 256, 0), (128, 512, 0), (1024, 2048, 512)):
+        idx = oracle.tiled_scale_index(rows, k, gated)
+        assert idx.min() == 0 and idx.max() == oracle.tiled_scale_bytes(rows, k) - 1
+        assert np.unique(idx).size == idx.size
+        for r, kb in ((0, 0), (33, 5), (rows - 1, k // 16 - 1)):
+            tr = oracle.lib().qs3o_gated_tiled_row(r, gated) if gated else r
+            assert idx[r, kb] == oracle.lib().qs3o_tiled_scale_offset(tr, kb, k)
