@@ -1,0 +1,384 @@
+#!/usr/bin/env python3
+"""MoE-layer throughput benchmark.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the whole MoE layer (router logits -> top-k -> permute ->
+grouped gate_up GEMM + SwiGLU -> grouped down GEMM -> shared expert -> combine) over
+one batch of synthetic tokens. At N = 1 the workload is the NVFP4 prefill layer
+(8192 tokens, hidden 2048, 512 experts, top-10 + shared expert, Zipf-skewed router);
+at N > 1 it is the expert-parallel variant with 4096 tokens per rank (weak scaling),
+launched one process per GPU by torch.distributed.run.
+
+Prints ONE JSON line on rank 0. `value` is device-timed (CUDA events, max over
+ranks) with inputs resident in HBM; `e2e` goes through the same C-ABI call with the
+tokens starting in pinned host memory and the result read back to the host inside
+the timed region. `roofline` describes the dominant kernel (grouped gate_up GEMM),
+timed with CUDA events around that kernel; `cpu_baseline` times the CPU oracle on a
+bounded sample of the same workload on this machine's host cores.
+
+`--impl reference` times the CPU oracle alone (the reference has no CPU MoE path of
+its own and its GPU path has no NVFP4 kernels, so the restated algorithm is the only
+reference implementation of this workload that exists).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, s[2:]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU oracle leg ---
+
+def _host_copies(data, ops):
+    """numpy copies of what the CPU oracle needs (weights in the declared linear layout)."""
+    def triple(q):
+        return (q.packed.cpu().numpy(), q.scale_linear.cpu().numpy(), q.global_scale.cpu().numpy())
+
+    import torch
+    host = {
+        "hidden": data.hidden.cpu().view(torch.uint16).numpy(),
+        "router": data.router.cpu().view(torch.uint16).numpy(),
+        "bias": None if data.bias is None else data.bias.cpu().numpy(),
+        "gu": triple(data.gate_up), "d": triple(data.down), "shared": None,
+    }
+    if data.shared is not None:
+        host["shared"] = dict(gu=triple(data.shared.gate_up), d=triple(data.shared.down),
+                              gate_w=data.shared.gate_weight.cpu().view(torch.uint16).numpy())
+    return host
+
+
+def _oracle_layer(orc, host, cfg, tokens):
+    """Whole layer on the host cores for the listed tokens; returns bf16 bit patterns."""
+    import numpy as np
+    hid = host["hidden"][tokens]
+    logits = orc.gemm_bf16(hid, host["router"], "f32")
+    ids, w = orc.router_topk(logits, cfg.top_k, 0, True, 1.0, host["bias"])
+    hp, hs = orc.nvfp4_quantize_act(hid, 1.0)
+    return orc.moe_nvfp4(hp, hs, ids, w, host["gu"], host["d"], shared=host["shared"], hidden_bf16=hid), ids
+
+
+def time_oracle(host, cfg, target_seconds=12.0, max_tokens=4096):
+    """tokens/s of the CPU oracle on a bounded sample sized for ~target_seconds."""
+    import numpy as np
+    from oracle import binding as orc
+    orc.build()
+    probe = np.arange(min(8, cfg.tokens))
+    t0 = time.perf_counter()
+    _oracle_layer(orc, host, cfg, probe)
+    per_token = (time.perf_counter() - t0) / len(probe)
+    n = int(max(8, min(max_tokens, cfg.tokens, target_seconds / max(per_token, 1e-6))))
+    sample = np.arange(n)
+    t0 = time.perf_counter()
+    _oracle_layer(orc, host, cfg, sample)
+    dt = time.perf_counter() - t0
+    return n / dt, n, dt, orc.num_threads()
+
+
+# ----------------------------------------------------------------------- main legs ---
+
+def run_reference(args, rank, world):
+    """Reference arm: the CPU restatement on the host cores, rank 0 only."""
+    if rank != 0:
+        return
+    import torch
+    from qs3_b200 import ops, workload
+    cfg = workload.PREFILL_NVFP4 if args.gpus == 1 else workload.EP_NVFP4
+    ctx = ops.Context(0)
+    data = workload.LayerData(cfg, ctx, seed=0)
+    host = _host_copies(data, ops)
+    del data
+    torch.cuda.empty_cache()
+    vals = []
+    n = dt = cores = 0
+    per_step = max(2.0, min(20.0, 150.0 / max(1, args.steps + args.warmup)))
+    for step in range(args.warmup + args.steps):
+        v, n, dt, cores = time_oracle(host, cfg, target_seconds=per_step)
+        if step >= args.warmup:
+            vals.append(v)
+    value = statistics.mean(vals)
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1000.0 * dt, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4", "data": "synthetic",
+        "config": {"workload": cfg.name, "tokens": cfg.tokens, "hidden": cfg.hidden, "experts": cfg.experts,
+                   "top_k": cfg.top_k, "intermediate": cfg.inter, "shared_intermediate": cfg.shared_inter},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"first {n} tokens of the batch per step, whole layer on the CPU oracle"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from qs3_b200 import ops, workload
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ctx = ops.Context(local_rank)
+    ctx.validate_target()
+
+    if world == 1:
+        cfg = workload.PREFILL_NVFP4
+        data = workload.LayerData(cfg, ctx, seed=0)
+        layer = SingleGpuLayer(ctx, data)
+    else:
+        from qs3_b200 import ep
+        cfg = workload.EP_NVFP4
+        per = cfg.experts // world
+        data = workload.LayerData(cfg, ctx, seed=0, expert_range=(rank * per, per), token_seed=rank + 1)
+        layer = ep.ExpertParallelLayer(ctx, data, rank, world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- value: inputs resident in HBM ----
+    for _ in range(args.warmup):
+        layer.step()
+    barrier()
+    launches0 = ops.launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            layer.step()
+        stop.record()
+        barrier()
+    elapsed_ms = start.elapsed_time(stop)
+    launches = ops.launch_count() - launches0
+    if ctx.read_device_error() != 0:
+        raise RuntimeError("a tensor-core kernel reported a bounded-wait expiry")
+
+    # ---- e2e: tokens start in pinned host memory, result is read back ----
+    h_in = torch.empty((cfg.tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory()
+    h_in.copy_(data.hidden.cpu())
+    h_out = torch.empty((cfg.tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory()
+    for _ in range(min(3, max(1, args.warmup))):
+        layer.step_e2e(h_in, h_out)
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        layer.step_e2e(h_in, h_out)
+    e_stop.record()
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_stop)
+
+    # ---- per-stage profile (separate pass, CUDA events around every stage) ----
+    stage_ms = {}
+    if hasattr(layer, "profile"):
+        stage_ms = layer.profile(max(3, min(args.steps, 10)))
+
+    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = times.tolist()
+    total_tokens = cfg.tokens * world
+    value = total_tokens * args.steps / (elapsed_ms / 1000.0)
+    e2e_value = total_tokens * args.steps / (e2e_ms / 1000.0)
+
+    if rank != 0:
+        return
+    hbm_gbs, peak_kind = _peaks()
+    line = {
+        "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
+        "data": "synthetic",
+        "config": {"workload": cfg.name, "tokens_per_gpu": cfg.tokens, "hidden": cfg.hidden,
+                   "experts": cfg.experts, "top_k": cfg.top_k, "intermediate": cfg.inter,
+                   "shared_intermediate": cfg.shared_inter, "router_bias": f"zipf(s={cfg.zipf_s})",
+                   "parallelism": "single" if world == 1 else f"ep{world}",
+                   "l2_policy": "inputs_exceed_l2 (expert weights ~0.9 GB per pass)"},
+        "e2e": {"value": e2e_value, "unit": "tokens/s",
+                "h2d_bytes_per_step": h_in.numel() * 2 * world, "d2h_bytes_per_step": h_out.numel() * 2 * world},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+        "stage_ms": stage_ms,
+    }
+    line["roofline"] = layer.roofline(stage_ms, hbm_gbs, peak_kind)
+    if world == 1 and not args.no_cpu_baseline:
+        host = _host_copies(data, ops)
+        v, n, dt, cores = time_oracle(host, cfg)
+        line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                "sample": f"first {n} tokens of the batch, whole layer on the CPU oracle, {dt:.1f} s"}
+    print(json.dumps(line), flush=True)
+
+
+class SingleGpuLayer:
+    """One GPU, all experts local: a single qs3_moe_layer_execute per step."""
+
+    def __init__(self, ctx, data):
+        import torch
+        from qs3_b200 import ops
+        self.ops, self.ctx, self.data = ops, ctx, data
+        cfg = data.cfg
+        self.plan = data.plan(ctx)
+        dev = data.hidden.device
+        self.ws = torch.empty(self.plan.layer_workspace_size(cfg.tokens, cfg.shared_inter), dtype=torch.uint8,
+                              device=dev)
+        self.out = torch.empty((cfg.tokens, cfg.hidden), dtype=torch.bfloat16, device=dev)
+        self.x_dev = torch.empty_like(data.hidden)
+        self.ids = torch.empty((cfg.tokens, cfg.top_k), dtype=torch.int32, device=dev)
+
+    def step(self, hidden=None):
+        d = self.data
+        self.ops.moe_layer_execute(self.plan, d.hidden if hidden is None else hidden, d.router, d.gate_up,
+                                   d.down, self.out, self.ws, router_bias=d.bias, shared=d.shared,
+                                   topk_ids=self.ids)
+
+    def step_e2e(self, h_in, h_out):
+        self.x_dev.copy_(h_in, non_blocking=True)
+        self.step(self.x_dev)
+        h_out.copy_(self.out, non_blocking=True)
+
+    def profile(self, iters):
+        acc = {}
+        for _ in range(iters):
+            self.ops.profile_begin(self.ctx)
+            self.step()
+            for name, ms in self.ops.profile_end(self.ctx):
+                acc.setdefault(name, []).append(ms)
+        return {k: statistics.mean(v) for k, v in acc.items()}
+
+    def roofline(self, stage_ms, hbm_gbs, peak_kind):
+        """Dominant kernel: grouped gate_up GEMM + SwiGLU. Algorithmic bytes per launch =
+        gate_up weights (codes + scales) of every expert that received a row, plus the
+        quantised activation rows read and the quantised SwiGLU rows written."""
+        import torch
+        cfg = self.data.cfg
+        ms = stage_ms.get("gate_up_gemm_swiglu")
+        if not ms:
+            return None
+        counts = torch.bincount(self.ids.flatten().long(), minlength=cfg.experts)
+        hit = int((counts > 0).sum().item())
+        routes = cfg.tokens * cfg.top_k
+        gu_bytes, _ = self.data.weight_bytes_per_expert()
+        act_in = routes * (cfg.hidden // 2 + cfg.hidden // 16)
+        act_out = routes * (cfg.inter // 2 + cfg.inter // 16)
+        algo = hit * gu_bytes + act_in + act_out
+        achieved = algo / (ms * 1e-3) / 1e9
+        flops = 2.0 * routes * 2 * cfg.inter * cfg.hidden
+        return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
+                "frac": achieved / hbm_gbs, "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
+                "kernel": "gemm_tc_kernel<nvfp4, gated, swiglu_nvfp4>", "kernel_ms": ms,
+                "algorithmic_bytes": algo, "experts_hit": hit,
+                "max_rows_per_expert": int(counts.max().item()),
+                "tensor_tflops": flops / (ms * 1e-3) / 1e12, "tensor_frac_of_nominal_fp4": flops / (ms * 1e-3) / 9e15}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    elif args.gpus != 1:
+        raise SystemExit("launch N > 1 with torch.distributed.run (one process per GPU)")
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -417,6 +417,18 @@ qsfi_status qs3_moe_routing_tables(
  * (and clears) the word; synchronises the context's stream. 0 = no error. */
 qsfi_status qs3_moe_read_device_error(qsfi_context* ctx, uint32_t* code);
 
+/* Measurement aids. qs3_moe_launch_count: kernels this library has launched in this
+ * process so far. qs3_moe_profile_begin / _end: between the two calls every
+ * qs3_moe_layer_execute records a CUDA event on the context's stream at each stage
+ * boundary; _end synchronises the stream and returns, per recorded stage, its id
+ * (1 router-logits GEMM, 2 router top-k, 3 route sort, 4 gather/quantise, 5 gate_up
+ * GEMM + SwiGLU, 6 down GEMM, 7 shared expert, 8 combine) and its duration in ms. */
+uint64_t qs3_moe_launch_count(void);
+qsfi_status qs3_moe_profile_begin(qsfi_context* ctx);
+qsfi_status qs3_moe_profile_end(
+    qsfi_context* ctx, int32_t* stage_ids, float* stage_ms, uint32_t capacity, uint32_t* count
+);
+
 #ifdef __cplusplus
 }
 #endif

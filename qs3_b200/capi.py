@@ -199,6 +199,10 @@ _SIGNATURES = {
     "qs3_moe_routing_tables": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
                                          _P(RoutingView)]),
     "qs3_moe_read_device_error": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
+    "qs3_moe_launch_count": (C.c_uint64, []),
+    "qs3_moe_profile_begin": (C.c_int, [C.c_void_p]),
+    "qs3_moe_profile_end": (C.c_int, [C.c_void_p, _P(C.c_int32), _P(C.c_float), C.c_uint32,
+                                      _P(C.c_uint32)]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

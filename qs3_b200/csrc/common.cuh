@@ -47,6 +47,15 @@ qsfi_status status_from_cuda(cudaError_t err);
 // Device-side error word shared by the tensor-core kernels (one per device).
 uint32_t* device_error_word();
 
+// Kernel-launch counter (all kernels of this library) and the optional per-stage
+// event recorder behind qs3_moe_profile_begin / qs3_moe_profile_end.
+void note_launch(uint32_t n = 1);
+enum Stage {
+    STAGE_END = 0, STAGE_ROUTER_GEMM = 1, STAGE_ROUTER_TOPK = 2, STAGE_ROUTE_SORT = 3,
+    STAGE_GATHER = 4, STAGE_GATE_UP_GEMM = 5, STAGE_DOWN_GEMM = 6, STAGE_SHARED = 7, STAGE_COMBINE = 8
+};
+void stage_mark(cudaStream_t stream, int stage);
+
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 template <typename T> bool contiguous1(const T& t) { return t.stride[0] == 1; }

@@ -3,6 +3,7 @@
 // MoE path uses; the build target answered here is sm_100 (compute 10.0).
 #include "common.cuh"
 
+#include <atomic>
 #include <mutex>
 #include <new>
 
@@ -103,6 +104,26 @@ uint32_t* device_error_word()
         words[dev] = static_cast<uint32_t*>(p);
     }
     return words[dev];
+}
+
+static std::atomic<uint64_t> g_launches { 0 };
+void note_launch(uint32_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+struct StageRecorder {
+    bool on = false;
+    bool created = false;
+    int count = 0;
+    cudaEvent_t ev[64];
+    int ids[64];
+};
+static StageRecorder g_rec;
+
+void stage_mark(cudaStream_t stream, int stage)
+{
+    if (!g_rec.on || g_rec.count >= 64)
+        return;
+    cudaEventRecord(g_rec.ev[g_rec.count], stream);
+    g_rec.ids[g_rec.count++] = stage;
 }
 
 } // namespace qs3
@@ -245,6 +266,57 @@ qsfi_status qs3_moe_read_device_error(qsfi_context* ctx, uint32_t* code)
     if (err == cudaSuccess && *code != 0)
         err = cudaMemset(word, 0, sizeof(uint32_t));
     return set_cuda_error(ctx, err, "qs3_moe_read_device_error");
+}
+
+uint64_t qs3_moe_launch_count(void)
+{
+    return g_launches.load(std::memory_order_relaxed);
+}
+
+qsfi_status qs3_moe_profile_begin(qsfi_context* ctx)
+{
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (!g_rec.created) {
+        for (int i = 0; i < 64; ++i) {
+            cudaError_t err = cudaEventCreate(&g_rec.ev[i]);
+            if (err != cudaSuccess)
+                return set_cuda_error(ctx, err, "cudaEventCreate");
+        }
+        g_rec.created = true;
+    }
+    g_rec.count = 0;
+    g_rec.on = true;
+    return QSFI_STATUS_OK;
+}
+
+qsfi_status qs3_moe_profile_end(qsfi_context* ctx, int32_t* stage_ids, float* stage_ms, uint32_t capacity,
+                                uint32_t* count)
+{
+    if (ctx == nullptr || stage_ids == nullptr || stage_ms == nullptr || count == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    g_rec.on = false;
+    *count = 0;
+    cudaError_t err = cudaStreamSynchronize(ctx->stream);
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "cudaStreamSynchronize");
+    for (int i = 0; i + 1 < g_rec.count && *count < capacity; ++i) {
+        if (g_rec.ids[i] == STAGE_END)
+            continue;
+        float ms = 0.0f;
+        err = cudaEventElapsedTime(&ms, g_rec.ev[i], g_rec.ev[i + 1]);
+        if (err != cudaSuccess)
+            return set_cuda_error(ctx, err, "cudaEventElapsedTime");
+        stage_ids[*count] = g_rec.ids[i];
+        stage_ms[*count] = ms;
+        *count += 1;
+    }
+    return QSFI_STATUS_OK;
 }
 
 } // extern "C"

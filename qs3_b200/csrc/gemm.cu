@@ -610,6 +610,7 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
             configured[dev] = true;
     }
     kernel<<<grid, kThreads, smem, stream>>>(ma, mb, tp);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -727,6 +728,7 @@ cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** 
             *why = "epilogue not available on the CUDA-core kernel";
         return cudaErrorNotSupported;
     }
+    note_launch();
     return cudaGetLastError();
 }
 

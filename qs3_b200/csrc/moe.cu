@@ -283,6 +283,7 @@ qsfi_status run_routed_bf16(qsfi_context* ctx, const qsfi_moe_plan_desc& p, cons
                                          w.expanded, ctx->stream);
     if (err != cudaSuccess)
         return set_cuda_error(ctx, err, "MoE gather");
+    stage_mark(ctx->stream, STAGE_GATE_UP_GEMM);
     GemmProblem g1 = grouped_problem(w.rt, p.local_num_experts);
     g1.a = w.expanded;
     g1.a_pitch_bytes = static_cast<uint64_t>(p.hidden_size) * 2;
@@ -297,6 +298,7 @@ qsfi_status run_routed_bf16(qsfi_context* ctx, const qsfi_moe_plan_desc& p, cons
     qsfi_status status = gemm_or_error(ctx, g1, "MoE gate_up GEMM");
     if (status != QSFI_STATUS_OK)
         return status;
+    stage_mark(ctx->stream, STAGE_DOWN_GEMM);
     GemmProblem g2 = grouped_problem(w.rt, p.local_num_experts);
     g2.a = w.act;
     g2.a_pitch_bytes = static_cast<uint64_t>(p.intermediate_size) * 2;
@@ -325,6 +327,7 @@ qsfi_status run_routed_nvfp4(qsfi_context* ctx, const qsfi_moe_plan_desc& p, con
 {
     const float ga = act_global == 0.0f ? 1.0f : act_global;
     const float ga2 = act2_global == 0.0f ? 1.0f : act2_global;
+    stage_mark(ctx->stream, STAGE_GATE_UP_GEMM);
     GemmProblem g1 = grouped_problem(w.rt, p.local_num_experts);
     g1.nvfp4 = 1;
     g1.a = w.xq;
@@ -346,6 +349,7 @@ qsfi_status run_routed_nvfp4(qsfi_context* ctx, const qsfi_moe_plan_desc& p, con
     qsfi_status status = gemm_or_error(ctx, g1, "NVFP4 MoE gate_up GEMM");
     if (status != QSFI_STATUS_OK)
         return status;
+    stage_mark(ctx->stream, STAGE_DOWN_GEMM);
     GemmProblem g2 = grouped_problem(w.rt, p.local_num_experts);
     g2.nvfp4 = 1;
     g2.a = w.act;
@@ -849,6 +853,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
     LayerExtra x = carve_layer(base, routed_bytes, p, d->num_tokens, shared ? is : 0, nvfp4);
     const __nv_bfloat16* hidden = static_cast<const __nv_bfloat16*>(d->hidden.data);
 
+    stage_mark(st, STAGE_ROUTER_GEMM);
     // 1. router logits: f32 [T, E] = hidden . router_weight^T  (src/model.rs:2082-2090)
     float* logits = d->router_logits.data != nullptr ? static_cast<float*>(d->router_logits.data) : x.logits;
     GemmProblem gl {};
@@ -867,6 +872,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
     if (status != QSFI_STATUS_OK)
         return status;
 
+    stage_mark(st, STAGE_ROUTER_TOPK);
     // 2. top-k routing (src/model.rs:2092-2115)
     int32_t* ids = d->topk_ids.data != nullptr ? static_cast<int32_t*>(d->topk_ids.data) : x.topk_ids;
     float* wts = d->topk_weights.data != nullptr ? static_cast<float*>(d->topk_weights.data) : x.topk_weights;
@@ -875,6 +881,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
                                          d->score == QSCU_ROUTER_SCORE_SIGMOID, d->renormalize != 0,
                                          d->routed_scaling_factor, st);
     // 3. permutation
+    stage_mark(st, STAGE_ROUTE_SORT);
     if (err == cudaSuccess)
         err = launch_route_sort(ids, wts, routes, p.top_k, p.local_expert_offset, p.local_num_experts, rt, st);
     if (err != cudaSuccess)
@@ -883,6 +890,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
     const __nv_bfloat16* y2 = nullptr;
     if (nvfp4) {
         // 4. gather + quantise, 5./6. grouped GEMMs
+        stage_mark(st, STAGE_GATHER);
         err = launch_nvfp4_gather_quantize(hidden, rt.route_prows, routes, p.top_k, p.hidden_size,
                                            d->act_global_scale, wn.xq, wn.xq_sf, st);
         if (err != cudaSuccess)
@@ -900,6 +908,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         y2 = wn.y2;
         if (shared) {
             // 7. shared expert as a dense problem over the tokens in natural order
+            stage_mark(st, STAGE_SHARED);
             err = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
                                                d->act_global_scale, x.sh_xq, x.sh_xq_sf, st);
             if (err != cudaSuccess)
@@ -951,6 +960,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
                 return status;
         }
     } else {
+        stage_mark(st, STAGE_GATHER);
         status = run_routed_bf16(ctx, p, wb, hidden, d->num_tokens,
                                  static_cast<const __nv_bfloat16*>(d->gate_up_weight.data),
                                  static_cast<const __nv_bfloat16*>(d->down_weight.data));
@@ -959,6 +969,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         y2 = wb.y2;
         if (shared) {
             // shared expert, src/model.rs:2174-2228, with SiLU*mul fused into the first GEMM
+            stage_mark(st, STAGE_SHARED);
             GemmProblem s1 {};
             s1.a = hidden;
             s1.a_rows = d->num_tokens;
@@ -994,6 +1005,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
     }
 
     // 8. weighted combine (+ sigmoid-gated shared expert)
+    stage_mark(st, STAGE_COMBINE);
     CombineParams cp {};
     cp.route_prows = rt.route_prows;
     cp.topk_weights = wts;
@@ -1008,7 +1020,9 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         cp.gate_w = static_cast<const __nv_bfloat16*>(d->shared_gate_weight.data);
         cp.round_before_shared = nvfp4 ? 0 : 1;
     }
-    return set_cuda_error(ctx, launch_combine(cp, st), "qs3_moe_layer_execute");
+    status = set_cuda_error(ctx, launch_combine(cp, st), "qs3_moe_layer_execute");
+    stage_mark(st, STAGE_END);
+    return status;
 }
 
 } // extern "C"

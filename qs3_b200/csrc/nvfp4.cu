@@ -194,6 +194,7 @@ cudaError_t launch_nvfp4_gather_quantize(const __nv_bfloat16* hidden, const int3
     gather_quantize_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
         hidden, route_prows, total, top_k, hidden_size, global_scale == 0.0f ? 1.0f : global_scale, packed,
         scale_tiled);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -205,6 +206,7 @@ cudaError_t launch_nvfp4_gather_packed(const uint8_t* hidden_packed, const uint8
     const uint64_t total = static_cast<uint64_t>(routes) * (hidden_size / 64);
     gather_packed_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
         hidden_packed, hidden_scale, route_prows, total, top_k, hidden_size, packed, scale_tiled);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -214,6 +216,7 @@ cudaError_t launch_tile_scales(const uint8_t* linear, uint32_t experts, uint32_t
     const uint64_t total = static_cast<uint64_t>(experts) * rows * (k / 64);
     tile_scales_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
         linear, rows, k, total, tiled, qs3_nvfp4_tiled_scale_bytes(rows, k), gated);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -283,6 +286,7 @@ qsfi_status qs3_nvfp4_quantize_weight(qsfi_context* ctx, const qs3_nvfp4_quantiz
         static_cast<uint32_t>(k), total, static_cast<const float*>(d->global_scale.data),
         static_cast<uint8_t*>(d->packed.data), static_cast<uint8_t*>(d->scale_linear.data),
         static_cast<uint8_t*>(d->scale_tiled.data), tiled_bytes, d->gated_rows != 0);
+    note_launch(3);
     return set_cuda_error(ctx, cudaGetLastError(), "qs3_nvfp4_quantize_weight");
 }
 
@@ -314,6 +318,7 @@ qsfi_status qs3_nvfp4_quantize_act(qsfi_context* ctx, const qs3_nvfp4_quantize_a
         static_cast<const __nv_bfloat16*>(d->x.data), static_cast<uint32_t>(k), total,
         d->global_scale == 0.0f ? 1.0f : d->global_scale, static_cast<uint8_t*>(d->packed.data),
         static_cast<uint8_t*>(d->scale_linear.data));
+    note_launch();
     return set_cuda_error(ctx, cudaGetLastError(), "qs3_nvfp4_quantize_act");
 }
 

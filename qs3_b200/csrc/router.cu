@@ -237,6 +237,7 @@ cudaError_t launch_router_topk(const void* logits, int logits_bf16, const float*
             static_cast<const float*>(logits), bias, ids, weights, num_tokens, num_experts, top_k,
             sigmoid_score, renormalize, scaling);
     }
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -319,6 +320,7 @@ qsfi_status qscu_silu_and_mul_bf16(const qscu_silu_and_mul_desc* d, qsfi_cuda_st
     silu_and_mul_kernel<<<static_cast<uint32_t>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(d->gate.data), static_cast<const __nv_bfloat16*>(d->up.data),
         static_cast<__nv_bfloat16*>(d->out.data), total, vec_ok);
+    note_launch();
     return status_from_cuda(cudaGetLastError());
 }
 
@@ -356,6 +358,7 @@ qsfi_status qscu_qwen36_shared_expert_gate_add_bf16(
             static_cast<const __nv_bfloat16*>(d->gate_logits.data),
             static_cast<const __nv_bfloat16*>(d->shared.data),
             static_cast<__nv_bfloat16*>(d->out.data), d->hidden_size, total);
+    note_launch();
     return status_from_cuda(cudaGetLastError());
 }
 

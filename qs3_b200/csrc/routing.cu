@@ -268,7 +268,10 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p)
     }
     const uint4* y2 = reinterpret_cast<const uint4*>(p.expert_out);
     uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
-    for (uint32_t i = lane; i < vec_per_row; i += 32) {
+    // the trip count is warp-uniform: the shuffles below need every lane
+    for (uint32_t i0 = 0; i0 < vec_per_row; i0 += 32) {
+        const uint32_t i = i0 + lane;
+        const bool active = i < vec_per_row;
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -276,7 +279,7 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p)
         for (uint32_t k = 0; k < p.top_k; ++k) {
             const int row = __shfl_sync(0xffffffffu, my_row, k);
             const float w = __shfl_sync(0xffffffffu, my_w, k);
-            if (row < 0)
+            if (row < 0 || !active)
                 continue;
             const uint4 v = y2[static_cast<size_t>(row) * vec_per_row + i];
             const uint32_t vs[4] = { v.x, v.y, v.z, v.w };
@@ -286,6 +289,8 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p)
                 acc[2 * j + 1] += w * bf16_bits_to_f32(vs[j] >> 16);
             }
         }
+        if (!active)
+            continue;
         if (p.shared_out != nullptr) {
             const uint4 s = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
             const uint32_t ss[4] = { s.x, s.y, s.z, s.w };
@@ -380,6 +385,7 @@ cudaError_t launch_route_sort(const int32_t* topk_ids, const float* topk_weights
         return err;
     route_place_kernel<<<rt.route_blocks, kSortWarps * 32, smem, stream>>>(
         topk_ids, topk_weights, routes, top_k, local_offset, experts, rt);
+    note_launch(3);
     return cudaGetLastError();
 }
 
@@ -390,12 +396,14 @@ cudaError_t launch_gather_bf16(const __nv_bfloat16* hidden, const int32_t* route
     gather_bf16_kernel<<<(routes + 7) / 8, 256, 0, stream>>>(
         reinterpret_cast<const uint4*>(hidden), route_prows, routes, top_k, hidden_size / 8,
         reinterpret_cast<uint4*>(expanded));
+    note_launch();
     return cudaGetLastError();
 }
 
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream)
 {
     combine_kernel<<<(p.num_tokens + 7) / 8, 256, 0, stream>>>(p);
+    note_launch();
     return cudaGetLastError();
 }
 

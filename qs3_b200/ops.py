@@ -427,3 +427,28 @@ def moe_layer_execute(plan: MoePlan, hidden, router_weight, gate_up, down, out, 
     d.workspace = _desc(workspace, 1)
     d.num_tokens = hidden.shape[0] if num_tokens is None else num_tokens
     ctx.check(ctx._lib.qs3_moe_layer_execute(ctx.handle, plan.handle, C.byref(d)))
+
+
+# ------------------------------------------------------------ measurement aids ---
+
+STAGE_NAMES = {1: "router_logits_gemm", 2: "router_topk", 3: "route_sort", 4: "gather_quantize",
+               5: "gate_up_gemm_swiglu", 6: "down_gemm", 7: "shared_expert", 8: "combine"}
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(capi.load().qs3_moe_launch_count())
+
+
+def profile_begin(ctx: Context):
+    ctx.check(ctx._lib.qs3_moe_profile_begin(ctx.handle))
+
+
+def profile_end(ctx: Context):
+    """[(stage name, ms), ...] for every stage recorded since ``profile_begin``."""
+    cap = 64
+    ids = (C.c_int32 * cap)()
+    ms = (C.c_float * cap)()
+    n = C.c_uint32(0)
+    ctx.check(ctx._lib.qs3_moe_profile_end(ctx.handle, ids, ms, cap, C.byref(n)))
+    return [(STAGE_NAMES.get(ids[i], str(ids[i])), float(ms[i])) for i in range(n.value)]

@@ -1,0 +1,117 @@
+"""Synthetic MoE-layer workloads with the shapes and value distributions of the
+benchmark configurations, generated on the device from a seed.
+
+The reference publishes no dataset for this path; the configurations name only
+shapes and distributions (activations ~ N(0, 1), weights ~ N(0, 0.02), a Zipf-like
+additive router bias), so seeded synthetic tensors stand in for real checkpoints.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import capi, ops
+
+
+@dataclass
+class LayerConfig:
+    name: str
+    tokens: int
+    hidden: int
+    experts: int
+    top_k: int
+    inter: int
+    shared_inter: int = 0
+    nvfp4: bool = True
+    zipf_s: float = 0.0
+
+
+# Qwen3-Next-shaped prefill layer: 8192 tokens, 512 experts, top-10 + shared expert, NVFP4
+PREFILL_NVFP4 = LayerConfig("qwen3next_moe_prefill_nvfp4", 8192, 2048, 512, 10, 512, 512, True, 1.1)
+# per-rank slice of the expert-parallel configuration (4096 tokens per rank)
+EP_NVFP4 = LayerConfig("qwen3next_moe_ep_nvfp4", 4096, 2048, 512, 10, 512, 512, True, 1.1)
+TINY_BF16 = LayerConfig("tiny_bf16", 16, 256, 8, 2, 128, 0, False, 0.0)
+
+
+def _normal_bf16(shape, std, gen, device, chunk_rows=64):
+    """N(0, std) in bf16, generated in slices of the leading dimension to bound f32 scratch."""
+    out = torch.empty(shape, dtype=torch.bfloat16, device=device)
+    lead = shape[0]
+    for s in range(0, lead, chunk_rows):
+        e = min(lead, s + chunk_rows)
+        out[s:e] = (torch.randn((e - s, *shape[1:]), generator=gen, device=device, dtype=torch.float32)
+                    * std).to(torch.bfloat16)
+    return out
+
+
+class LayerData:
+    """Weights (quantised once, like a weight loader would) and inputs of one layer.
+
+    ``expert_range`` = (first, count) keeps only that slice of the routed experts on
+    this device (expert parallelism); router and shared expert are always whole.
+    """
+
+    def __init__(self, cfg: LayerConfig, ctx: ops.Context, seed: int = 0, expert_range=None,
+                 token_seed: int | None = None, keep_bf16: bool = False):
+        dev = torch.device("cuda", ctx.device)
+        self.cfg = cfg
+        first, count = expert_range if expert_range is not None else (0, cfg.experts)
+        self.expert_range = (first, count)
+        gw = torch.Generator(device=dev)
+        gw.manual_seed(1000 * seed + 1)
+        h, i, s = cfg.hidden, cfg.inter, cfg.shared_inter
+        self.router = _normal_bf16((cfg.experts, h), 0.02, gw, dev)
+        self.bias = None
+        if cfg.zipf_s > 0:
+            perm = torch.randperm(cfg.experts, generator=gw, device=dev)
+            self.bias = (-cfg.zipf_s * torch.log1p(perm.to(torch.float32))).contiguous()
+        # routed experts: generate every expert so that all ranks agree, keep the local slice
+        gate_up = torch.empty((count, 2 * i, h), dtype=torch.bfloat16, device=dev)
+        down = torch.empty((count, h, i), dtype=torch.bfloat16, device=dev)
+        for e in range(cfg.experts):
+            ge = torch.Generator(device=dev)
+            ge.manual_seed(1000 * seed + 100 + e)
+            if first <= e < first + count:
+                gate_up[e - first] = (torch.randn((2 * i, h), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
+                down[e - first] = (torch.randn((h, i), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
+        self.shared = None
+        if s:
+            sgu = _normal_bf16((1, 2 * s, h), 0.02, gw, dev)
+            sdn = _normal_bf16((1, h, s), 0.02, gw, dev)
+            sgate = _normal_bf16((1, h), 0.02, gw, dev)
+        if cfg.nvfp4:
+            self.gate_up = ops.nvfp4_quantize_weight(ctx, gate_up, True)
+            self.down = ops.nvfp4_quantize_weight(ctx, down, False)
+            if s:
+                self.shared = ops.SharedExpert(ops.nvfp4_quantize_weight(ctx, sgu, True),
+                                               ops.nvfp4_quantize_weight(ctx, sdn, False), sgate, s)
+            torch.cuda.synchronize(dev)
+        else:
+            self.gate_up, self.down = gate_up, down
+            if s:
+                self.shared = ops.SharedExpert(sgu, sdn, sgate, s)
+        if keep_bf16:
+            self.gate_up_bf16, self.down_bf16 = gate_up, down
+            if s:
+                self.shared_bf16 = (sgu, sdn, sgate)
+        gt = torch.Generator(device=dev)
+        gt.manual_seed(1000 * seed + 7 + (token_seed or 0))
+        self.hidden = _normal_bf16((cfg.tokens, h), 1.0, gt, dev, chunk_rows=1024)
+
+    def plan(self, ctx: ops.Context, max_tokens: int | None = None) -> ops.MoePlan:
+        cfg = self.cfg
+        first, count = self.expert_range
+        return ops.MoePlan(ctx, ops.MoePlanConfig(
+            max_num_tokens=max_tokens or cfg.tokens, hidden_size=cfg.hidden, intermediate_size=cfg.inter,
+            num_experts=cfg.experts, top_k=cfg.top_k, local_expert_offset=first, local_num_experts=count,
+            backend=capi.MOE_BACKEND_NVFP4 if cfg.nvfp4 else capi.MOE_BACKEND_STAGED_BF16,
+            route_mode=capi.MOE_ROUTE_ROUTER_LOGITS))
+
+    def weight_bytes_per_expert(self):
+        """(gate_up bytes, down bytes) of one routed expert as the kernels read them."""
+        cfg = self.cfg
+        if cfg.nvfp4:
+            return (2 * cfg.inter * cfg.hidden // 2 + 2 * cfg.inter * cfg.hidden // 16,
+                    cfg.hidden * cfg.inter // 2 + cfg.hidden * cfg.inter // 16)
+        return 2 * cfg.inter * cfg.hidden * 2, cfg.hidden * cfg.inter * 2

@@ -82,3 +82,24 @@ def make_moe_inputs(seed, tokens, hidden, experts, inter, shared_inter=0, weight
         out["sh_down"] = bf16(rng.standard_normal((1, hidden, shared_inter), dtype=np.float32) * weight_std)
         out["sh_gate"] = bf16(rng.standard_normal((1, hidden), dtype=np.float32) * weight_std)
     return out
+
+
+# ------------------------------------------------------------ device helpers ---
+
+def to_dev(a, kind=None):
+    """numpy -> torch device tensor; uint16 arrays become bf16 unless kind == 'raw'."""
+    import torch
+    a = np.ascontiguousarray(a)
+    t = torch.from_numpy(a)
+    if a.dtype == np.uint16 and kind != "raw":
+        t = t.view(torch.bfloat16)
+    return t.cuda()
+
+
+def to_np(t):
+    """torch device tensor -> numpy; bf16 tensors come back as uint16 bit patterns."""
+    import torch
+    t = t.detach().cpu()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.uint16).numpy().copy()
+    return t.numpy().copy()
