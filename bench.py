@@ -199,6 +199,11 @@ def run_ours(args, rank, world, local_rank):
 
     if world == 1:
         cfg = workload.PREFILL_NVFP4
+        if args.tokens or args.experts:
+            # reduced case for profiler captures only (never a reported bench value)
+            import dataclasses
+            cfg = dataclasses.replace(cfg, name=cfg.name + "_reduced", tokens=args.tokens or cfg.tokens,
+                                      experts=args.experts or cfg.experts)
         data = workload.LayerData(cfg, ctx, seed=0)
         layer = SingleGpuLayer(ctx, data)
     else:
@@ -221,11 +226,13 @@ def run_ours(args, rank, world, local_rank):
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
+        torch.cuda.cudart().cudaProfilerStart()  # lets `ncu --profile-from-start off` see only this region
         start.record()
         for _ in range(args.steps):
             layer.step()
         stop.record()
         barrier()
+        torch.cuda.cudart().cudaProfilerStop()
     elapsed_ms = start.elapsed_time(stop)
     launches = ops.launch_count() - launches0
     if ctx.read_device_error() != 0:
@@ -235,20 +242,22 @@ def run_ours(args, rank, world, local_rank):
     h_in = torch.empty((cfg.tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory()
     h_in.copy_(data.hidden.cpu())
     h_out = torch.empty((cfg.tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory()
-    for _ in range(min(3, max(1, args.warmup))):
-        layer.step_e2e(h_in, h_out)
-    barrier()
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record()
-    for _ in range(args.steps):
-        layer.step_e2e(h_in, h_out)
-    e_stop.record()
-    barrier()
-    e2e_ms = e_start.elapsed_time(e_stop)
+    e2e_ms = float("nan")
+    if not args.kernels_only:
+        for _ in range(min(3, max(1, args.warmup))):
+            layer.step_e2e(h_in, h_out)
+        barrier()
+        e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e_start.record()
+        for _ in range(args.steps):
+            layer.step_e2e(h_in, h_out)
+        e_stop.record()
+        barrier()
+        e2e_ms = e_start.elapsed_time(e_stop)
 
     # ---- per-stage profile (separate pass, CUDA events around every stage) ----
     stage_ms = {}
-    if hasattr(layer, "profile"):
+    if hasattr(layer, "profile") and not args.kernels_only:
         stage_ms = layer.profile(max(3, min(args.steps, 10)))
 
     times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
@@ -279,7 +288,7 @@ def run_ours(args, rank, world, local_rank):
         "stage_ms": stage_ms,
     }
     line["roofline"] = layer.roofline(stage_ms, hbm_gbs, peak_kind)
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not args.kernels_only:
         host = _host_copies(data, ops)
         v, n, dt, cores = time_oracle(host, cfg)
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
@@ -356,6 +365,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="only the device-timed loop (for profiler captures; prints no valid bench line)")
+    ap.add_argument("--tokens", type=int, default=0, help="reduced token count, profiler captures only")
+    ap.add_argument("--experts", type=int, default=0, help="reduced expert count, profiler captures only")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
