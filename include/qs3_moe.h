@@ -412,6 +412,45 @@ qsfi_status qs3_moe_routing_tables(
     qs3_moe_routing_view* out
 );
 
+/* Route sort that allocates nothing. No counterpart in the reference: upstream only
+ * ever sorts routes inside qsfi_moe_execute_bf16 with scratch from the caller's
+ * workspace. This entry point is for callers that cannot allocate device memory when
+ * they need the routing tables (all HBM already committed to fixed pools at start-up,
+ * or a section where cudaMalloc's device-wide synchronisation is unacceptable): the
+ * kernels' scratch lives in a fixed QS3_ROUTE_SORT_STATIC_SCRATCH_BYTES array inside
+ * the library image, which every GPU that loads the library keeps until exit.
+ *
+ *  - Inputs and outputs are still the caller's: topk_ids / topk_weights in; counts,
+ *    indptr, route_rows (-1 for routes to non-local experts), row_tokens, row_scales
+ *    out, identical to what qs3_moe_routing_tables reports after an execute call.
+ *  - Limits: num_tokens * top_k <= QS3_ROUTE_SORT_STATIC_MAX_ROUTES and
+ *    local_num_experts <= QS3_ROUTE_SORT_STATIC_MAX_EXPERTS; anything larger returns
+ *    QSFI_STATUS_UNSUPPORTED with the limits in the context's last-error message.
+ *  - No cudaMalloc, cudaFree or allocating library routine is called. The first call on
+ *    each device resolves the array's device address (cudaGetSymbolAddress); make that
+ *    first call before starting any stream capture on that device.
+ *  - All calls on one device share the one array and it keeps the previous call's
+ *    contents. Nothing in it has to start at zero (every word is written before it is
+ *    read within a call), but two calls whose kernels overlap on the GPU (different
+ *    streams, or different host threads) race on it: serialise them. */
+#define QS3_ROUTE_SORT_STATIC_MAX_ROUTES 131072u
+#define QS3_ROUTE_SORT_STATIC_MAX_EXPERTS 1024u
+#define QS3_ROUTE_SORT_STATIC_SCRATCH_BYTES (2u << 20)
+typedef struct {
+    qsfi_tensor2 topk_ids;     /* in:  i32 [num_tokens, top_k], global expert ids */
+    qsfi_tensor2 topk_weights; /* in:  f32 [num_tokens, top_k] */
+    qsfi_tensor1 counts;       /* out: i32 [>= local_num_experts] */
+    qsfi_tensor1 indptr;       /* out: i32 [>= local_num_experts + 1] */
+    qsfi_tensor1 route_rows;   /* out: i32 [>= num_tokens * top_k] */
+    qsfi_tensor1 row_tokens;   /* out: i32 [>= num_tokens * top_k], first indptr[E] entries valid */
+    qsfi_tensor1 row_scales;   /* out: f32 [>= num_tokens * top_k], first indptr[E] entries valid */
+    uint32_t num_tokens;
+    uint32_t top_k;
+    uint32_t local_expert_offset;
+    uint32_t local_num_experts;
+} qs3_route_sort_static_desc;
+qsfi_status qs3_moe_route_sort_static(qsfi_context* ctx, const qs3_route_sort_static_desc* desc);
+
 /* Device-side error word of the tensor-core kernels: every wait inside them is
  * bounded; a wait that runs out records where and the kernel returns. Reads
  * (and clears) the word; synchronises the context's stream. 0 = no error. */

@@ -164,6 +164,17 @@ class RoutingView(C.Structure):
                 ("row_tokens", C.c_void_p), ("row_scales", C.c_void_p)]
 
 
+ROUTE_SORT_STATIC_MAX_ROUTES = 131072
+ROUTE_SORT_STATIC_MAX_EXPERTS = 1024
+
+
+class RouteSortStaticDesc(C.Structure):
+    _fields_ = [("topk_ids", Tensor2), ("topk_weights", Tensor2), ("counts", Tensor1),
+                ("indptr", Tensor1), ("route_rows", Tensor1), ("row_tokens", Tensor1),
+                ("row_scales", Tensor1), ("num_tokens", C.c_uint32), ("top_k", C.c_uint32),
+                ("local_expert_offset", C.c_uint32), ("local_num_experts", C.c_uint32)]
+
+
 # Every symbol include/qs3_moe.h declares: (restype, argtypes)
 _P = C.POINTER
 _SIGNATURES = {
@@ -198,6 +209,7 @@ _SIGNATURES = {
     "qs3_moe_layer_execute": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeLayerDesc)]),
     "qs3_moe_routing_tables": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
                                          _P(RoutingView)]),
+    "qs3_moe_route_sort_static": (C.c_int, [C.c_void_p, _P(RouteSortStaticDesc)]),
     "qs3_moe_read_device_error": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
     "qs3_moe_launch_count": (C.c_uint64, []),
     "qs3_moe_profile_begin": (C.c_int, [C.c_void_p]),

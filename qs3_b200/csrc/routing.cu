@@ -3,11 +3,13 @@
 // scatter_hidden / finalize (qsfi_moe.cu:327-409,465-492).
 #include "common.cuh"
 
+#include <mutex>
+
 namespace qs3 {
 
 namespace {
 
-constexpr int kSortWarps = 8;               // warps per block of the counting sort
+constexpr int kSortWarps = 8;              // warps per block of the counting sort
 constexpr int kSortRounds = 4;              // 32-route rounds per warp
 constexpr int kSortChunk = kSortWarps * kSortRounds * 32; // routes per block (1024)
 
@@ -408,3 +410,134 @@ cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream)
 }
 
 } // namespace qs3
+
+// ---- route sort without any allocation ------------------------------------------------
+//
+// qs3_moe_route_sort_static runs the same three counting-sort kernels as the MoE
+// execute calls, but takes its scratch (block histograms, padded segment starts, tile
+// table) from the fixed array below instead of a caller workspace. It is meant for
+// callers that cannot obtain device memory at the point where they need the routing
+// tables: a serving process that handed its whole HBM budget to weight and cache pools
+// at start-up and forbids later cudaMalloc, or code inside a latency-critical or
+// stream-ordered section where cudaMalloc's implicit device-wide synchronisation is
+// not acceptable. The price is a hard size limit and a buffer that every device
+// loading this library keeps until the process exits.
+namespace {
+
+constexpr size_t kStaticScratchBytes = QS3_ROUTE_SORT_STATIC_SCRATCH_BYTES;
+
+// Device-resident scratch. In HOST code this name is only a handle for the runtime's
+// symbol table, not a device address: kernels must be given the pointer that
+// cudaGetSymbolAddress returns (looked up once per device below).
+static __device__ __align__(256) unsigned char g_route_sort_scratch[kStaticScratchBytes];
+
+// Per-device address of g_route_sort_scratch, resolved with that device current.
+cudaError_t static_scratch_base(unsigned char** out)
+{
+    static std::mutex mu;
+    static unsigned char* base[64] = {};
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess)
+        return err;
+    if (dev < 0 || dev >= 64)
+        return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    if (base[dev] == nullptr) {
+        unsigned char* ptr = nullptr;
+        err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_route_sort_scratch);
+        if (err != cudaSuccess)
+            return err;
+        if (ptr == nullptr)
+            return cudaErrorInvalidSymbol;
+        base[dev] = ptr;
+    }
+    *out = base[dev];
+    return cudaSuccess;
+}
+
+template <typename T> T* static_take(unsigned char* base, size_t& offset, size_t count)
+{
+    offset = qs3::align_up(offset, qs3::kWorkspaceAlign);
+    T* p = reinterpret_cast<T*>(base + offset);
+    offset += count * sizeof(T);
+    return p;
+}
+
+bool bad_out(const qsfi_tensor1& t, qsfi_dtype dtype, uint64_t count)
+{
+    return t.data == nullptr || t.dtype != dtype || t.stride[0] != 1 || t.shape[0] < 0
+        || static_cast<uint64_t>(t.shape[0]) < count || (reinterpret_cast<uintptr_t>(t.data) & 3u) != 0;
+}
+
+} // namespace
+
+extern "C" qsfi_status qs3_moe_route_sort_static(qsfi_context* ctx, const qs3_route_sort_static_desc* d)
+{
+    using namespace qs3;
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (d == nullptr)
+        return set_invalid_arg(ctx, "desc is null");
+    if (d->num_tokens == 0 || d->top_k == 0 || d->local_num_experts == 0)
+        return set_invalid_arg(ctx, "route sort dimensions must be non-zero");
+    const uint64_t routes64 = static_cast<uint64_t>(d->num_tokens) * d->top_k;
+    if (routes64 > QS3_ROUTE_SORT_STATIC_MAX_ROUTES || d->local_num_experts > QS3_ROUTE_SORT_STATIC_MAX_EXPERTS)
+        return set_unsupported(
+            ctx,
+            "qs3_moe_route_sort_static handles at most %u routes and %u local experts (got %llu and %u); "
+            "use an execute call with a caller workspace for larger problems",
+            QS3_ROUTE_SORT_STATIC_MAX_ROUTES, QS3_ROUTE_SORT_STATIC_MAX_EXPERTS,
+            static_cast<unsigned long long>(routes64), d->local_num_experts);
+    const uint32_t routes = static_cast<uint32_t>(routes64);
+    const uint32_t experts = d->local_num_experts;
+    if (d->topk_ids.data == nullptr || d->topk_ids.dtype != QSFI_DTYPE_I32 || !contiguous2(d->topk_ids)
+        || d->topk_ids.shape[0] != d->num_tokens || d->topk_ids.shape[1] != d->top_k)
+        return set_invalid_arg(ctx, "topk_ids must be a contiguous i32 [num_tokens, top_k] tensor");
+    if (d->topk_weights.data == nullptr || d->topk_weights.dtype != QSFI_DTYPE_F32
+        || !contiguous2(d->topk_weights) || d->topk_weights.shape[0] != d->num_tokens
+        || d->topk_weights.shape[1] != d->top_k)
+        return set_invalid_arg(ctx, "topk_weights must be a contiguous f32 [num_tokens, top_k] tensor");
+    if (bad_out(d->counts, QSFI_DTYPE_I32, experts) || bad_out(d->indptr, QSFI_DTYPE_I32, experts + 1ull)
+        || bad_out(d->route_rows, QSFI_DTYPE_I32, routes) || bad_out(d->row_tokens, QSFI_DTYPE_I32, routes)
+        || bad_out(d->row_scales, QSFI_DTYPE_F32, routes))
+        return set_invalid_arg(ctx, "route sort outputs must be contiguous i32/f32 vectors of the documented length");
+
+    unsigned char* base = nullptr;
+    cudaError_t err = static_scratch_base(&base);
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "cudaGetSymbolAddress(route sort scratch)");
+
+    // caller-owned outputs + scratch-owned internals; every scratch word that a kernel
+    // reads is written earlier in the same call, so nothing needs clearing between calls
+    RouteTables rt {};
+    size_t off = 0;
+    const uint64_t seg = routes < experts ? routes : experts;
+    rt.max_pad_rows = static_cast<uint32_t>(align_up(routes, kTileM) + seg * kTileM);
+    rt.max_tiles = rt.max_pad_rows / kTileM;
+    rt.route_blocks = (routes + kSortChunk - 1) / kSortChunk;
+    rt.counts = static_cast<int32_t*>(d->counts.data);
+    rt.indptr = static_cast<int32_t*>(d->indptr.data);
+    rt.route_rows = static_cast<int32_t*>(d->route_rows.data);
+    rt.row_tokens = static_cast<int32_t*>(d->row_tokens.data);
+    rt.row_scales = static_cast<float*>(d->row_scales.data);
+    rt.pad_indptr = static_take<int32_t>(base, off, experts + 1ull);
+    rt.route_prows = static_take<int32_t>(base, off, routes);
+    rt.tile_expert = static_take<int32_t>(base, off, rt.max_tiles);
+    rt.tile_row0 = static_take<int32_t>(base, off, rt.max_tiles);
+    rt.tile_nrows = static_take<int32_t>(base, off, rt.max_tiles);
+    rt.total_tiles = static_take<int32_t>(base, off, 1);
+    rt.block_hist = static_take<int32_t>(base, off, static_cast<size_t>(rt.route_blocks) * experts);
+    if (off > kStaticScratchBytes)
+        return set_unsupported(ctx, "route sort scratch need of %llu bytes exceeds the static %llu bytes",
+                               static_cast<unsigned long long>(off),
+                               static_cast<unsigned long long>(kStaticScratchBytes));
+    err = launch_route_sort(static_cast<const int32_t*>(d->topk_ids.data),
+                            static_cast<const float*>(d->topk_weights.data), routes, d->top_k,
+                            d->local_expert_offset, experts, rt, ctx->stream);
+    return set_cuda_error(ctx, err, "qs3_moe_route_sort_static");
+}

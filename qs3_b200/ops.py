@@ -429,6 +429,38 @@ def moe_layer_execute(plan: MoePlan, hidden, router_weight, gate_up, down, out, 
     ctx.check(ctx._lib.qs3_moe_layer_execute(ctx.handle, plan.handle, C.byref(d)))
 
 
+def route_sort_static(ctx: Context, topk_ids, topk_weights, local_expert_offset: int,
+                      local_num_experts: int, out=None):
+    """``qs3_moe_route_sort_static``: the route permutation with library-resident scratch.
+
+    For callers that may not allocate device memory when they need the routing tables
+    (every byte of HBM already handed to fixed pools, or a section that cannot afford
+    ``cudaMalloc``'s device-wide synchronisation). The five output tensors are the
+    caller's and can be passed in as ``out=(counts, indptr, route_rows, row_tokens,
+    row_scales)`` so that this wrapper allocates nothing either; without ``out`` it
+    creates them with torch for convenience. At most 131072 routes and 1024 local
+    experts; calls on one device must not overlap on the GPU (they share the scratch).
+    Returns ``(counts, indptr, route_rows, row_tokens, row_scales)``; the last two are
+    valid up to ``indptr[-1]`` entries.
+    """
+    t, k = topk_ids.shape
+    dev = topk_ids.device
+    if out is None:
+        out = (torch.empty(local_num_experts, dtype=torch.int32, device=dev),
+               torch.empty(local_num_experts + 1, dtype=torch.int32, device=dev),
+               torch.empty(t * k, dtype=torch.int32, device=dev),
+               torch.empty(t * k, dtype=torch.int32, device=dev),
+               torch.empty(t * k, dtype=torch.float32, device=dev))
+    d = capi.RouteSortStaticDesc()
+    d.topk_ids = _desc(topk_ids, 2)
+    d.topk_weights = _desc(topk_weights, 2)
+    d.counts, d.indptr, d.route_rows, d.row_tokens, d.row_scales = (_desc(x, 1) for x in out)
+    d.num_tokens, d.top_k = t, k
+    d.local_expert_offset, d.local_num_experts = local_expert_offset, local_num_experts
+    ctx.check(ctx._lib.qs3_moe_route_sort_static(ctx.handle, C.byref(d)))
+    return out
+
+
 # ------------------------------------------------------------ measurement aids ---
 
 STAGE_NAMES = {1: "router_logits_gemm", 2: "router_topk", 3: "route_sort", 4: "gather_quantize",
