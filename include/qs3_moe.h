@@ -396,6 +396,80 @@ qsfi_status qs3_moe_layer_workspace_size(
 qsfi_status
 qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_layer_desc* desc);
 
+/* ---- expert parallelism (no upstream counterpart: upstream rejects partial expert ranges) ----
+ * One layer on n ranks, experts split in contiguous blocks, tokens data-parallel:
+ *   qs3_moe_ep_route            local tokens -> top-k ids/weights (+ NVFP4 codes of the tokens)
+ *   [caller: all-gather of codes, scales, ids, weights over NCCL]
+ *   qs3_moe_execute_nvfp4_prepared   local experts over ALL gathered tokens -> partial sums
+ *   [caller: all-to-all of the partial sums back to the token owners over NCCL]
+ *   qs3_moe_ep_finish           shared expert + sum of the n partials in rank order -> out
+ * The exchanges belong to the caller; the library never waits on another rank. */
+typedef struct {
+    qsfi_tensor2 hidden;         /* in:  bf16 [num_tokens, hidden] */
+    qsfi_tensor2 router_weight;  /* in:  bf16 [num_experts, hidden] */
+    qsfi_tensor1 router_bias;    /* in:  optional f32 [num_experts] */
+    qsfi_tensor2 router_logits;  /* out: f32 [num_tokens, num_experts] (scratch the caller owns) */
+    qsfi_tensor2 topk_ids;       /* out: i32 [num_tokens, top_k], global ids */
+    qsfi_tensor2 topk_weights;   /* out: f32 [num_tokens, top_k] */
+    qsfi_tensor2 hidden_packed;  /* out, optional: u8 [num_tokens, hidden/2] */
+    qsfi_tensor2 hidden_scale;   /* out, with hidden_packed: e4m3 [num_tokens, hidden/16], linear */
+    qscu_router_score score;
+    uint32_t renormalize;
+    float routed_scaling_factor;
+    float act_global_scale;      /* 0 means 1 */
+    uint32_t num_tokens;
+} qs3_moe_ep_route_desc;
+qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_ep_route_desc* desc);
+
+/* qsfi_moe_execute_nvfp4 with prepared weights: activations in the declared layout
+ * (linear scales), weights as qs3_nvfp4_quantize_weight leaves them (tiled scales +
+ * per-expert global scales). Workspace: qsfi_moe_workspace_size of the plan suffices. */
+typedef struct {
+    qsfi_tensor2 hidden_packed;        /* u8   [num_tokens, hidden/2] */
+    qsfi_tensor2 hidden_scale;         /* e4m3 [num_tokens, hidden/16] */
+    qsfi_tensor2 topk_ids;             /* i32  [num_tokens, top_k], global ids */
+    qsfi_tensor2 topk_weights;         /* f32  [num_tokens, top_k] */
+    qsfi_tensor3 gate_up_weight;       /* u8   [local_experts, 2*inter, hidden/2] */
+    qsfi_tensor1 gate_up_scale_tiled;
+    qsfi_tensor1 gate_up_global_scale; /* optional f32 [local_experts] */
+    qsfi_tensor3 down_weight;          /* u8   [local_experts, hidden, inter/2] */
+    qsfi_tensor1 down_scale_tiled;
+    qsfi_tensor1 down_global_scale;    /* optional f32 [local_experts] */
+    float act_global_scale;
+    float act2_global_scale;
+    qsfi_tensor2 out;                  /* bf16 [num_tokens, hidden]: sum over the LOCAL routes */
+    qsfi_tensor1 workspace;
+    uint32_t num_tokens;
+} qs3_moe_nvfp4_prepared_desc;
+qsfi_status qs3_moe_execute_nvfp4_prepared(
+    qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_nvfp4_prepared_desc* desc
+);
+
+typedef struct {
+    qsfi_tensor2 hidden;                      /* bf16 [num_tokens, hidden], this rank's tokens */
+    qsfi_tensor3 partials;                    /* bf16 [num_ranks, num_tokens, hidden] (phase 2) */
+    qsfi_tensor3 shared_gate_up_weight;       /* optional shared expert, NVFP4 as in qs3_moe_layer_desc */
+    qsfi_tensor1 shared_gate_up_scale_tiled;
+    qsfi_tensor1 shared_gate_up_global_scale;
+    qsfi_tensor3 shared_down_weight;
+    qsfi_tensor1 shared_down_scale_tiled;
+    qsfi_tensor1 shared_down_global_scale;
+    qsfi_tensor2 shared_gate_weight;
+    uint32_t shared_intermediate_size;
+    float act_global_scale;
+    float act2_global_scale;
+    qsfi_tensor2 out;                         /* bf16 [num_tokens, hidden] (phase 2) */
+    qsfi_tensor1 workspace;                   /* >= qs3_moe_ep_finish_workspace_size; keep it between phases */
+    uint32_t num_tokens;
+    uint32_t num_ranks;
+    uint32_t phases; /* bit 0: shared expert (can run while the exchange is in flight); bit 1: sum + store */
+} qs3_moe_ep_finish_desc;
+qsfi_status qs3_moe_ep_finish_workspace_size(
+    qsfi_context* ctx, const qsfi_moe_plan* plan, uint32_t num_tokens, uint32_t num_ranks,
+    uint32_t shared_intermediate_size, size_t* device_bytes
+);
+qsfi_status qs3_moe_ep_finish(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_ep_finish_desc* desc);
+
 /* Routing tables of the last execute on this workspace, for parity checks:
  * copies of counts[E_local], indptr[E_local+1], route_rows[T*K] (-1: not local),
  * row_tokens[R_local], row_scales[R_local] (upstream qsfi_moe.cu:26-31). Device

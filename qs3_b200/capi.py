@@ -159,6 +159,33 @@ class MoeLayerDesc(C.Structure):
                 ("workspace", Tensor1), ("num_tokens", C.c_uint32)]
 
 
+class MoeEpRouteDesc(C.Structure):
+    _fields_ = [("hidden", Tensor2), ("router_weight", Tensor2), ("router_bias", Tensor1),
+                ("router_logits", Tensor2), ("topk_ids", Tensor2), ("topk_weights", Tensor2),
+                ("hidden_packed", Tensor2), ("hidden_scale", Tensor2), ("score", C.c_int),
+                ("renormalize", C.c_uint32), ("routed_scaling_factor", C.c_float),
+                ("act_global_scale", C.c_float), ("num_tokens", C.c_uint32)]
+
+
+class MoeNvfp4PreparedDesc(C.Structure):
+    _fields_ = [("hidden_packed", Tensor2), ("hidden_scale", Tensor2), ("topk_ids", Tensor2),
+                ("topk_weights", Tensor2), ("gate_up_weight", Tensor3), ("gate_up_scale_tiled", Tensor1),
+                ("gate_up_global_scale", Tensor1), ("down_weight", Tensor3), ("down_scale_tiled", Tensor1),
+                ("down_global_scale", Tensor1), ("act_global_scale", C.c_float),
+                ("act2_global_scale", C.c_float), ("out", Tensor2), ("workspace", Tensor1),
+                ("num_tokens", C.c_uint32)]
+
+
+class MoeEpFinishDesc(C.Structure):
+    _fields_ = [("hidden", Tensor2), ("partials", Tensor3), ("shared_gate_up_weight", Tensor3),
+                ("shared_gate_up_scale_tiled", Tensor1), ("shared_gate_up_global_scale", Tensor1),
+                ("shared_down_weight", Tensor3), ("shared_down_scale_tiled", Tensor1),
+                ("shared_down_global_scale", Tensor1), ("shared_gate_weight", Tensor2),
+                ("shared_intermediate_size", C.c_uint32), ("act_global_scale", C.c_float),
+                ("act2_global_scale", C.c_float), ("out", Tensor2), ("workspace", Tensor1),
+                ("num_tokens", C.c_uint32), ("num_ranks", C.c_uint32), ("phases", C.c_uint32)]
+
+
 class RoutingView(C.Structure):
     _fields_ = [("counts", C.c_void_p), ("indptr", C.c_void_p), ("route_rows", C.c_void_p),
                 ("row_tokens", C.c_void_p), ("row_scales", C.c_void_p)]
@@ -210,6 +237,11 @@ _SIGNATURES = {
     "qs3_moe_routing_tables": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
                                          _P(RoutingView)]),
     "qs3_moe_route_sort_static": (C.c_int, [C.c_void_p, _P(RouteSortStaticDesc)]),
+    "qs3_moe_ep_route": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeEpRouteDesc)]),
+    "qs3_moe_execute_nvfp4_prepared": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeNvfp4PreparedDesc)]),
+    "qs3_moe_ep_finish_workspace_size": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                                   _P(C.c_size_t)]),
+    "qs3_moe_ep_finish": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeEpFinishDesc)]),
     "qs3_moe_read_device_error": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
     "qs3_moe_launch_count": (C.c_uint64, []),
     "qs3_moe_profile_begin": (C.c_int, [C.c_void_p]),

@@ -123,6 +123,8 @@ struct CombineParams {
     int round_before_shared;         // 1: round the routed sum to bf16 first (upstream chain)
 };
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
+cudaError_t launch_ep_rank_routes(int32_t* rows, float* weights, uint32_t tokens, uint32_t ranks,
+                                  cudaStream_t stream);
 
 // ---- GEMMs ----------------------------------------------------------------------
 enum GemmEpilogue {

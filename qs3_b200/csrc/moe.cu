@@ -1025,4 +1025,360 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
     return status;
 }
 
+// ---- expert-parallel phases ------------------------------------------------------------
+// One layer on n ranks = route (local tokens) -> token exchange -> local experts over the
+// gathered tokens -> partial-sum exchange -> finish (shared expert + ordered sum). The
+// exchanges are the caller's (NCCL); these three calls are the compute between them.
+
+qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_ep_route_desc* d)
+{
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (plan == nullptr || d == nullptr)
+        return set_invalid_arg(ctx, "plan/desc is null");
+    const qsfi_moe_plan_desc& p = plan->desc;
+    if (d->num_tokens == 0)
+        return set_invalid_arg(ctx, "invalid MoE num_tokens");
+    const int64_t t = d->num_tokens, h = p.hidden_size;
+    status = validate_tensor(ctx, d->hidden, "hidden", QSFI_DTYPE_BF16);
+    if (status == QSFI_STATUS_OK)
+        status = validate_tensor(ctx, d->router_weight, "router_weight", QSFI_DTYPE_BF16);
+    if (status == QSFI_STATUS_OK)
+        status = validate_tensor(ctx, d->router_logits, "router_logits", QSFI_DTYPE_F32);
+    if (status == QSFI_STATUS_OK)
+        status = validate_tensor(ctx, d->topk_ids, "topk_ids", QSFI_DTYPE_I32);
+    if (status == QSFI_STATUS_OK)
+        status = validate_tensor(ctx, d->topk_weights, "topk_weights", QSFI_DTYPE_F32);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (!contiguous2(d->hidden) || !contiguous2(d->router_weight) || !contiguous2(d->router_logits)
+        || !contiguous2(d->topk_ids) || !contiguous2(d->topk_weights))
+        return set_invalid_arg(ctx, "MoE route tensors must be contiguous");
+    if (d->hidden.shape[0] != t || d->hidden.shape[1] != h || d->router_weight.shape[0] != p.num_experts
+        || d->router_weight.shape[1] != h || d->router_logits.shape[0] != t
+        || d->router_logits.shape[1] != p.num_experts || d->topk_ids.shape[0] != t
+        || d->topk_ids.shape[1] != p.top_k || d->topk_weights.shape[0] != t
+        || d->topk_weights.shape[1] != p.top_k)
+        return set_invalid_arg(ctx, "MoE token/top-k tensor shape mismatch");
+    if (d->router_bias.data != nullptr
+        && (d->router_bias.dtype != QSFI_DTYPE_F32 || d->router_bias.shape[0] != p.num_experts
+            || !contiguous1(d->router_bias)))
+        return set_invalid_arg(ctx, "router_bias must be a contiguous f32 [num_experts] tensor");
+    if (p.top_k > 16 || p.num_experts > 4096 || p.top_k > p.num_experts)
+        return set_unsupported(ctx, "router supports top_k <= 16 and num_experts <= 4096");
+    if (!std::isfinite(d->routed_scaling_factor) || d->routed_scaling_factor <= 0.0f)
+        return set_invalid_arg(ctx, "routed_scaling_factor must be finite and positive");
+    const bool quantise = d->hidden_packed.data != nullptr;
+    if (quantise) {
+        if (h % 16 != 0 || d->hidden_packed.dtype != QSFI_DTYPE_U8 || !contiguous2(d->hidden_packed)
+            || d->hidden_packed.shape[0] != t || d->hidden_packed.shape[1] != h / 2
+            || d->hidden_scale.data == nullptr || d->hidden_scale.dtype != QSFI_DTYPE_FP8_E4M3
+            || !contiguous2(d->hidden_scale) || d->hidden_scale.shape[0] != t
+            || d->hidden_scale.shape[1] != h / 16)
+            return set_invalid_arg(ctx, "NVFP4 MoE hidden tensor shape mismatch");
+    }
+    if (!aligned16(d->hidden.data) || !aligned16(d->router_weight.data)
+        || (quantise && !aligned16(d->hidden_packed.data)))
+        return set_invalid_arg(ctx, "MoE tensors must be 16-byte aligned");
+
+    GemmProblem gl {};
+    gl.a = d->hidden.data;
+    gl.a_rows = d->num_tokens;
+    gl.a_pitch_bytes = static_cast<uint64_t>(h) * 2;
+    gl.b = d->router_weight.data;
+    gl.b_pitch_bytes = static_cast<uint64_t>(h) * 2;
+    gl.groups = 1;
+    gl.n = p.num_experts;
+    gl.k = p.hidden_size;
+    gl.epilogue = EPI_STORE_F32;
+    gl.out = d->router_logits.data;
+    gl.out_pitch_elems = p.num_experts;
+    status = gemm_or_error(ctx, gl, "MoE router-logits GEMM");
+    if (status != QSFI_STATUS_OK)
+        return status;
+    cudaError_t err = launch_router_topk(d->router_logits.data, 0, static_cast<const float*>(d->router_bias.data),
+                                         static_cast<int32_t*>(d->topk_ids.data),
+                                         static_cast<float*>(d->topk_weights.data), d->num_tokens,
+                                         p.num_experts, p.top_k, d->score == QSCU_ROUTER_SCORE_SIGMOID,
+                                         d->renormalize != 0, d->routed_scaling_factor, ctx->stream);
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "MoE routing");
+    if (quantise) {
+        qs3_nvfp4_quantize_act_desc q {};
+        q.x = d->hidden;
+        q.packed = d->hidden_packed;
+        q.scale_linear = d->hidden_scale;
+        q.global_scale = d->act_global_scale;
+        q.rows = d->num_tokens;
+        return qs3_nvfp4_quantize_act(ctx, &q);
+    }
+    return QSFI_STATUS_OK;
+}
+
+qsfi_status qs3_moe_execute_nvfp4_prepared(qsfi_context* ctx, const qsfi_moe_plan* plan,
+                                           const qs3_moe_nvfp4_prepared_desc* d)
+{
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (plan == nullptr || d == nullptr)
+        return set_invalid_arg(ctx, "plan/desc is null");
+    const qsfi_moe_plan_desc& p = plan->desc;
+    if (p.backend != QSFI_MOE_BACKEND_FLASHINFER_NVFP4)
+        return set_invalid_arg(ctx, "qs3_moe_execute_nvfp4_prepared requires an NVFP4 MoE plan");
+    if (d->num_tokens == 0 || d->num_tokens > p.max_num_tokens)
+        return set_invalid_arg(ctx, "invalid MoE num_tokens");
+    const int64_t t = d->num_tokens, h = p.hidden_size, i = p.intermediate_size, e = p.local_num_experts;
+    status = validate_tensor(ctx, d->hidden_packed, "hidden_packed", QSFI_DTYPE_U8);
+    if (status == QSFI_STATUS_OK)
+        status = validate_tensor(ctx, d->hidden_scale, "hidden_scale", QSFI_DTYPE_FP8_E4M3);
+    if (status == QSFI_STATUS_OK)
+        status = validate_tensor(ctx, d->gate_up_weight, "gate_up_weight", QSFI_DTYPE_U8);
+    if (status == QSFI_STATUS_OK)
+        status = validate_tensor(ctx, d->down_weight, "down_weight", QSFI_DTYPE_U8);
+    if (status == QSFI_STATUS_OK)
+        status = validate_routing_tensors(ctx, p, d->num_tokens, d->topk_ids, d->topk_weights, d->out);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (!contiguous2(d->hidden_packed) || !contiguous2(d->hidden_scale) || !contiguous3(d->gate_up_weight)
+        || !contiguous3(d->down_weight))
+        return set_invalid_arg(ctx, "NVFP4 MoE tensors must be contiguous");
+    if (d->hidden_packed.shape[0] != t || d->hidden_packed.shape[1] != h / 2 || d->hidden_scale.shape[0] != t
+        || d->hidden_scale.shape[1] != h / 16)
+        return set_invalid_arg(ctx, "NVFP4 MoE hidden tensor shape mismatch");
+    if (d->gate_up_weight.shape[0] != e || d->gate_up_weight.shape[1] != 2 * i
+        || d->gate_up_weight.shape[2] != h / 2 || d->down_weight.shape[0] != e || d->down_weight.shape[1] != h
+        || d->down_weight.shape[2] != i / 2)
+        return set_invalid_arg(ctx, "NVFP4 MoE expert weight shape mismatch");
+    status = validate_nvfp4_dims(ctx, p.hidden_size, p.intermediate_size, "");
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (d->gate_up_scale_tiled.data == nullptr || d->down_scale_tiled.data == nullptr
+        || static_cast<uint64_t>(d->gate_up_scale_tiled.shape[0]) < e * qs3_nvfp4_tiled_scale_bytes(2 * i, h)
+        || static_cast<uint64_t>(d->down_scale_tiled.shape[0]) < e * qs3_nvfp4_tiled_scale_bytes(h, i))
+        return set_invalid_arg(ctx, "NVFP4 MoE needs tiled weight scales of the right size");
+    for (const qsfi_tensor1* g : { &d->gate_up_global_scale, &d->down_global_scale })
+        if (g->data != nullptr && (g->dtype != QSFI_DTYPE_F32 || g->shape[0] != e || !contiguous1(*g)))
+            return set_invalid_arg(ctx, "global scales must be contiguous f32 [local_num_experts] tensors");
+    const size_t need = carve_nvfp4(nullptr, p, d->num_tokens, false).bytes;
+    status = validate_workspace(ctx, d->workspace, need);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_limits(ctx, p, d->num_tokens);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (!aligned16(d->hidden_packed.data) || !aligned16(d->out.data) || !aligned16(d->gate_up_weight.data)
+        || !aligned16(d->down_weight.data) || (reinterpret_cast<uintptr_t>(d->hidden_scale.data) & 3u) != 0)
+        return set_invalid_arg(ctx, "NVFP4 MoE tensors must be 16-byte aligned (scales 4-byte aligned)");
+
+    Nvfp4Workspace w = carve_nvfp4(static_cast<char*>(d->workspace.data), p, d->num_tokens, false);
+    const uint32_t routes = d->num_tokens * p.top_k;
+    cudaStream_t st = ctx->stream;
+    cudaError_t err = launch_route_sort(static_cast<const int32_t*>(d->topk_ids.data),
+                                        static_cast<const float*>(d->topk_weights.data), routes, p.top_k,
+                                        p.local_expert_offset, p.local_num_experts, w.rt, st);
+    if (err == cudaSuccess)
+        err = launch_nvfp4_gather_packed(static_cast<const uint8_t*>(d->hidden_packed.data),
+                                         static_cast<const uint8_t*>(d->hidden_scale.data), w.rt.route_prows,
+                                         routes, p.top_k, p.hidden_size, w.xq, w.xq_sf, st);
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "NVFP4 MoE routing");
+    Nvfp4Weights wt {};
+    wt.gu_packed = static_cast<const uint8_t*>(d->gate_up_weight.data);
+    wt.gu_sf_tiled = static_cast<const uint8_t*>(d->gate_up_scale_tiled.data);
+    wt.gu_global = static_cast<const float*>(d->gate_up_global_scale.data);
+    wt.d_packed = static_cast<const uint8_t*>(d->down_weight.data);
+    wt.d_sf_tiled = static_cast<const uint8_t*>(d->down_scale_tiled.data);
+    wt.d_global = static_cast<const float*>(d->down_global_scale.data);
+    status = run_routed_nvfp4(ctx, p, w, wt, d->act_global_scale, d->act2_global_scale);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    CombineParams cp {};
+    cp.route_prows = w.rt.route_prows;
+    cp.topk_weights = static_cast<const float*>(d->topk_weights.data);
+    cp.expert_out = w.y2;
+    cp.out = static_cast<__nv_bfloat16*>(d->out.data);
+    cp.num_tokens = d->num_tokens;
+    cp.top_k = p.top_k;
+    cp.hidden_size = p.hidden_size;
+    return set_cuda_error(ctx, launch_combine(cp, st), "qs3_moe_execute_nvfp4_prepared");
+}
+
+qsfi_status qs3_moe_ep_finish_workspace_size(qsfi_context* ctx, const qsfi_moe_plan* plan, uint32_t num_tokens,
+                                             uint32_t num_ranks, uint32_t shared_intermediate_size,
+                                             size_t* device_bytes)
+{
+    if (device_bytes == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    *device_bytes = 0;
+    if (ctx == nullptr || plan == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    if (num_tokens == 0 || num_ranks == 0 || num_ranks > 32)
+        return set_invalid_arg(ctx, "invalid expert-parallel finish dimensions");
+    const size_t routes = static_cast<size_t>(num_tokens) * num_ranks;
+    size_t off = 0;
+    carve<int32_t>(nullptr, off, routes);
+    carve<float>(nullptr, off, routes);
+    const size_t base = align_up(off, kWorkspaceAlign);
+    *device_bytes = carve_layer(nullptr, base, plan->desc, num_tokens, shared_intermediate_size, true).bytes;
+    return QSFI_STATUS_OK;
+}
+
+qsfi_status qs3_moe_ep_finish(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_ep_finish_desc* d)
+{
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (plan == nullptr || d == nullptr)
+        return set_invalid_arg(ctx, "plan/desc is null");
+    const qsfi_moe_plan_desc& p = plan->desc;
+    if (p.backend != QSFI_MOE_BACKEND_FLASHINFER_NVFP4)
+        return set_invalid_arg(ctx, "qs3_moe_ep_finish requires an NVFP4 MoE plan");
+    if (d->num_tokens == 0 || d->num_ranks == 0 || d->num_ranks > 32 || (d->phases & 3u) == 0)
+        return set_invalid_arg(ctx, "invalid expert-parallel finish dimensions");
+    const int64_t t = d->num_tokens, h = p.hidden_size;
+    const uint32_t is = d->shared_intermediate_size;
+    const bool shared = d->shared_gate_up_weight.data != nullptr;
+    status = validate_tensor(ctx, d->hidden, "hidden", QSFI_DTYPE_BF16);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (!contiguous2(d->hidden) || d->hidden.shape[0] != t || d->hidden.shape[1] != h)
+        return set_invalid_arg(ctx, "MoE token/top-k tensor shape mismatch");
+    if (shared) {
+        if (is == 0 || is % 256 != 0)
+            return set_invalid_arg(ctx, "invalid shared_intermediate_size");
+        status = validate_tensor(ctx, d->shared_gate_up_weight, "shared_gate_up_weight", QSFI_DTYPE_U8);
+        if (status == QSFI_STATUS_OK)
+            status = validate_tensor(ctx, d->shared_down_weight, "shared_down_weight", QSFI_DTYPE_U8);
+        if (status == QSFI_STATUS_OK)
+            status = validate_tensor(ctx, d->shared_gate_weight, "shared_gate_weight", QSFI_DTYPE_BF16);
+        if (status != QSFI_STATUS_OK)
+            return status;
+        if (!contiguous3(d->shared_gate_up_weight) || !contiguous3(d->shared_down_weight)
+            || !contiguous2(d->shared_gate_weight) || d->shared_gate_up_weight.shape[0] != 1
+            || d->shared_gate_up_weight.shape[1] != 2ll * is || d->shared_gate_up_weight.shape[2] != h / 2
+            || d->shared_down_weight.shape[0] != 1 || d->shared_down_weight.shape[1] != h
+            || d->shared_down_weight.shape[2] != is / 2 || d->shared_gate_weight.shape[0] != 1
+            || d->shared_gate_weight.shape[1] != h)
+            return set_invalid_arg(ctx, "MoE shared expert weight shape mismatch");
+        if (d->shared_gate_up_scale_tiled.data == nullptr || d->shared_down_scale_tiled.data == nullptr
+            || static_cast<uint64_t>(d->shared_gate_up_scale_tiled.shape[0]) < qs3_nvfp4_tiled_scale_bytes(2 * is, h)
+            || static_cast<uint64_t>(d->shared_down_scale_tiled.shape[0]) < qs3_nvfp4_tiled_scale_bytes(h, is))
+            return set_invalid_arg(ctx, "NVFP4 MoE layer needs tiled shared-expert scales of the right size");
+        status = validate_nvfp4_dims(ctx, p.hidden_size, is, "shared-expert");
+        if (status != QSFI_STATUS_OK)
+            return status;
+    }
+    size_t need = 0;
+    status = qs3_moe_ep_finish_workspace_size(ctx, plan, d->num_tokens, d->num_ranks, shared ? is : 0, &need);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_workspace(ctx, d->workspace, need);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    char* base = static_cast<char*>(d->workspace.data);
+    size_t off = 0;
+    const size_t routes = static_cast<size_t>(d->num_tokens) * d->num_ranks;
+    int32_t* rows = carve<int32_t>(base, off, routes);
+    float* ones = carve<float>(base, off, routes);
+    LayerExtra x = carve_layer(base, align_up(off, kWorkspaceAlign), p, d->num_tokens, shared ? is : 0, true);
+    cudaStream_t st = ctx->stream;
+    const __nv_bfloat16* hidden = static_cast<const __nv_bfloat16*>(d->hidden.data);
+
+    if ((d->phases & 1u) != 0 && shared) {
+        cudaError_t err = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
+                                                       d->act_global_scale, x.sh_xq, x.sh_xq_sf, st);
+        if (err != cudaSuccess)
+            return set_cuda_error(ctx, err, "NVFP4 shared expert quantise");
+        const float ga = d->act_global_scale == 0.0f ? 1.0f : d->act_global_scale;
+        const float ga2 = d->act2_global_scale == 0.0f ? 1.0f : d->act2_global_scale;
+        GemmProblem s1 {};
+        s1.nvfp4 = 1;
+        s1.a = x.sh_xq;
+        s1.a_rows = d->num_tokens;
+        s1.a_pitch_bytes = h / 2;
+        s1.a_scale_tiled = x.sh_xq_sf;
+        s1.b = d->shared_gate_up_weight.data;
+        s1.b_pitch_bytes = h / 2;
+        s1.b_scale_tiled = static_cast<const uint8_t*>(d->shared_gate_up_scale_tiled.data);
+        s1.groups = 1;
+        s1.n = is;
+        s1.k = p.hidden_size;
+        s1.gated = 1;
+        s1.epilogue = EPI_SWIGLU_NVFP4;
+        s1.out = x.sh_actq;
+        s1.out_pitch_elems = is / 2;
+        s1.out_scale_tiled = x.sh_actq_sf;
+        s1.alpha = ga;
+        s1.group_scale = static_cast<const float*>(d->shared_gate_up_global_scale.data);
+        s1.out_global_scale = ga2;
+        status = gemm_or_error(ctx, s1, "NVFP4 shared gate_up GEMM");
+        if (status != QSFI_STATUS_OK)
+            return status;
+        GemmProblem s2 {};
+        s2.nvfp4 = 1;
+        s2.a = x.sh_actq;
+        s2.a_rows = d->num_tokens;
+        s2.a_pitch_bytes = is / 2;
+        s2.a_scale_tiled = x.sh_actq_sf;
+        s2.b = d->shared_down_weight.data;
+        s2.b_pitch_bytes = is / 2;
+        s2.b_scale_tiled = static_cast<const uint8_t*>(d->shared_down_scale_tiled.data);
+        s2.groups = 1;
+        s2.n = p.hidden_size;
+        s2.k = is;
+        s2.epilogue = EPI_STORE_BF16;
+        s2.out = x.sh_out;
+        s2.out_pitch_elems = p.hidden_size;
+        s2.alpha = ga2;
+        s2.group_scale = static_cast<const float*>(d->shared_down_global_scale.data);
+        status = gemm_or_error(ctx, s2, "NVFP4 shared down GEMM");
+        if (status != QSFI_STATUS_OK)
+            return status;
+    }
+    if ((d->phases & 2u) != 0) {
+        status = validate_tensor(ctx, d->partials, "partials", QSFI_DTYPE_BF16);
+        if (status == QSFI_STATUS_OK)
+            status = validate_tensor(ctx, d->out, "out", QSFI_DTYPE_BF16);
+        if (status != QSFI_STATUS_OK)
+            return status;
+        if (!contiguous3(d->partials) || d->partials.shape[0] != d->num_ranks || d->partials.shape[1] != t
+            || d->partials.shape[2] != h || !contiguous2(d->out) || d->out.shape[0] != t || d->out.shape[1] != h)
+            return set_invalid_arg(ctx, "expert-parallel partial-sum tensor shape mismatch");
+        if (!aligned16(d->partials.data) || !aligned16(d->out.data))
+            return set_invalid_arg(ctx, "MoE tensors must be 16-byte aligned");
+        // out[t] = sum over source ranks r (ascending) of partials[r][t]: the combine
+        // kernel with one unit-weight "route" per rank pointing at row r * T + t
+        cudaError_t err = launch_ep_rank_routes(rows, ones, d->num_tokens, d->num_ranks, st);
+        if (err != cudaSuccess)
+            return set_cuda_error(ctx, err, "expert-parallel combine setup");
+        CombineParams cp {};
+        cp.route_prows = rows;
+        cp.topk_weights = ones;
+        cp.expert_out = static_cast<const __nv_bfloat16*>(d->partials.data);
+        cp.out = static_cast<__nv_bfloat16*>(d->out.data);
+        cp.num_tokens = d->num_tokens;
+        cp.top_k = d->num_ranks;
+        cp.hidden_size = p.hidden_size;
+        if (shared) {
+            cp.shared_out = x.sh_out;
+            cp.hidden = hidden;
+            cp.gate_w = static_cast<const __nv_bfloat16*>(d->shared_gate_weight.data);
+        }
+        return set_cuda_error(ctx, launch_combine(cp, st), "qs3_moe_ep_finish");
+    }
+    return QSFI_STATUS_OK;
+}
+
 } // extern "C"

@@ -317,6 +317,17 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p)
     }
 }
 
+// rows[t * ranks + r] = r * tokens + t, weights = 1: lets the combine kernel sum the
+// per-rank partial rows of one token in ascending rank order.
+__global__ void ep_rank_routes_kernel(int32_t* rows, float* weights, uint32_t tokens, uint32_t ranks)
+{
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= tokens * ranks)
+        return;
+    rows[i] = static_cast<int32_t>((i % ranks) * tokens + i / ranks);
+    weights[i] = 1.0f;
+}
+
 template <typename T> T* carve(char* base, size_t& offset, size_t count)
 {
     offset = align_up(offset, kWorkspaceAlign);
@@ -326,6 +337,15 @@ template <typename T> T* carve(char* base, size_t& offset, size_t count)
 }
 
 } // namespace
+
+cudaError_t launch_ep_rank_routes(int32_t* rows, float* weights, uint32_t tokens, uint32_t ranks,
+                                  cudaStream_t stream)
+{
+    const uint32_t total = tokens * ranks;
+    ep_rank_routes_kernel<<<(total + 255) / 256, 256, 0, stream>>>(rows, weights, tokens, ranks);
+    note_launch();
+    return cudaGetLastError();
+}
 
 size_t route_tables_carve(char* base, uint32_t routes, uint32_t experts, RouteTables* out)
 {
