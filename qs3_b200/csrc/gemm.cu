@@ -17,192 +17,16 @@
 // Every wait is bounded: when a barrier does not flip within ~1 s of SM clocks the
 // kernel records a code in the device error word and leaves through the normal
 // teardown (tensor memory is freed).
-#include "common.cuh"
-#include "nvfp4.cuh"
+#include "tcgen05.cuh"
 
+#include <algorithm>
 #include <mutex>
 
 namespace qs3 {
 
 namespace {
 
-constexpr int kBM = 128;         // tile rows (tensor-memory lanes)
-constexpr int kBN = 128;         // tile columns (accumulator columns)
-constexpr int kStages = 3;
-constexpr int kTileBytes = 128 * 128; // one operand tile: 128 rows x 128 bytes
-constexpr int kSfBytes = 2048;        // scale tile of one stage: 4 k-groups x 512 bytes
-constexpr int kThreads = 192;
-constexpr uint64_t kWaitCycles = 2000000000ull;
-
-enum : uint32_t {
-    ERR_FULL_WAIT = 0x51000001u,
-    ERR_EMPTY_WAIT = 0x51000002u,
-    ERR_ACC_WAIT = 0x51000003u,
-};
-
-struct TcParams {
-    uint32_t n;             // output features (gated: gate features)
-    uint32_t k_blocks;      // number of 128-byte k blocks
-    uint32_t b_rows;        // B rows per group
-    uint32_t kgroups;       // k / 64, NVFP4 scale tiling
-    const uint8_t* sfa;
-    const uint8_t* sfb;
-    uint64_t sfb_group_stride;
-    const int32_t* tile_expert;
-    const int32_t* tile_row0;
-    const int32_t* tile_nrows;
-    const int32_t* total_tiles;
-    uint32_t dense_rows;
-    void* out;
-    uint64_t out_pitch;     // elements; bytes for packed output
-    uint8_t* out_sf;
-    uint32_t out_kgroups;   // n / 64 of the quantised output
-    float alpha;
-    float beta;
-    const float* group_scale;
-    const float* bias;
-    float out_global;
-    uint32_t* err;
-};
-
-// ---- PTX wrappers -------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p)
-{
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok)
-                 : "r"(smem_u32(bar)), "r"(parity)
-                 : "memory");
-    return ok != 0;
-}
-
-// Bounded wait; on expiry records `code` and raises the CTA's abort flag.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* err, uint32_t code)
-{
-    if (mbar_try_wait(bar, parity))
-        return true;
-    const uint64_t start = clock64();
-    while (true) {
-        if (mbar_try_wait(bar, parity))
-            return true;
-        if (*abort_flag != 0)
-            return false;
-        if (static_cast<uint64_t>(clock64()) - start > kWaitCycles) {
-            *abort_flag = 1;
-            if (err != nullptr)
-                atomicCAS(err, 0u, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-                 " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
-                 "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-                 : "memory");
-}
-
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint64_t* bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void tc_cp_scales(uint32_t taddr, uint64_t sdesc)
-{
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc)
-{
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
-                 "l"(a), "l"(b), "r"(idesc), "r"(acc)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tc_mma_nvfp4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc,
-                                             uint32_t sfa, uint32_t sfb)
-{
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X"
-                 " [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d),
-                 "l"(a), "l"(b), "r"(idesc), "r"(acc), "r"(sfa), "r"(sfb)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r)
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32"
-                 " {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                   "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-                   "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major operand tile stored with the
-// 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes apart.
-__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr)
-{
-    return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (static_cast<uint64_t>(1024 >> 4) << 32)
-        | (1ull << 46) | (2ull << 61);
-}
-
-// Descriptor of one 512-byte scale tile (32 rows x 16 bytes, no swizzle; groups of
-// 8 rows are 128 bytes apart) for tcgen05.cp.32x128b.
-__device__ __forceinline__ uint64_t scale_desc(uint32_t smem_addr)
-{
-    return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (static_cast<uint64_t>(128 >> 4) << 32)
-        | (1ull << 46);
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b)
-{
-    const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
-
-__device__ __forceinline__ float round_bf16(float v)
-{
-    return __bfloat162float(__float2bfloat16(v));
-}
+using namespace tc;
 
 // ---- the kernel ---------------------------------------------------------------------
 
@@ -350,131 +174,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const bool ready = __all_sync(0xffffffffu, mbar_wait(acc_bar, 0, abort_flag, p.err, ERR_ACC_WAIT));
         tc_fence_after();
         if (ready) {
-            const int r = static_cast<int>(warp * 32 + lane); // tile row = TMEM lane
-            const bool row_ok = r < nrows;
-            const uint64_t grow = static_cast<uint64_t>(row0) + r;
-            const uint32_t lane_base = (warp * 32) << 16;
-            float scale = p.alpha == 0.0f ? 1.0f : p.alpha;
-            if (p.group_scale != nullptr)
-                scale *= p.group_scale[expert];
-
-            if constexpr (!GATED) {
-                for (uint32_t c = 0; c < kBN / 16; ++c) {
-                    const uint32_t nb = n0 + c * 16;
-                    if (nb >= p.n)
-                        break;
-                    uint32_t v[16];
-                    tc_ld16(tmem_base + lane_base + c * 16, v);
-                    tc_ld_wait();
-                    if (!row_ok)
-                        continue;
-                    float f[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        f[i] = __uint_as_float(v[i]) * scale;
-                    const bool full = nb + 16 <= p.n;
-                    if constexpr (EPI == EPI_STORE_F32) {
-                        float* o = static_cast<float*>(p.out) + grow * p.out_pitch + nb;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            if (full || nb + i < p.n) {
-                                if (p.beta != 0.0f)
-                                    f[i] += p.beta * o[i];
-                                if (p.bias != nullptr)
-                                    f[i] += p.bias[nb + i];
-                            }
-                        }
-                        if (full && ((reinterpret_cast<uintptr_t>(o) & 15u) == 0)) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                reinterpret_cast<float4*>(o)[i]
-                                    = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                if (nb + i < p.n)
-                                    o[i] = f[i];
-                        }
-                    } else {
-                        __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + grow * p.out_pitch + nb;
-                        if (p.beta != 0.0f) {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                if (full || nb + i < p.n)
-                                    f[i] += p.beta * __bfloat162float(o[i]);
-                        }
-                        if (full && ((reinterpret_cast<uintptr_t>(o) & 15u) == 0)) {
-                            uint32_t w[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                w[i] = pack_bf16x2(f[2 * i], f[2 * i + 1]);
-                            reinterpret_cast<uint4*>(o)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                            reinterpret_cast<uint4*>(o)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                if (nb + i < p.n)
-                                    o[i] = __float2bfloat16(f[i]);
-                        }
-                    }
-                }
-            } else {
-                uint32_t sf_word = 0;
-                for (uint32_t c = 0; c < kFeat / 16; ++c) {
-                    const uint32_t fb = n0 + c * 16; // first gate feature of this chunk
-                    if (fb >= p.n)
-                        break;
-                    uint32_t vg[16], vu[16];
-                    tc_ld16(tmem_base + lane_base + c * 16, vg);
-                    tc_ld16(tmem_base + lane_base + kFeat + c * 16, vu);
-                    tc_ld_wait();
-                    if (!row_ok)
-                        continue;
-                    float act[16];
-                    if constexpr (EPI == EPI_SWIGLU_BF16) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            // upstream stores the gate_up product as bf16 before SwiGLU
-                            // (qsfi_moe.cu:638-651,445-463)
-                            const float g = round_bf16(__uint_as_float(vg[i]) * scale);
-                            const float u = round_bf16(__uint_as_float(vu[i]) * scale);
-                            act[i] = g * sigmoid_fast(g) * u;
-                        }
-                        __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + grow * p.out_pitch + fb;
-                        if (fb + 16 <= p.n && ((reinterpret_cast<uintptr_t>(o) & 15u) == 0)) {
-                            uint32_t w[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                w[i] = pack_bf16x2(act[2 * i], act[2 * i + 1]);
-                            reinterpret_cast<uint4*>(o)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                            reinterpret_cast<uint4*>(o)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                if (fb + i < p.n)
-                                    o[i] = __float2bfloat16(act[i]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const float g = __uint_as_float(vg[i]) * scale;
-                            const float u = __uint_as_float(vu[i]) * scale;
-                            act[i] = g * sigmoid_fast(g) * u;
-                        }
-                        uint32_t lo, hi;
-                        const uint8_t code = quantize_block16(act, p.out_global, &lo, &hi);
-                        sf_word |= static_cast<uint32_t>(code) << (8 * c);
-                        uint8_t* o = static_cast<uint8_t*>(p.out) + grow * p.out_pitch + fb / 2;
-                        *reinterpret_cast<uint2*>(o) = make_uint2(lo, hi);
-                    }
-                }
-                if constexpr (EPI == EPI_SWIGLU_NVFP4) {
-                    // the tile's 64 features are exactly one k-group of the next GEMM
-                    if (row_ok && n0 < p.n)
-                        *reinterpret_cast<uint32_t*>(p.out_sf + tiled_scale_offset(grow, 4ull * nt, p.out_kgroups))
-                            = sf_word;
-                }
-            }
+            epilogue_tile<GATED, EPI>(p, tmem_base, warp, lane, expert, row0, nrows, nt);
         }
     }
 
@@ -482,6 +182,243 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---- NVFP4 kernel with a resident A panel ------------------------------------------------
+//
+// The 128 x 128 kernel above re-streams its A tile for every column tile, so each byte
+// brought into shared memory feeds only ~233 FLOP and the kernel is bound by L2 -> SM
+// operand delivery. Here one CTA owns a 128-row tile, loads the whole [128, k] A panel
+// (codes: k/2 bytes per row, up to 128 KB; scales: straight into tensor memory) ONCE and
+// then walks its share of the column tiles streaming only B through the ring, which
+// doubles the FLOP per streamed byte. Two 128-column accumulators in tensor memory
+// alternate, so the epilogue of column tile i overlaps the MMAs of tile i + 1.
+//
+//   TMEM: [0,128) acc 0 | [128,256) acc 1 | [256,384) A scales (k/64 * 4 columns) | [384,400) B scales
+//   smem: A panel k_blocks x 16 KB | A-scale staging k_blocks x 2 KB | ring of (16 KB B + 2 KB scales)
+//
+// Grid: (n_splits, row tiles). A CTA handles column tiles [split * per, ...); n_splits > 1
+// only when there are too few row tiles to fill the GPU.
+constexpr int kAsMaxKBlocks = 8;   // k <= 2048
+constexpr int kAsMaxStages = 8;
+constexpr int kAsThreads = 320;    // warps 0-7 epilogue (two per TMEM lane quadrant), 8 producer, 9 MMA
+constexpr uint32_t kAsStageBytes = kTileBytes + kSfBytes;
+
+enum : uint32_t {
+    ERR_AS_PANEL_WAIT = 0x52000001u,
+    ERR_AS_FULL_WAIT = 0x52000002u,
+    ERR_AS_EMPTY_WAIT = 0x52000003u,
+    ERR_AS_ACC_FULL_WAIT = 0x52000004u,
+    ERR_AS_ACC_EMPTY_WAIT = 0x52000005u,
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <bool GATED, int EPI>
+__global__ void __launch_bounds__(kAsThreads, 1)
+gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const TcParams p, const uint32_t stages, const uint32_t nt_per_split)
+{
+    const uint32_t tile = blockIdx.y;
+    int expert = 0, row0 = 0, nrows = 0;
+    if (p.tile_expert != nullptr) {
+        if (static_cast<int>(tile) >= *p.total_tiles)
+            return;
+        expert = p.tile_expert[tile];
+        row0 = p.tile_row0[tile];
+        nrows = p.tile_nrows[tile];
+    } else {
+        row0 = static_cast<int>(tile) * kBM;
+        nrows = min(kBM, static_cast<int>(p.dense_rows) - row0);
+    }
+    constexpr uint32_t kFeat = GATED ? kBN / 2 : kBN;
+    const uint32_t n_tiles = (p.n + kFeat - 1) / kFeat;
+    const uint32_t nt_begin = blockIdx.x * nt_per_split;
+    const uint32_t nt_end = min(n_tiles, nt_begin + nt_per_split);
+    if (nt_begin >= nt_end)
+        return;
+    const uint32_t kb_count = p.k_blocks;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* a_panel = smem;
+    uint8_t* sfa_stage = a_panel + kb_count * kTileBytes;
+    uint8_t* ring = sfa_stage + kb_count * kSfBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + stages * kAsStageBytes);
+    uint64_t* empty_bar = full_bar + kAsMaxStages;
+    uint64_t* acc_full = empty_bar + kAsMaxStages;
+    uint64_t* acc_empty = acc_full + 2;
+    uint64_t* panel_bar = acc_empty + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(panel_bar + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    constexpr uint32_t kTmemCols = 512;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8); // one arrival per epilogue warp
+        }
+        mbar_init(panel_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_sfa = tmem_base + 256;
+    const uint32_t tmem_sfb = tmem_base + 384; // two 16-column buffers, alternating per stage
+    const uint32_t total_loads = (nt_end - nt_begin) * kb_count;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------ producer --
+        if (lane == 0) {
+            // the A panel and its scales, once
+            mbar_expect_tx(panel_bar, kb_count * (kTileBytes + kSfBytes));
+            for (uint32_t kb = 0; kb < kb_count; ++kb)
+                tma_load_2d(a_panel + kb * kTileBytes, &map_a, panel_bar, static_cast<int>(kb) * 128, row0);
+            bulk_load(sfa_stage, p.sfa + (static_cast<uint64_t>(row0 >> 7) * p.kgroups) * 512,
+                      kb_count * kSfBytes, panel_bar);
+            // B tiles of every column tile of this CTA
+            uint32_t it = 0;
+            for (uint32_t nt = nt_begin; nt < nt_end; ++nt) {
+                const int b_row = expert * static_cast<int>(p.b_rows) + static_cast<int>(nt * kFeat);
+                const uint8_t* sfb_src = p.sfb + static_cast<uint64_t>(expert) * p.sfb_group_stride
+                    + (static_cast<uint64_t>(nt) * p.kgroups) * 512;
+                bool ok = true;
+                for (uint32_t kb = 0; kb < kb_count; ++kb, ++it) {
+                    const uint32_t s = it % stages;
+                    const uint32_t ph = (it / stages) & 1;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_AS_EMPTY_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sb = ring + s * kAsStageBytes;
+                    if (p.debug & 1u) {
+                        mbar_arrive(&full_bar[s]);
+                        continue;
+                    }
+                    mbar_expect_tx(&full_bar[s], kAsStageBytes);
+                    const int c0 = static_cast<int>(kb) * 128;
+                    if (GATED) {
+                        tma_load_2d(sb, &map_b, &full_bar[s], c0, b_row);
+                        tma_load_2d(sb + kTileBytes / 2, &map_b, &full_bar[s], c0, b_row + static_cast<int>(p.n));
+                    } else {
+                        tma_load_2d(sb, &map_b, &full_bar[s], c0, b_row);
+                    }
+                    bulk_load(sb + kTileBytes, sfb_src + static_cast<uint64_t>(kb) * kSfBytes, kSfBytes,
+                              &full_bar[s]);
+                }
+                if (!ok)
+                    break;
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------------------------------------------------- MMA issuer --
+        if (lane == 0) {
+            constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+            bool ok = mbar_wait(panel_bar, 0, abort_flag, p.err, ERR_AS_PANEL_WAIT);
+            if (ok) {
+                tc_fence_after();
+                // A scales: one 512-byte tile per 64 k elements -> 4 TMEM columns each
+                for (uint32_t g = 0; g < kb_count * 4; ++g)
+                    tc_cp_scales(tmem_sfa + 4 * g, scale_desc(smem_u32(sfa_stage) + g * 512));
+            }
+            uint32_t it = 0;
+            for (uint32_t nt = nt_begin; ok && nt < nt_end; ++nt) {
+                const uint32_t local = nt - nt_begin;
+                const uint32_t buf = local & 1;
+                const uint32_t use = local >> 1;
+                if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.err, ERR_AS_ACC_EMPTY_WAIT)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + buf * kBN;
+                for (uint32_t kb = 0; kb < kb_count; ++kb, ++it) {
+                    const uint32_t s = it % stages;
+                    const uint32_t ph = (it / stages) & 1;
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, ERR_AS_FULL_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sb = smem_u32(ring + s * kAsStageBytes);
+                    if (!(p.debug & 2u)) {
+#pragma unroll
+                        // B scales alternate between two TMEM buffers so that this copy does
+                        // not have to wait for the previous stage's MMAs to finish reading
+                        const uint32_t sfb_cols = tmem_sfb + 16 * (it & 1);
+                        if (!(p.debug & 8u))
+                            for (uint32_t j = 0; j < 4; ++j)
+                                tc_cp_scales(sfb_cols + 4 * j, scale_desc(sb + kTileBytes + j * 512));
+                        const uint64_t da = operand_desc(smem_u32(a_panel + kb * kTileBytes));
+                        const uint64_t db = operand_desc(sb);
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            if ((p.debug & 32u) && (j & 1))
+                                continue; // timing experiment: half the MMAs
+                            // timing experiment (debug 16): N = 256 instructions on the same operands
+                            const uint32_t idesc = (p.debug & 16u)
+                                ? ((1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((kBM >> 4) << 24))
+                                : kIdesc;
+                            tc_mma_nvfp4((p.debug & 16u) ? tmem_base : tmem_acc, da + 2 * j, db + 2 * j, idesc,
+                                         (kb > 0 || j > 0) ? 1u : 0u, tmem_sfa + 16 * kb + 4 * j, sfb_cols + 4 * j);
+                        }
+                    }
+                    tc_commit(&empty_bar[s]);
+                }
+                if (ok)
+                    tc_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue --
+        for (uint32_t nt = nt_begin; nt < nt_end; ++nt) {
+            const uint32_t local = nt - nt_begin;
+            const uint32_t buf = local & 1;
+            const uint32_t use = local >> 1;
+            const bool ready = __all_sync(
+                0xffffffffu, mbar_wait(&acc_full[buf], use & 1, abort_flag, p.err, ERR_AS_ACC_FULL_WAIT));
+            if (!ready)
+                break;
+            tc_fence_after();
+            if (!(p.debug & 4u))
+                epilogue_tile<GATED, EPI, 2>(p, tmem_base + buf * kBN, warp & 3, lane, expert, row0, nrows, nt,
+                                             warp >> 2);
+            // hand the accumulator back once every lane of the warp has read it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    (void)total_loads;
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                      : "memory");
@@ -614,6 +551,57 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
     return cudaGetLastError();
 }
 
+template <bool GATED, int EPI>
+cudaError_t launch_astat(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& tp, dim3 grid,
+                         uint32_t nt_per_split, cudaStream_t stream)
+{
+    constexpr size_t kSmemBudget = 227 * 1024 - 1024 /* alignment slack */ - 512 /* barriers */;
+    const size_t panel = static_cast<size_t>(tp.k_blocks) * (kTileBytes + kSfBytes);
+    uint32_t stages = static_cast<uint32_t>((kSmemBudget - panel) / kAsStageBytes);
+    stages = std::min<uint32_t>(stages, kAsMaxStages);
+    const size_t smem = panel + static_cast<size_t>(stages) * kAsStageBytes + 1024 + 512;
+    auto kernel = gemm_tc_astat_kernel<GATED, EPI>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess)
+        return err;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (err != cudaSuccess)
+            return err;
+        if (dev >= 0 && dev < 64)
+            configured[dev] = true;
+    }
+    kernel<<<grid, kAsThreads, smem, stream>>>(ma, mb, tp, stages, nt_per_split);
+    note_launch();
+    return cudaGetLastError();
+}
+
+bool astat_enabled()
+{
+    static const bool on = [] {
+        const char* v = getenv("QS3_GEMM_RESIDENT_A");
+        return v == nullptr || v[0] != '0';
+    }();
+    return on;
+}
+
+uint32_t sm_count()
+{
+    static int count[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return 148;
+    if (count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        count[dev] = n;
+    }
+    return static_cast<uint32_t>(count[dev]);
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 TcParams make_params(const GemmProblem& g)
@@ -641,6 +629,11 @@ TcParams make_params(const GemmProblem& g)
     tp.bias = g.bias;
     tp.out_global = g.out_global_scale == 0.0f ? 1.0f : g.out_global_scale;
     tp.err = device_error_word();
+    static const uint32_t debug = [] {
+        const char* v = getenv("QS3_GEMM_DEBUG");
+        return v != nullptr ? static_cast<uint32_t>(atoi(v)) : 0u;
+    }();
+    tp.debug = debug;
     return tp;
 }
 
@@ -688,6 +681,22 @@ cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** 
             if (why != nullptr)
                 *why = "cuTensorMapEncodeTiled failed";
             return cudaErrorInvalidValue;
+        }
+        if (g.nvfp4 && tp.k_blocks <= kAsMaxKBlocks && astat_enabled()) {
+            // resident-A kernel: row tiles (estimated on the host) decide how far the
+            // column tiles of one row tile are split over CTAs
+            const uint32_t n_tiles = grid.x;
+            const uint32_t m_est = g.tile_expert != nullptr
+                ? (g.max_tiles > g.groups ? g.max_tiles - g.groups : 1u)
+                : m_tiles;
+            const uint32_t want_splits = std::max(1u, (2u * sm_count() + m_est - 1) / m_est);
+            const uint32_t nt_per = std::max(1u, (n_tiles + want_splits - 1) / want_splits);
+            const uint32_t splits = (n_tiles + nt_per - 1) / nt_per;
+            dim3 agrid(splits, m_tiles, 1);
+            if (g.gated && g.epilogue == EPI_SWIGLU_NVFP4)
+                return launch_astat<true, EPI_SWIGLU_NVFP4>(ma, mb, tp, agrid, nt_per, stream);
+            if (!g.gated && g.epilogue == EPI_STORE_BF16)
+                return launch_astat<false, EPI_STORE_BF16>(ma, mb, tp, agrid, nt_per, stream);
         }
         if (g.nvfp4) {
             if (g.gated && g.epilogue == EPI_SWIGLU_NVFP4)

@@ -144,12 +144,17 @@ LayerExtra carve_layer(char* base, size_t start, const qsfi_moe_plan_desc& d, ui
     x.logits = carve<float>(base, off, t * d.num_experts);
     x.topk_ids = carve<int32_t>(base, off, t * d.top_k);
     x.topk_weights = carve<float>(base, off, t * d.top_k);
+    if (nvfp4) {
+        // tokens quantised once, in token order: source of the routed gather and A operand
+        // of the shared expert
+        const size_t t128 = align_up(t, kTileM);
+        x.sh_xq = carve<uint8_t>(base, off, t128 * h / 2);
+        x.sh_xq_sf = carve<uint8_t>(base, off, qs3_nvfp4_tiled_scale_bytes(t128, h));
+    }
     if (shared_inter != 0) {
         x.sh_out = carve<__nv_bfloat16>(base, off, t * h);
         if (nvfp4) {
             const size_t t128 = align_up(t, kTileM);
-            x.sh_xq = carve<uint8_t>(base, off, t128 * h / 2);
-            x.sh_xq_sf = carve<uint8_t>(base, off, qs3_nvfp4_tiled_scale_bytes(t128, h));
             x.sh_actq = carve<uint8_t>(base, off, t128 * shared_inter / 2);
             x.sh_actq_sf = carve<uint8_t>(base, off, qs3_nvfp4_tiled_scale_bytes(t128, shared_inter));
         } else {
@@ -889,10 +894,14 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
 
     const __nv_bfloat16* y2 = nullptr;
     if (nvfp4) {
-        // 4. gather + quantise, 5./6. grouped GEMMs
+        // 4. quantise every token once (token order), then gather the codes by expert;
+        //    5./6. grouped GEMMs
         stage_mark(st, STAGE_GATHER);
-        err = launch_nvfp4_gather_quantize(hidden, rt.route_prows, routes, p.top_k, p.hidden_size,
-                                           d->act_global_scale, wn.xq, wn.xq_sf, st);
+        err = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
+                                           d->act_global_scale, x.sh_xq, x.sh_xq_sf, st);
+        if (err == cudaSuccess)
+            err = launch_nvfp4_gather_packed(x.sh_xq, x.sh_xq_sf, rt.route_prows, routes, p.top_k,
+                                             p.hidden_size, wn.xq, wn.xq_sf, st, 1);
         if (err != cudaSuccess)
             return set_cuda_error(ctx, err, "NVFP4 MoE gather");
         Nvfp4Weights wt {};
@@ -909,10 +918,6 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         if (shared) {
             // 7. shared expert as a dense problem over the tokens in natural order
             stage_mark(st, STAGE_SHARED);
-            err = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
-                                               d->act_global_scale, x.sh_xq, x.sh_xq_sf, st);
-            if (err != cudaSuccess)
-                return set_cuda_error(ctx, err, "NVFP4 shared expert quantise");
             const float ga = d->act_global_scale == 0.0f ? 1.0f : d->act_global_scale;
             const float ga2 = d->act2_global_scale == 0.0f ? 1.0f : d->act2_global_scale;
             GemmProblem s1 {};

@@ -136,7 +136,8 @@ gather_quantize_kernel(const __nv_bfloat16* __restrict__ hidden, const int32_t* 
 __global__ void __launch_bounds__(256)
 gather_packed_kernel(const uint8_t* __restrict__ hidden_packed, const uint8_t* __restrict__ hidden_scale,
                      const int32_t* __restrict__ route_prows, uint64_t total, uint32_t top_k,
-                     uint32_t hidden_size, uint8_t* __restrict__ packed, uint8_t* __restrict__ scale_tiled)
+                     uint32_t hidden_size, uint8_t* __restrict__ packed, uint8_t* __restrict__ scale_tiled,
+                     int src_scale_tiled)
 {
     const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total)
@@ -152,7 +153,10 @@ gather_packed_kernel(const uint8_t* __restrict__ hidden_packed, const uint8_t* _
     uint4* dst = reinterpret_cast<uint4*>(packed + static_cast<uint64_t>(prow) * (hidden_size / 2) + kg * 32);
     dst[0] = src[0];
     dst[1] = src[1];
-    const uint32_t sf = *reinterpret_cast<const uint32_t*>(hidden_scale + token * (hidden_size / 16) + kg * 4);
+    // source scales: row-major [T, H/16], or already tiled by token row
+    const uint64_t src_off = src_scale_tiled ? tiled_scale_offset(token, 4ull * kg, kgroups)
+                                             : token * (hidden_size / 16) + kg * 4;
+    const uint32_t sf = *reinterpret_cast<const uint32_t*>(hidden_scale + src_off);
     *reinterpret_cast<uint32_t*>(scale_tiled + tiled_scale_offset(prow, 4ull * kg, kgroups)) = sf;
 }
 
@@ -201,11 +205,12 @@ cudaError_t launch_nvfp4_gather_quantize(const __nv_bfloat16* hidden, const int3
 cudaError_t launch_nvfp4_gather_packed(const uint8_t* hidden_packed, const uint8_t* hidden_scale,
                                        const int32_t* route_prows, uint32_t routes, uint32_t top_k,
                                        uint32_t hidden_size, uint8_t* packed, uint8_t* scale_tiled,
-                                       cudaStream_t stream)
+                                       cudaStream_t stream, int src_scale_tiled)
 {
     const uint64_t total = static_cast<uint64_t>(routes) * (hidden_size / 64);
     gather_packed_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
-        hidden_packed, hidden_scale, route_prows, total, top_k, hidden_size, packed, scale_tiled);
+        hidden_packed, hidden_scale, route_prows, total, top_k, hidden_size, packed, scale_tiled,
+        src_scale_tiled);
     note_launch();
     return cudaGetLastError();
 }
