@@ -224,7 +224,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 template <bool GATED, int EPI>
 __global__ void __launch_bounds__(kAsThreads, 1)
 gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     const TcParams p, const uint32_t stages, const uint32_t nt_per_split)
+                     const __grid_constant__ CUtensorMap map_o, const TcParams p, const uint32_t stages,
+                     const uint32_t nt_per_split, const uint32_t kbs)
 {
     const uint32_t tile = blockIdx.y;
     int expert = 0, row0 = 0, nrows = 0;
@@ -251,7 +252,8 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     uint8_t* a_panel = smem;
     uint8_t* sfa_stage = a_panel + kb_count * kTileBytes;
     uint8_t* ring = sfa_stage + kb_count * kSfBytes;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + stages * kAsStageBytes);
+    uint8_t* staging = ring + stages * kbs * kAsStageBytes; // 32 KB output tile, only with p.tma_store
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + (p.tma_store ? 2 * kTileBytes : 0));
     uint64_t* empty_bar = full_bar + kAsMaxStages;
     uint64_t* acc_full = empty_bar + kAsMaxStages;
     uint64_t* acc_empty = acc_full + 2;
@@ -289,7 +291,8 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_sfa = tmem_base + 256;
     const uint32_t tmem_sfb = tmem_base + 384; // two 16-column buffers, alternating per stage
-    const uint32_t total_loads = (nt_end - nt_begin) * kb_count;
+    const uint32_t stage_bytes = kbs * kAsStageBytes;   // kbs k-blocks of B codes, then their scales
+    const uint32_t stages_per_tile = kb_count / kbs;
 
     if (warp == 8) {
         // ------------------------------------------------------------ producer --
@@ -301,93 +304,97 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             bulk_load(sfa_stage, p.sfa + (static_cast<uint64_t>(row0 >> 7) * p.kgroups) * 512,
                       kb_count * kSfBytes, panel_bar);
             // B tiles of every column tile of this CTA
-            uint32_t it = 0;
-            for (uint32_t nt = nt_begin; nt < nt_end; ++nt) {
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t nt = nt_begin; ok && nt < nt_end; ++nt) {
                 const int b_row = expert * static_cast<int>(p.b_rows) + static_cast<int>(nt * kFeat);
                 const uint8_t* sfb_src = p.sfb + static_cast<uint64_t>(expert) * p.sfb_group_stride
                     + (static_cast<uint64_t>(nt) * p.kgroups) * 512;
-                bool ok = true;
-                for (uint32_t kb = 0; kb < kb_count; ++kb, ++it) {
-                    const uint32_t s = it % stages;
-                    const uint32_t ph = (it / stages) & 1;
-                    if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_AS_EMPTY_WAIT)) {
+                for (uint32_t st = 0; st < stages_per_tile; ++st) {
+                    if (!mbar_wait<true>(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_AS_EMPTY_WAIT)) {
                         ok = false;
                         break;
                     }
-                    uint8_t* sb = ring + s * kAsStageBytes;
+                    uint8_t* sb = ring + s * stage_bytes;
                     if (p.debug & 1u) {
                         mbar_arrive(&full_bar[s]);
-                        continue;
-                    }
-                    mbar_expect_tx(&full_bar[s], kAsStageBytes);
-                    const int c0 = static_cast<int>(kb) * 128;
-                    if (GATED) {
-                        tma_load_2d(sb, &map_b, &full_bar[s], c0, b_row);
-                        tma_load_2d(sb + kTileBytes / 2, &map_b, &full_bar[s], c0, b_row + static_cast<int>(p.n));
                     } else {
-                        tma_load_2d(sb, &map_b, &full_bar[s], c0, b_row);
+                        mbar_expect_tx(&full_bar[s], stage_bytes);
+                        for (uint32_t q = 0; q < kbs; ++q) {
+                            const int c0 = static_cast<int>(st * kbs + q) * 128;
+                            uint8_t* dst = sb + q * kTileBytes;
+                            if (GATED) {
+                                tma_load_2d(dst, &map_b, &full_bar[s], c0, b_row);
+                                tma_load_2d(dst + kTileBytes / 2, &map_b, &full_bar[s], c0,
+                                            b_row + static_cast<int>(p.n));
+                            } else {
+                                tma_load_2d(dst, &map_b, &full_bar[s], c0, b_row);
+                            }
+                        }
+                        bulk_load(sb + kbs * kTileBytes, sfb_src + static_cast<uint64_t>(st * kbs) * kSfBytes,
+                                  kbs * kSfBytes, &full_bar[s]);
                     }
-                    bulk_load(sb + kTileBytes, sfb_src + static_cast<uint64_t>(kb) * kSfBytes, kSfBytes,
-                              &full_bar[s]);
+                    if (++s == stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
-                if (!ok)
-                    break;
             }
         }
     } else if (warp == 9) {
         // ---------------------------------------------------------- MMA issuer --
         if (lane == 0) {
             constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
-            bool ok = mbar_wait(panel_bar, 0, abort_flag, p.err, ERR_AS_PANEL_WAIT);
+            bool ok = mbar_wait<true>(panel_bar, 0, abort_flag, p.err, ERR_AS_PANEL_WAIT);
             if (ok) {
                 tc_fence_after();
                 // A scales: one 512-byte tile per 64 k elements -> 4 TMEM columns each
                 for (uint32_t g = 0; g < kb_count * 4; ++g)
                     tc_cp_scales(tmem_sfa + 4 * g, scale_desc(smem_u32(sfa_stage) + g * 512));
             }
-            uint32_t it = 0;
+            const uint32_t a_addr = smem_u32(a_panel);
+            uint32_t s = 0, ph = 0, sf_flip = 0;
             for (uint32_t nt = nt_begin; ok && nt < nt_end; ++nt) {
                 const uint32_t local = nt - nt_begin;
                 const uint32_t buf = local & 1;
                 const uint32_t use = local >> 1;
-                if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.err, ERR_AS_ACC_EMPTY_WAIT)) {
+                if (!mbar_wait<true>(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.err, ERR_AS_ACC_EMPTY_WAIT)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + buf * kBN;
-                for (uint32_t kb = 0; kb < kb_count; ++kb, ++it) {
-                    const uint32_t s = it % stages;
-                    const uint32_t ph = (it / stages) & 1;
-                    if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, ERR_AS_FULL_WAIT)) {
+                for (uint32_t st = 0; st < stages_per_tile; ++st) {
+                    if (!mbar_wait<true>(&full_bar[s], ph, abort_flag, p.err, ERR_AS_FULL_WAIT)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sb = smem_u32(ring + s * kAsStageBytes);
+                    const uint32_t sb = smem_u32(ring + s * stage_bytes);
                     if (!(p.debug & 2u)) {
+                        for (uint32_t q = 0; q < kbs; ++q) {
+                            const uint32_t kb = st * kbs + q;
+                            // B scales alternate between two TMEM buffers so that this copy does
+                            // not have to wait for the previous k-block's MMAs to finish reading
+                            const uint32_t sfb_cols = tmem_sfb + 16 * sf_flip;
+                            sf_flip ^= 1;
+                            const uint32_t sf_smem = sb + kbs * kTileBytes + q * kSfBytes;
 #pragma unroll
-                        // B scales alternate between two TMEM buffers so that this copy does
-                        // not have to wait for the previous stage's MMAs to finish reading
-                        const uint32_t sfb_cols = tmem_sfb + 16 * (it & 1);
-                        if (!(p.debug & 8u))
                             for (uint32_t j = 0; j < 4; ++j)
-                                tc_cp_scales(sfb_cols + 4 * j, scale_desc(sb + kTileBytes + j * 512));
-                        const uint64_t da = operand_desc(smem_u32(a_panel + kb * kTileBytes));
-                        const uint64_t db = operand_desc(sb);
+                                tc_cp_scales(sfb_cols + 4 * j, scale_desc(sf_smem + j * 512));
+                            const uint64_t da = operand_desc(a_addr + kb * kTileBytes);
+                            const uint64_t db = operand_desc(sb + q * kTileBytes);
 #pragma unroll
-                        for (uint32_t j = 0; j < 4; ++j) {
-                            if ((p.debug & 32u) && (j & 1))
-                                continue; // timing experiment: half the MMAs
-                            // timing experiment (debug 16): N = 256 instructions on the same operands
-                            const uint32_t idesc = (p.debug & 16u)
-                                ? ((1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((kBM >> 4) << 24))
-                                : kIdesc;
-                            tc_mma_nvfp4((p.debug & 16u) ? tmem_base : tmem_acc, da + 2 * j, db + 2 * j, idesc,
-                                         (kb > 0 || j > 0) ? 1u : 0u, tmem_sfa + 16 * kb + 4 * j, sfb_cols + 4 * j);
+                            for (uint32_t j = 0; j < 4; ++j)
+                                tc_mma_nvfp4(tmem_acc, da + 2 * j, db + 2 * j, kIdesc, (kb > 0 || j > 0) ? 1u : 0u,
+                                             tmem_sfa + 16 * kb + 4 * j, sfb_cols + 4 * j);
                         }
                     }
                     tc_commit(&empty_bar[s]);
+                    if (++s == stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
                 if (ok)
                     tc_commit(&acc_full[buf]);
@@ -404,6 +411,51 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             if (!ready)
                 break;
             tc_fence_after();
+            if (EPI == EPI_STORE_BF16 && p.tma_store) {
+                // bf16 tile -> shared memory (128-byte swizzled rows) -> one TMA store per
+                // 64-column half. Every row of the tile is written: rows past the segment
+                // end are padding rows of the same expert, rows past the tensor are clipped.
+                const uint32_t quad = warp & 3, half = warp >> 2;
+                const uint32_t r = quad * 32 + lane;
+                if (warp == 0 && lane == 0) // the previous tile's stores must have left smem
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                float scale = p.alpha == 0.0f ? 1.0f : p.alpha;
+                if (p.group_scale != nullptr)
+                    scale *= p.group_scale[expert];
+                uint8_t* row_smem = staging + half * kTileBytes + r * 128;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {
+                    uint32_t v[16];
+                    tc_ld16(tmem_base + buf * kBN + ((quad * 32) << 16) + half * 64 + c * 16, v);
+                    tc_ld_wait();
+                    uint32_t w[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        w[i] = pack_bf16x2(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
+                    *reinterpret_cast<uint4*>(row_smem + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(row_smem + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+                // accumulator is free again; publish the staged tile to the async proxy
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&acc_empty[buf]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (warp == 0 && lane == 0) {
+                    const int n0 = static_cast<int>(nt * kBN);
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        if (n0 + h2 * 64 < static_cast<int>(p.n))
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                             reinterpret_cast<uint64_t>(&map_o)),
+                                         "r"(smem_u32(staging + h2 * kTileBytes)), "r"(n0 + h2 * 64), "r"(row0)
+                                         : "memory");
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                continue;
+            }
             if (!(p.debug & 4u))
                 epilogue_tile<GATED, EPI, 2>(p, tmem_base + buf * kBN, warp & 3, lane, expert, row0, nrows, nt,
                                              warp >> 2);
@@ -413,8 +465,9 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             if (lane == 0)
                 mbar_arrive(&acc_empty[buf]);
         }
+        if (EPI == EPI_STORE_BF16 && p.tma_store && warp == 0 && lane == 0)
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // stores done before smem goes away
     }
-    (void)total_loads;
 
     tc_fence_before();
     __syncthreads();
@@ -552,14 +605,18 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
 }
 
 template <bool GATED, int EPI>
-cudaError_t launch_astat(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& tp, dim3 grid,
-                         uint32_t nt_per_split, cudaStream_t stream)
+cudaError_t launch_astat(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcParams& tp,
+                         dim3 grid, uint32_t nt_per_split, cudaStream_t stream)
 {
     constexpr size_t kSmemBudget = 227 * 1024 - 1024 /* alignment slack */ - 512 /* barriers */;
     const size_t panel = static_cast<size_t>(tp.k_blocks) * (kTileBytes + kSfBytes);
-    uint32_t stages = static_cast<uint32_t>((kSmemBudget - panel) / kAsStageBytes);
+    // two k-blocks per ring stage: one barrier round trip of the single issuing thread
+    // costs about as much as four 128x128x64 MMAs, so stages carry eight of them
+    const uint32_t kbs = tp.k_blocks % 2 == 0 ? 2u : 1u;
+    const size_t staging = tp.tma_store ? 2 * kTileBytes : 0;
+    uint32_t stages = static_cast<uint32_t>((kSmemBudget - panel - staging) / (kbs * kAsStageBytes));
     stages = std::min<uint32_t>(stages, kAsMaxStages);
-    const size_t smem = panel + static_cast<size_t>(stages) * kAsStageBytes + 1024 + 512;
+    const size_t smem = panel + staging + static_cast<size_t>(stages) * kbs * kAsStageBytes + 1024 + 512;
     auto kernel = gemm_tc_astat_kernel<GATED, EPI>;
     static bool configured[64] = {};
     int dev = 0;
@@ -573,7 +630,7 @@ cudaError_t launch_astat(const CUtensorMap& ma, const CUtensorMap& mb, const TcP
         if (dev >= 0 && dev < 64)
             configured[dev] = true;
     }
-    kernel<<<grid, kAsThreads, smem, stream>>>(ma, mb, tp, stages, nt_per_split);
+    kernel<<<grid, kAsThreads, smem, stream>>>(ma, mb, mo, tp, stages, nt_per_split, kbs);
     note_launch();
     return cudaGetLastError();
 }
@@ -694,9 +751,17 @@ cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** 
             const uint32_t splits = (n_tiles + nt_per - 1) / nt_per;
             dim3 agrid(splits, m_tiles, 1);
             if (g.gated && g.epilogue == EPI_SWIGLU_NVFP4)
-                return launch_astat<true, EPI_SWIGLU_NVFP4>(ma, mb, tp, agrid, nt_per, stream);
-            if (!g.gated && g.epilogue == EPI_STORE_BF16)
-                return launch_astat<false, EPI_STORE_BF16>(ma, mb, tp, agrid, nt_per, stream);
+                return launch_astat<true, EPI_SWIGLU_NVFP4>(ma, mb, ma, tp, agrid, nt_per, stream);
+            if (!g.gated && g.epilogue == EPI_STORE_BF16) {
+                // bf16 output through shared memory + TMA store when the output is a plain
+                // row-major matrix whose rows may all be written (no beta read-modify-write)
+                CUtensorMap mo = ma;
+                TcParams tpo = tp;
+                if (g.beta == 0.0f && aligned16(g.out) && (g.out_pitch_elems * 2) % 16 == 0
+                    && make_map(&mo, false, g.out, g.n, g.a_rows, g.out_pitch_elems * 2, kBM))
+                    tpo.tma_store = 1;
+                return launch_astat<false, EPI_STORE_BF16>(ma, mb, mo, tpo, agrid, nt_per, stream);
+            }
         }
         if (g.nvfp4) {
             if (g.gated && g.epilogue == EPI_SWIGLU_NVFP4)

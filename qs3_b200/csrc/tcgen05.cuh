@@ -45,7 +45,8 @@ struct TcParams {
     const float* bias;
     float out_global;
     uint32_t* err;
-    uint32_t debug; // timing experiments only (QS3_GEMM_DEBUG): 1 no loads, 2 no MMAs, 4 no epilogue
+    uint32_t tma_store; // resident-A kernel, bf16 output: stage the tile in smem and store it with TMA
+    uint32_t debug;     // timing experiments only (QS3_GEMM_DEBUG): 1 no loads, 2 no MMAs, 4 no epilogue // timing experiments only (QS3_GEMM_DEBUG): 1 no loads, 2 no MMAs, 4 no epilogue
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------
@@ -78,16 +79,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait; on expiry records `code` and raises the CTA's abort flag.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+
+// Bounded wait; on expiry records `code` and raises the CTA's abort flag. POLL selects
+// non-blocking test_wait polling (lowest wake-up latency; for the single producer and
+// MMA threads) instead of the suspending try_wait (for whole epilogue warps).
+template <bool POLL = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* err, uint32_t code)
 {
-    if (mbar_try_wait(bar, parity))
+    if (POLL ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity))
         return true;
     const uint64_t start = clock64();
+    uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity))
+        if (POLL ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity))
             return true;
+        if (POLL && (++spins & 63u) != 0)
+            continue;
         if (*abort_flag != 0)
             return false;
         if (static_cast<uint64_t>(clock64()) - start > kWaitCycles) {
