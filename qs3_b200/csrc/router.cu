@@ -133,6 +133,122 @@ router_topk_kernel(const LogitT* __restrict__ logits, const float* __restrict__ 
     }
 }
 
+// Order-preserving map float -> u32 for the values upstream's insertion accepts
+// (score >= -FLT_MAX, not NaN); everything else maps to 0 and never wins. -0 is folded
+// into +0 so that equal floats give equal keys.
+__device__ __forceinline__ uint32_t score_key(float s)
+{
+    if (!(s >= kRouterNegInf))
+        return 0u;
+    const uint32_t b = __float_as_uint(s + 0.0f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ float key_score(uint32_t k)
+{
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// Same routing as router_topk_kernel for num_experts <= 32 * ITEMS, with the token's
+// scores held in registers (lane owns experts lane, lane + 32, ...). A round is a
+// register arg-max per lane, one redux.sync max over the keys and one redux.sync min
+// over the candidate ids (ties go to the lowest id, as upstream's insertion does).
+template <typename LogitT, int ITEMS>
+__global__ void __launch_bounds__(kRouterWarps * 32)
+router_topk_reg_kernel(const LogitT* __restrict__ logits, const float* __restrict__ bias,
+                       int32_t* __restrict__ topk_ids, float* __restrict__ topk_weights,
+                       uint32_t num_tokens, uint32_t num_experts, uint32_t top_k, int sigmoid_score,
+                       int renormalize, float scaling)
+{
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t token = blockIdx.x * kRouterWarps + (threadIdx.x >> 5);
+    if (token >= num_tokens)
+        return;
+    const LogitT* row = logits + static_cast<size_t>(token) * num_experts;
+
+    float val[ITEMS];
+    uint32_t key[ITEMS];
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+        const uint32_t e = lane + 32u * j;
+        float l = __uint_as_float(0x7fc00000u); // padding: NaN, never selected, skipped below
+        if (e < num_experts) {
+            if constexpr (sizeof(LogitT) == 2)
+                l = __bfloat162float(row[e]);
+            else
+                l = row[e];
+            if (bias != nullptr)
+                l += bias[e];
+        }
+        val[j] = l;
+    }
+    uint32_t kmax = 0;
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+        key[j] = score_key(val[j]);
+        kmax = max(kmax, key[j]);
+    }
+    kmax = __reduce_max_sync(0xffffffffu, kmax);
+    const float vmax = kmax != 0u ? key_score(kmax) : kRouterNegInf;
+
+    float denom = 0.0f;
+    if (!sigmoid_score) {
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j)
+            if (lane + 32u * j < num_experts)
+                denom += expf(val[j] - vmax);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    } else {
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j)
+            key[j] = lane + 32u * j < num_experts ? score_key(sigmoid_fast(val[j])) : 0u;
+    }
+
+    float my_weight = 0.0f;
+    int my_id = 0;
+    for (uint32_t pos = 0; pos < top_k; ++pos) {
+        uint32_t best = 0;
+        int bj = 0;
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j)
+            if (key[j] > best) { // strict: the lowest id of equal keys stays
+                best = key[j];
+                bj = j;
+            }
+        const uint32_t top = __reduce_max_sync(0xffffffffu, best);
+        float w = 0.0f;
+        int id = static_cast<int>(pos); // unfilled slot (qscu.cu:945-949)
+        if (top != 0u) {
+            const uint32_t cand = best == top ? lane + 32u * static_cast<uint32_t>(bj) : 0xffffffffu;
+            const uint32_t win = __reduce_min_sync(0xffffffffu, cand);
+            id = static_cast<int>(win);
+            const float s = key_score(top);
+            w = sigmoid_score ? s : (denom > 0.0f ? expf(s - vmax) / denom : 0.0f);
+            if (cand == win) {
+#pragma unroll
+                for (int j = 0; j < ITEMS; ++j)
+                    if (j == bj)
+                        key[j] = 0u;
+            }
+        }
+        if (lane == pos) {
+            my_weight = w;
+            my_id = id;
+        }
+    }
+
+    float sum = 0.0f;
+    for (uint32_t pos = 0; pos < top_k; ++pos)
+        sum += __shfl_sync(0xffffffffu, my_weight, pos);
+    const float renorm = renormalize ? 1.0f / fmaxf(sum, 1.0e-20f) : 1.0f;
+    if (lane < top_k) {
+        topk_ids[static_cast<size_t>(token) * top_k + lane] = my_id;
+        topk_weights[static_cast<size_t>(token) * top_k + lane] = my_weight * renorm * scaling;
+    }
+}
+
 // out = bf16(silu(gate) * up); eight elements per thread when aligned.
 __global__ void silu_and_mul_kernel(const __nv_bfloat16* __restrict__ gate,
                                     const __nv_bfloat16* __restrict__ up,
@@ -214,6 +330,35 @@ cudaError_t launch_router_topk(const void* logits, int logits_bf16, const float*
 {
     const size_t smem = static_cast<size_t>(kRouterWarps) * num_experts * sizeof(float);
     const uint32_t blocks = (num_tokens + kRouterWarps - 1) / kRouterWarps;
+    if (num_experts <= 512) {
+        // register-resident variant: ITEMS = experts per lane, rounded up to a power of two
+        const uint32_t per_lane = (num_experts + 31) / 32;
+#define QS3_ROUTER_REG(T, N)                                                                        \
+    router_topk_reg_kernel<T, N><<<blocks, kRouterWarps * 32, 0, stream>>>(                         \
+        static_cast<const T*>(logits), bias, ids, weights, num_tokens, num_experts, top_k,          \
+        sigmoid_score, renormalize, scaling)
+#define QS3_ROUTER_REG_PICK(T)                                                                      \
+    do {                                                                                            \
+        if (per_lane <= 1)                                                                          \
+            QS3_ROUTER_REG(T, 1);                                                                   \
+        else if (per_lane <= 2)                                                                     \
+            QS3_ROUTER_REG(T, 2);                                                                   \
+        else if (per_lane <= 4)                                                                     \
+            QS3_ROUTER_REG(T, 4);                                                                   \
+        else if (per_lane <= 8)                                                                     \
+            QS3_ROUTER_REG(T, 8);                                                                   \
+        else                                                                                        \
+            QS3_ROUTER_REG(T, 16);                                                                  \
+    } while (0)
+        if (logits_bf16)
+            QS3_ROUTER_REG_PICK(__nv_bfloat16);
+        else
+            QS3_ROUTER_REG_PICK(float);
+#undef QS3_ROUTER_REG_PICK
+#undef QS3_ROUTER_REG
+        note_launch();
+        return cudaGetLastError();
+    }
     if (logits_bf16) {
         auto kernel = router_topk_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) {
