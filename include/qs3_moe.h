@@ -440,6 +440,7 @@ typedef struct {
     qsfi_tensor2 out;                  /* bf16 [num_tokens, hidden]: sum over the LOCAL routes */
     qsfi_tensor1 workspace;
     uint32_t num_tokens;
+    uint32_t flags; /* bit 0: leave `out` rows of tokens that have no local route unwritten */
 } qs3_moe_nvfp4_prepared_desc;
 qsfi_status qs3_moe_execute_nvfp4_prepared(
     qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_nvfp4_prepared_desc* desc
@@ -463,6 +464,17 @@ typedef struct {
     uint32_t num_tokens;
     uint32_t num_ranks;
     uint32_t phases; /* bit 0: shared expert (can run while the exchange is in flight); bit 1: sum + store */
+    /* Pull mode of phase 2 (peer_partials != NULL, `partials` unused): instead of summing
+     * exchanged copies, read every rank's partial-sum buffer [num_ranks * num_tokens, hidden]
+     * in place through peer-mapped pointers (HOST array of num_ranks device pointers, entry r
+     * = rank r's buffer as mapped on this device). Only (token, rank) pairs that have a route
+     * are read, decided from this rank's own topk_ids and the plan's expert block
+     * (rank r owns experts [r * local_num_experts, (r + 1) * local_num_experts)). The caller
+     * orders the launch after every rank finished writing its buffer (a barrier or any
+     * collective on the stream) and does not let a rank overwrite it before all ranks ran
+     * this phase. */
+    const qsfi_device_ptr* peer_partials;
+    qsfi_tensor2 topk_ids; /* i32 [num_tokens, top_k], pull mode only */
 } qs3_moe_ep_finish_desc;
 qsfi_status qs3_moe_ep_finish_workspace_size(
     qsfi_context* ctx, const qsfi_moe_plan* plan, uint32_t num_tokens, uint32_t num_ranks,

@@ -173,7 +173,7 @@ class MoeNvfp4PreparedDesc(C.Structure):
                 ("gate_up_global_scale", Tensor1), ("down_weight", Tensor3), ("down_scale_tiled", Tensor1),
                 ("down_global_scale", Tensor1), ("act_global_scale", C.c_float),
                 ("act2_global_scale", C.c_float), ("out", Tensor2), ("workspace", Tensor1),
-                ("num_tokens", C.c_uint32)]
+                ("num_tokens", C.c_uint32), ("flags", C.c_uint32)]
 
 
 class MoeEpFinishDesc(C.Structure):
@@ -183,7 +183,8 @@ class MoeEpFinishDesc(C.Structure):
                 ("shared_down_global_scale", Tensor1), ("shared_gate_weight", Tensor2),
                 ("shared_intermediate_size", C.c_uint32), ("act_global_scale", C.c_float),
                 ("act2_global_scale", C.c_float), ("out", Tensor2), ("workspace", Tensor1),
-                ("num_tokens", C.c_uint32), ("num_ranks", C.c_uint32), ("phases", C.c_uint32)]
+                ("num_tokens", C.c_uint32), ("num_ranks", C.c_uint32), ("phases", C.c_uint32),
+                ("peer_partials", C.POINTER(C.c_void_p)), ("topk_ids", Tensor2)]
 
 
 class RoutingView(C.Structure):

@@ -121,7 +121,19 @@ struct CombineParams {
     const __nv_bfloat16* hidden;     // [T, H] for the gate logit
     const __nv_bfloat16* gate_w;     // [H]
     int round_before_shared;         // 1: round the routed sum to bf16 first (upstream chain)
+    int skip_empty;                  // 1: leave rows of tokens without any local route unwritten
 };
+
+struct EpPullParams {
+    const __nv_bfloat16* peer[32];   // every rank's partial-sum buffer [num_ranks * T, H] (peer-mapped)
+    const int32_t* topk_ids;         // [T, K] this rank's routing (global expert ids)
+    __nv_bfloat16* out;              // [T, H]
+    const __nv_bfloat16* shared_out; // optional [T, H]
+    const __nv_bfloat16* hidden;     // [T, H]
+    const __nv_bfloat16* gate_w;     // [H]
+    uint32_t num_tokens, top_k, hidden_size, num_ranks, my_rank, experts_per_rank;
+};
+cudaError_t launch_ep_pull_combine(const EpPullParams& p, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
 cudaError_t launch_ep_rank_routes(int32_t* rows, float* weights, uint32_t tokens, uint32_t ranks,
                                   cudaStream_t stream);

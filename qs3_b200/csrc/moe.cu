@@ -1213,6 +1213,7 @@ qsfi_status qs3_moe_execute_nvfp4_prepared(qsfi_context* ctx, const qsfi_moe_pla
     cp.num_tokens = d->num_tokens;
     cp.top_k = p.top_k;
     cp.hidden_size = p.hidden_size;
+    cp.skip_empty = (d->flags & 1u) != 0;
     return set_cuda_error(ctx, launch_combine(cp, st), "qs3_moe_execute_nvfp4_prepared");
 }
 
@@ -1351,6 +1352,40 @@ qsfi_status qs3_moe_ep_finish(qsfi_context* ctx, const qsfi_moe_plan* plan, cons
         status = gemm_or_error(ctx, s2, "NVFP4 shared down GEMM");
         if (status != QSFI_STATUS_OK)
             return status;
+    }
+    if ((d->phases & 2u) != 0 && d->peer_partials != nullptr) {
+        // pull mode: read the ranks' partial sums in place through peer-mapped pointers
+        status = validate_tensor(ctx, d->out, "out", QSFI_DTYPE_BF16);
+        if (status == QSFI_STATUS_OK)
+            status = validate_tensor(ctx, d->topk_ids, "topk_ids", QSFI_DTYPE_I32);
+        if (status != QSFI_STATUS_OK)
+            return status;
+        if (!contiguous2(d->out) || d->out.shape[0] != t || d->out.shape[1] != h || !contiguous2(d->topk_ids)
+            || d->topk_ids.shape[0] != t || d->topk_ids.shape[1] != p.top_k)
+            return set_invalid_arg(ctx, "MoE token/top-k tensor shape mismatch");
+        if (static_cast<uint64_t>(p.local_num_experts) * d->num_ranks != p.num_experts
+            || p.local_expert_offset % p.local_num_experts != 0)
+            return set_invalid_arg(ctx, "pull combine needs equal contiguous expert blocks per rank");
+        EpPullParams pp {};
+        for (uint32_t r = 0; r < d->num_ranks; ++r) {
+            if (d->peer_partials[r] == nullptr || !aligned16(d->peer_partials[r]))
+                return set_invalid_arg(ctx, "peer_partials entries must be 16-byte aligned device pointers");
+            pp.peer[r] = static_cast<const __nv_bfloat16*>(d->peer_partials[r]);
+        }
+        pp.topk_ids = static_cast<const int32_t*>(d->topk_ids.data);
+        pp.out = static_cast<__nv_bfloat16*>(d->out.data);
+        if (shared) {
+            pp.shared_out = x.sh_out;
+            pp.hidden = hidden;
+            pp.gate_w = static_cast<const __nv_bfloat16*>(d->shared_gate_weight.data);
+        }
+        pp.num_tokens = d->num_tokens;
+        pp.top_k = p.top_k;
+        pp.hidden_size = p.hidden_size;
+        pp.num_ranks = d->num_ranks;
+        pp.my_rank = p.local_expert_offset / p.local_num_experts;
+        pp.experts_per_rank = p.local_num_experts;
+        return set_cuda_error(ctx, launch_ep_pull_combine(pp, st), "qs3_moe_ep_finish");
     }
     if ((d->phases & 2u) != 0) {
         status = validate_tensor(ctx, d->partials, "partials", QSFI_DTYPE_BF16);

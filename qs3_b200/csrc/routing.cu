@@ -268,6 +268,8 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p)
         my_row = p.route_prows[static_cast<size_t>(token) * p.top_k + lane];
         my_w = p.topk_weights[static_cast<size_t>(token) * p.top_k + lane];
     }
+    if (p.skip_empty && __all_sync(0xffffffffu, my_row < 0))
+        return; // no local route: the row stays unwritten and is never read
     const uint4* y2 = reinterpret_cast<const uint4*>(p.expert_out);
     uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
     // the trip count is warp-uniform: the shuffles below need every lane
@@ -336,7 +338,95 @@ template <typename T> T* carve(char* base, size_t& offset, size_t count)
     return p;
 }
 
+// Expert-parallel combine that PULLS: out[t] = bf16(sum over ranks r, ascending, of
+// f32(partial_r[my_rank * T + t]) + sigmoid(x . w_gate) * shared[t]), where partial_r is
+// rank r's partial-sum buffer read in place over NVLink (plain peer loads). A rank is
+// read only when one of the token's routes targets one of its experts, so pairs
+// (token, rank) without a route cost no traffic. Same summation order and roundings as
+// exchanging the partial sums first and then running combine_kernel on the copies.
+__global__ void __launch_bounds__(256) ep_pull_combine_kernel(EpPullParams p)
+{
+    const uint32_t token = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const uint32_t lane = threadIdx.x & 31;
+    if (token >= p.num_tokens)
+        return;
+    const uint32_t vec_per_row = p.hidden_size / 8;
+
+    // which ranks hold a partial sum for this token
+    uint32_t mine = 0;
+    if (lane < p.top_k) {
+        const int id = p.topk_ids[static_cast<size_t>(token) * p.top_k + lane];
+        if (id >= 0 && static_cast<uint32_t>(id) / p.experts_per_rank < p.num_ranks)
+            mine = 1u << (static_cast<uint32_t>(id) / p.experts_per_rank);
+    }
+    const uint32_t active = __reduce_or_sync(0xffffffffu, mine);
+
+    float gate = 0.0f;
+    if (p.shared_out != nullptr) {
+        const uint4* x = reinterpret_cast<const uint4*>(p.hidden) + static_cast<size_t>(token) * vec_per_row;
+        const uint4* w = reinterpret_cast<const uint4*>(p.gate_w);
+        float dot = 0.0f;
+        for (uint32_t i = lane; i < vec_per_row; i += 32) {
+            const uint4 xv = x[i], wv = w[i];
+            const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
+            const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                dot += bf16_bits_to_f32(xs[j] & 0xffffu) * bf16_bits_to_f32(ws[j] & 0xffffu);
+                dot += bf16_bits_to_f32(xs[j] >> 16) * bf16_bits_to_f32(ws[j] >> 16);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        gate = sigmoid_fast(dot);
+    }
+
+    const size_t row = static_cast<size_t>(p.my_rank) * p.num_tokens + token;
+    uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
+    for (uint32_t i = lane; i < vec_per_row; i += 32) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            acc[j] = 0.0f;
+        for (uint32_t r = 0; r < p.num_ranks; ++r) {
+            if (!((active >> r) & 1u))
+                continue;
+            const uint4 v = reinterpret_cast<const uint4*>(p.peer[r])[row * vec_per_row + i];
+            const uint32_t vs[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[2 * j] += bf16_bits_to_f32(vs[j] & 0xffffu);
+                acc[2 * j + 1] += bf16_bits_to_f32(vs[j] >> 16);
+            }
+        }
+        if (p.shared_out != nullptr) {
+            const uint4 s = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
+            const uint32_t ss[4] = { s.x, s.y, s.z, s.w };
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[2 * j] += gate * bf16_bits_to_f32(ss[j] & 0xffffu);
+                acc[2 * j + 1] += gate * bf16_bits_to_f32(ss[j] >> 16);
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 r2 = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+            o[j] = *reinterpret_cast<const uint32_t*>(&r2);
+        }
+        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 } // namespace
+
+cudaError_t launch_ep_pull_combine(const EpPullParams& p, cudaStream_t stream)
+{
+    ep_pull_combine_kernel<<<(p.num_tokens + 7) / 8, 256, 0, stream>>>(p);
+    note_launch();
+    return cudaGetLastError();
+}
 
 cudaError_t launch_ep_rank_routes(int32_t* rows, float* weights, uint32_t tokens, uint32_t ranks,
                                   cudaStream_t stream)

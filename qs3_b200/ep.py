@@ -11,7 +11,10 @@ Per layer and rank (T tokens per rank, n ranks):
                all-to-all and needs no host-side count exchange or synchronisation.
   3. experts   the rank's experts over all n*T tokens; routes to other ranks' experts are
                skipped (local_expert_offset), so row t holds the rank's partial sum
-  4. combine   all-to-all of the partial sums back to the token owners
+  4. combine   "pull": after a one-element all-reduce as barrier, the owner of a token reads
+               the partial sums straight out of the other ranks' buffers (symmetric memory,
+               plain peer loads over NVLink) and only for ranks the token has a route to;
+               "nccl": all-to-all of the partial sums back to the token owners
   5. finish    shared expert (issued while the exchanges run) + sum of the n partials in
                ascending rank order in f32 + sigmoid-gated shared term, one bf16 rounding
 
@@ -81,7 +84,7 @@ class CudaBackend:
         self.ctx.check(self.ctx._lib.qs3_moe_ep_route(self.ctx.handle, self.plan.handle, self.C.byref(d)))
         return self.packed, self.scale, self.ids, self.wts
 
-    def experts(self, packed, scale, ids, wts, out):
+    def experts(self, packed, scale, ids, wts, out, skip_empty=False):
         d = capi.MoeNvfp4PreparedDesc()
         dt = self.data
         d.hidden_packed = ops._desc(packed, 2)
@@ -98,11 +101,16 @@ class CudaBackend:
         d.out = ops._desc(out, 2)
         d.workspace = ops._desc(self.ws_experts, 1)
         d.num_tokens = packed.shape[0]
+        d.flags = 1 if skip_empty else 0
         self.ctx.check(self.ctx._lib.qs3_moe_execute_nvfp4_prepared(self.ctx.handle, self.plan.handle,
                                                                     self.C.byref(d)))
 
-    def _finish(self, hidden, partials, out, phases):
+    def _finish(self, hidden, partials, out, phases, peer_ptrs=None, ids=None):
         d = capi.MoeEpFinishDesc()
+        if peer_ptrs is not None:
+            self._peer_array = (self.C.c_void_p * len(peer_ptrs))(*peer_ptrs)
+            d.peer_partials = self._peer_array
+            d.topk_ids = ops._desc(ids, 2)
         sh = self.data.shared
         d.hidden = ops._desc(hidden, 2)
         d.partials = ops._desc(partials, 3)
@@ -128,11 +136,15 @@ class CudaBackend:
     def finish(self, hidden, partials, out):
         self._finish(hidden, partials, out, 2)
 
+    def finish_pull(self, hidden, peer_ptrs, ids, out):
+        """Phase 2 reading every rank's partial sums in place (peer-mapped pointers)."""
+        self._finish(hidden, None, out, 2, peer_ptrs=peer_ptrs, ids=ids)
+
 
 class ExpertParallelLayer:
     """Drives one layer across the ranks of the default process group."""
 
-    def __init__(self, ctx, data, rank: int, world: int, backend=None, group=None):
+    def __init__(self, ctx, data, rank: int, world: int, backend=None, group=None, combine="auto"):
         self.rank, self.world, self.group = rank, world, group
         self.data = data
         cfg = data.cfg
@@ -149,7 +161,26 @@ class ExpertParallelLayer:
         self.g_scale = torch.empty((n * t, h // 16), dtype=u8, device=dev)
         self.g_ids = torch.empty((n * t, k), dtype=i32, device=dev)
         self.g_wts = torch.empty((n * t, k), dtype=f32, device=dev)
-        self.partial = torch.empty((n * t, h), dtype=bf, device=dev)    # this rank's partial sums, all tokens
+        # this rank's partial sums for all n*T tokens. On GPUs it lives in symmetric memory so
+        # that the owners of the tokens can read it in place over NVLink ("pull" combine);
+        # when that cannot be set up the partial sums are exchanged with an NCCL all-to-all.
+        self.peer_ptrs = None
+        self.partial = None
+        if self.cuda and world > 1 and combine != "nccl":
+            try:
+                import torch.distributed._symmetric_memory as symm
+                self.partial = symm.empty((n * t, h), dtype=bf, device=dev)
+                hdl = symm.rendezvous(self.partial, dist.group.WORLD if group is None else group)
+                self.peer_ptrs = [int(ptr) for ptr in hdl.buffer_ptrs]
+                self._symm_handle = hdl
+            except Exception as exc:  # no peer mapping on this system: exchange copies instead
+                if combine == "pull":
+                    raise
+                self.partial, self.peer_ptrs, self.combine_note = None, None, f"nccl ({type(exc).__name__})"
+        if self.partial is None:
+            self.partial = torch.empty((n * t, h), dtype=bf, device=dev)
+        self.combine_mode = "pull" if self.peer_ptrs is not None else "nccl"
+        self.flag = torch.zeros(1, dtype=f32, device=dev) if self.cuda else None
         self.recv = torch.empty((n, t, h), dtype=bf, device=dev)        # partial sums of my tokens, per rank
         self.out = torch.empty((t, h), dtype=bf, device=dev)
         self.x_dev = torch.empty((t, h), dtype=bf, device=dev)
@@ -159,8 +190,15 @@ class ExpertParallelLayer:
 
     # -- collectives (NCCL on the communication stream; gloo in the CPU tests) --
     def _dispatch(self, packed, scale, ids, wts):
-        for dst, src in ((self.g_packed, packed), (self.g_scale, scale), (self.g_ids, ids), (self.g_wts, wts)):
-            dist.all_gather_into_tensor(dst, src, group=self.group)
+        pairs = ((self.g_packed, packed), (self.g_scale, scale), (self.g_ids, ids), (self.g_wts, wts))
+        if self.cuda:
+            # one NCCL group for the four gathers instead of four launches
+            with dist._coalescing_manager(group=self.group, device=packed.device, async_ops=False):
+                for dst, src in pairs:
+                    dist.all_gather_into_tensor(dst, src, group=self.group)
+        else:
+            for dst, src in pairs:
+                dist.all_gather_into_tensor(dst, src, group=self.group)
 
     def _combine(self):
         dist.all_to_all_single(self.recv.view(self.world * self.cfg.tokens, -1), self.partial, group=self.group)
@@ -184,14 +222,25 @@ class ExpertParallelLayer:
             self.ev[1].record(self.comm)
         b.shared_expert(hidden)              # overlaps the dispatch
         main.wait_event(self.ev[1])
-        b.experts(self.g_packed, self.g_scale, self.g_ids, self.g_wts, self.partial)
+        pull = self.combine_mode == "pull"
+        b.experts(self.g_packed, self.g_scale, self.g_ids, self.g_wts, self.partial, skip_empty=pull)
         self.ev[2].record(main)
         with torch.cuda.stream(self.comm):
             self.comm.wait_event(self.ev[2])
-            self._combine()
+            if pull:
+                # a one-element all-reduce as the cross-rank barrier: it completes here only
+                # after every rank's stream has passed its experts phase. The next step's
+                # dispatch all-gather is the barrier in the other direction (nobody overwrites
+                # a partial-sum buffer before all ranks finished reading it).
+                dist.all_reduce(self.flag, group=self.group)
+            else:
+                self._combine()
             self.ev[3].record(self.comm)
         main.wait_event(self.ev[3])
-        b.finish(hidden, self.recv, self.out)
+        if pull:
+            b.finish_pull(hidden, self.peer_ptrs, ids, self.out)
+        else:
+            b.finish(hidden, self.recv, self.out)
         return self.out
 
     def step_e2e(self, h_in, h_out):
@@ -215,11 +264,18 @@ class ExpertParallelLayer:
             ev[2].record()
             b.shared_expert(hidden)
             ev[3].record()
-            b.experts(self.g_packed, self.g_scale, self.g_ids, self.g_wts, self.partial)
+            pull = self.combine_mode == "pull"
+            b.experts(self.g_packed, self.g_scale, self.g_ids, self.g_wts, self.partial, skip_empty=pull)
             ev[4].record()
-            self._combine()
+            if pull:
+                dist.all_reduce(self.flag, group=self.group)
+            else:
+                self._combine()
             ev[5].record()
-            b.finish(hidden, self.recv, self.out)
+            if pull:
+                b.finish_pull(hidden, self.peer_ptrs, ids, self.out)
+            else:
+                b.finish(hidden, self.recv, self.out)
             ev[6].record()
             torch.cuda.synchronize()
             for i, name in enumerate(names):

@@ -48,7 +48,7 @@ def main():
     assert np.max(np.abs(f32(got) - want)) <= 2.0 ** -5 * np.max(np.abs(want))
     dist.barrier()
     if rank == 0:
-        print(f"EP_MULTI_OK world={world} rel_l2={err:.3e}")
+        print(f"EP_MULTI_OK world={world} rel_l2={err:.3e} combine={layer.combine_mode}")
     dist.destroy_process_group()
 
 

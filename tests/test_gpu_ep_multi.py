@@ -24,3 +24,4 @@ def test_expert_parallel_matches_single_gpu(world):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "EP_MULTI_OK" in r.stdout
+    print(r.stdout[-300:])
