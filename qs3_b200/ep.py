@@ -203,8 +203,9 @@ class ExpertParallelLayer:
     def _combine(self):
         dist.all_to_all_single(self.recv.view(self.world * self.cfg.tokens, -1), self.partial, group=self.group)
 
-    def step(self, hidden=None):
+    def step(self, hidden=None, out=None):
         hidden = self.data.hidden if hidden is None else hidden
+        out = self.out if out is None else out
         b = self.backend
         packed, scale, ids, wts = b.route(hidden)
         if not self.cuda:
@@ -212,8 +213,8 @@ class ExpertParallelLayer:
             b.shared_expert(hidden)
             b.experts(self.g_packed, self.g_scale, self.g_ids, self.g_wts, self.partial)
             self._combine()
-            b.finish(hidden, self.recv, self.out)
-            return self.out
+            b.finish(hidden, self.recv, out)
+            return out
         main = torch.cuda.current_stream()
         self.ev[0].record(main)
         with torch.cuda.stream(self.comm):
@@ -238,15 +239,10 @@ class ExpertParallelLayer:
             self.ev[3].record(self.comm)
         main.wait_event(self.ev[3])
         if pull:
-            b.finish_pull(hidden, self.peer_ptrs, ids, self.out)
+            b.finish_pull(hidden, self.peer_ptrs, ids, out)
         else:
-            b.finish(hidden, self.recv, self.out)
-        return self.out
-
-    def step_e2e(self, h_in, h_out):
-        self.x_dev.copy_(h_in, non_blocking=True)
-        self.step(self.x_dev)
-        h_out.copy_(self.out, non_blocking=True)
+            b.finish(hidden, self.recv, out)
+        return out
 
     # -- measurement helpers used by bench.py --
     def profile(self, iters):
