@@ -554,6 +554,14 @@ qsfi_status qs3_moe_profile_end(
     qsfi_context* ctx, int32_t* stage_ids, float* stage_ms, uint32_t capacity, uint32_t* count
 );
 
+/* Tensor-pipe ceiling of one tcgen05.mma shape on the context's device, no counterpart
+ * upstream: every SM issues `iters` x 4 back-to-back 128 x n MMAs (K = 32 bytes each) on
+ * operands resident in shared memory, timed with CUDA events on the context's stream.
+ * kind 0 = bf16 (kind::f16), 1 = fp8 e4m3 (kind::f8f6f4), 2 = NVFP4 block-scaled
+ * (kind::mxf4nvf4, scale_vec::4X). n is a multiple of 16 in [16, 256]. Returns dense
+ * TFLOP/s. Used as the denominator of the reported tensor-pipe fractions. */
+qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, uint32_t n, uint32_t iters, double* tflops);
+
 #ifdef __cplusplus
 }
 #endif

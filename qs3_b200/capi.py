@@ -248,6 +248,7 @@ _SIGNATURES = {
     "qs3_moe_profile_begin": (C.c_int, [C.c_void_p]),
     "qs3_moe_profile_end": (C.c_int, [C.c_void_p, _P(C.c_int32), _P(C.c_float), C.c_uint32,
                                       _P(C.c_uint32)]),
+    "qs3_tensor_peak_probe": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, _P(C.c_double)]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

@@ -1,0 +1,149 @@
+// Tensor-pipe peak probe: every SM issues back-to-back tcgen05.mma instructions on
+// operand tiles that already sit in shared memory (no loads inside the timed loop), so
+// the measured rate is the tensor-pipe ceiling of one instruction shape on this device.
+// It provides the FP4 / FP8 / BF16 denominators for the "fraction of tensor peak"
+// figures; it is not part of the MoE data path.
+#include "tcgen05.cuh"
+
+namespace qs3 {
+namespace {
+
+using namespace tc;
+
+enum ProbeKind { PROBE_BF16 = 0, PROBE_FP8 = 1, PROBE_NVFP4 = 2 };
+
+__device__ __forceinline__ void tc_mma_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
+                 "l"(a), "l"(b), "r"(idesc), "r"(acc)
+                 : "memory");
+}
+
+// One CTA per SM: A tile 128 rows x 128 bytes, B tile n rows x 128 bytes, 128-byte swizzle
+// layout (contents are pseudo-random bytes; the result is never read). Each iteration
+// issues the MMAs that consume one 128-byte k-block: 4 instructions of K = 32 bytes.
+__global__ void __launch_bounds__(128, 1)
+tensor_peak_kernel(int kind, uint32_t n, uint32_t iters, uint32_t* err)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* a_tile = smem;
+    uint8_t* b_tile = smem + kTileBytes;                 // up to 256 rows = 32 KB
+    uint8_t* sf_tile = b_tile + 2 * kTileBytes;          // 512 bytes of scale 1.0
+    uint64_t* done_bar = reinterpret_cast<uint64_t*>(sf_tile + 1024);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    uint32_t x = 0x9e3779b9u * (blockIdx.x + 1) + threadIdx.x;
+    for (uint32_t i = threadIdx.x; i < 3 * kTileBytes / 4; i += blockDim.x) {
+        x = x * 1664525u + 1013904223u;
+        // keep exponents small so that no format produces Inf/NaN in the accumulator
+        reinterpret_cast<uint32_t*>(smem)[i] = x & 0x37373737u;
+    }
+    for (uint32_t i = threadIdx.x; i < 512; i += blockDim.x)
+        sf_tile[i] = 0x38; // e4m3 1.0
+    if (threadIdx.x == 0) {
+        mbar_init(done_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (threadIdx.x == 0) {
+        const uint32_t nm = ((n >> 3) << 17) | ((kBM >> 4) << 24);
+        const uint32_t idesc = kind == PROBE_BF16 ? ((1u << 4) | (1u << 7) | (1u << 10) | nm)
+            : kind == PROBE_FP8                  ? ((1u << 4) | nm) // e4m3 x e4m3, f32 accumulate
+                                                 : ((1u << 7) | (1u << 10) | nm);
+        const uint64_t da = operand_desc(smem_u32(a_tile));
+        const uint64_t db = operand_desc(smem_u32(b_tile));
+        const uint32_t sfa = tmem_base + 256, sfb = tmem_base + 272;
+        if (kind == PROBE_NVFP4) {
+            for (uint32_t c = 0; c < 12; ++c) // scale 1.0 everywhere the MMAs may look
+                tc_cp_scales(sfa + 4 * c, scale_desc(smem_u32(sf_tile)));
+        }
+        for (uint32_t it = 0; it < iters; ++it) {
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                const uint32_t acc = (it | j) != 0 ? 1u : 0u;
+                if (kind == PROBE_BF16)
+                    tc_mma_bf16(tmem_base, da + 2 * j, db + 2 * j, idesc, acc);
+                else if (kind == PROBE_FP8)
+                    tc_mma_f8(tmem_base, da + 2 * j, db + 2 * j, idesc, acc);
+                else
+                    tc_mma_nvfp4(tmem_base, da + 2 * j, db + 2 * j, idesc, acc, sfa, sfb);
+            }
+        }
+        tc_commit(done_bar);
+        mbar_wait<true>(done_bar, 0, abort_flag, err, 0x53000001u);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
+                     : "memory");
+    }
+}
+
+} // namespace
+} // namespace qs3
+
+using namespace qs3;
+
+extern "C" qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, uint32_t n, uint32_t iters,
+                                             double* tflops)
+{
+    if (ctx == nullptr || tflops == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (kind > 2 || n < 16 || n > 256 || n % 16 != 0 || iters == 0 || iters > (1u << 22))
+        return set_invalid_arg(ctx, "peak probe: kind in {0,1,2}, n a multiple of 16 in [16, 256], iters in [1, 2^22]");
+    int dev = 0, sms = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err == cudaSuccess)
+        err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const size_t smem = 3 * kTileBytes + 1024 + 64 + 1024;
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(tensor_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(smem));
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (err == cudaSuccess)
+        err = cudaEventCreate(&e0);
+    if (err == cudaSuccess)
+        err = cudaEventCreate(&e1);
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "peak probe setup");
+    uint32_t* errw = device_error_word();
+    tensor_peak_kernel<<<sms, 128, smem, ctx->stream>>>(static_cast<int>(kind), n, 64, errw); // warm-up
+    cudaEventRecord(e0, ctx->stream);
+    tensor_peak_kernel<<<sms, 128, smem, ctx->stream>>>(static_cast<int>(kind), n, iters, errw);
+    cudaEventRecord(e1, ctx->stream);
+    note_launch(2);
+    err = cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    if (err == cudaSuccess)
+        err = cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "peak probe");
+    // K elements per instruction: 32 bytes of K -> 16 bf16, 32 fp8, 64 fp4
+    const double k_per_mma = kind == 0 ? 16.0 : kind == 1 ? 32.0 : 64.0;
+    const double flops = 2.0 * 128.0 * n * k_per_mma * 4.0 * iters * sms;
+    *tflops = flops / (static_cast<double>(ms) * 1e-3) / 1e12;
+    return QSFI_STATUS_OK;
+}

@@ -484,3 +484,14 @@ def profile_end(ctx: Context):
     n = C.c_uint32(0)
     ctx.check(ctx._lib.qs3_moe_profile_end(ctx.handle, ids, ms, cap, C.byref(n)))
     return [(STAGE_NAMES.get(ids[i], str(ids[i])), float(ms[i])) for i in range(n.value)]
+
+
+PEAK_KINDS = {"bf16": 0, "fp8": 1, "nvfp4": 2}
+
+
+def tensor_peak_probe(ctx: Context, kind: str = "nvfp4", n: int = 256, iters: int = 20000) -> float:
+    """Dense TFLOP/s of back-to-back ``tcgen05.mma`` (128 x n tiles, operands resident in
+    shared memory) on every SM: the tensor-pipe ceiling for one operand format."""
+    out = C.c_double(0.0)
+    ctx.check(ctx._lib.qs3_tensor_peak_probe(ctx.handle, PEAK_KINDS[kind], n, iters, C.byref(out)))
+    return float(out.value)

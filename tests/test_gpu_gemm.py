@@ -92,3 +92,14 @@ def test_validation_errors(gemm):
     with pytest.raises(ops.Qs3Error) as e:
         gemm.gemm_bf16(x.float(), w, torch.zeros((4, 8), dtype=torch.float32, device="cuda"))
     assert e.value.status == 1
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8", "nvfp4"])
+def test_tensor_peak_probe_runs(kind):
+    # the probe is a measurement aid: it must finish, report a plausible positive rate
+    # and leave the device error word clear (all its waits are bounded)
+    from qs3_b200 import ops
+    ctx = ops.Context()
+    tf = ops.tensor_peak_probe(ctx, kind, n=128, iters=2000)
+    assert 10.0 < tf < 40000.0
+    assert ctx.read_device_error() == 0
