@@ -349,6 +349,52 @@ typedef struct {
 } qs3_nvfp4_tile_scales_desc;
 qsfi_status qs3_nvfp4_tile_scales(qsfi_context* ctx, const qs3_nvfp4_tile_scales_desc* desc);
 
+/* ---- FP8 block-scaled experts (no upstream counterpart: upstream declares only the
+ * dtype values QSFI_DTYPE_FP8_E4M3 / _E5M2, qs_tensor.h:20-24, and no FP8 MoE entry) ----
+ * Weights: e4m3 codes [experts, rows, k] with one f32 scale per 128 x 128 block,
+ * scale tensor f32 [experts, ceil(rows / 128), k / 128]. Activations: e4m3 codes
+ * [tokens, k] with one f32 scale per token per 128 elements, f32 [tokens, k / 128].
+ *   scale = max(amax / 448, 1e-30),  code = e4m3_rn_sat(x * (1 / scale)).
+ * A plan for this path has backend = QS3_MOE_BACKEND_FP8_BLOCKSCALE, activation and
+ * weight dtype QSFI_DTYPE_FP8_E4M3, output dtype bf16; hidden_size and
+ * intermediate_size must be multiples of 128 and at most 4096. */
+#define QS3_MOE_BACKEND_FP8_BLOCKSCALE 100
+
+typedef struct {
+    qsfi_tensor3 weight; /* bf16 [experts, rows, k], contiguous */
+    qsfi_tensor3 codes;  /* e4m3 [experts, rows, k] out */
+    qsfi_tensor3 scale;  /* f32 [experts, ceil(rows / 128), k / 128] out */
+} qs3_fp8_quantize_weight_desc;
+qsfi_status qs3_fp8_quantize_weight(qsfi_context* ctx, const qs3_fp8_quantize_weight_desc* desc);
+
+typedef struct {
+    qsfi_tensor2 x;     /* bf16 [rows, k] */
+    qsfi_tensor2 codes; /* e4m3 [rows, k] out */
+    qsfi_tensor2 scale; /* f32 [rows, k / 128] out */
+    uint32_t rows;
+} qs3_fp8_quantize_act_desc;
+qsfi_status qs3_fp8_quantize_act(qsfi_context* ctx, const qs3_fp8_quantize_act_desc* desc);
+
+/* Routed experts on FP8 operands with precomputed routing: the FP8 sibling of
+ * qsfi_moe_execute_nvfp4 (same roles of the tensors, same workspace query
+ * qsfi_moe_workspace_size). SwiGLU output is re-quantised per token per 128
+ * features before the down projection. */
+typedef struct {
+    qsfi_tensor2 hidden;               /* e4m3 [num_tokens, hidden] */
+    qsfi_tensor2 hidden_scale;         /* f32 [num_tokens, hidden / 128] */
+    qsfi_tensor2 topk_ids;             /* i32 [num_tokens, top_k] */
+    qsfi_tensor2 topk_weights;         /* f32 [num_tokens, top_k] */
+    qsfi_tensor3 gate_up_weight;       /* e4m3 [E_local, 2I, H] */
+    qsfi_tensor3 gate_up_weight_scale; /* f32 [E_local, 2I / 128, H / 128] */
+    qsfi_tensor3 down_weight;          /* e4m3 [E_local, H, I] */
+    qsfi_tensor3 down_weight_scale;    /* f32 [E_local, H / 128, I / 128] */
+    qsfi_tensor2 out;                  /* bf16 [num_tokens, hidden] */
+    qsfi_tensor1 workspace;            /* u8 [>= qsfi_moe_workspace_size] */
+    uint32_t num_tokens;
+} qsfi_moe_fp8_execute_desc;
+qsfi_status
+qsfi_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, const qsfi_moe_fp8_execute_desc* desc);
+
 /* Whole MoE layer in one call: what upstream's execute_moe_mlp issues as five
  * GEMM calls, a router call, a MoE call and two element-wise calls
  * (src/model.rs:2072-2228), i.e. the QSFI_MOE_ROUTE_ROUTER_LOGITS mode upstream
@@ -358,12 +404,16 @@ typedef struct {
     qsfi_tensor2 hidden;        /* bf16 [num_tokens, hidden] */
     qsfi_tensor2 router_weight; /* bf16 [num_experts, hidden] */
     qsfi_tensor1 router_bias;   /* optional f32 [num_experts], added to the logits before top-k */
-    /* routed experts: bf16 plan -> *_weight bf16; NVFP4 plan -> packed + tiled scales */
+    /* routed experts: bf16 plan -> *_weight bf16; NVFP4 plan -> packed + tiled scales;
+       FP8 plan -> e4m3 codes [E_local, 2I, H] / [E_local, H, I], and the *_scale_tiled
+       fields carry the f32 block scales as flat f32 tensors
+       ([E_local * (2I / 128) * (H / 128)] and [E_local * (H / 128) * (I / 128)]);
+       FP8 plans take no shared expert */
     qsfi_tensor3 gate_up_weight;       /* bf16 [E_local, 2I, H] or u8 [E_local, 2I, H/2] */
-    qsfi_tensor1 gate_up_scale_tiled;  /* NVFP4 only */
+    qsfi_tensor1 gate_up_scale_tiled;  /* NVFP4 / FP8 only */
     qsfi_tensor1 gate_up_global_scale; /* NVFP4 only, f32 [E_local] */
     qsfi_tensor3 down_weight;          /* bf16 [E_local, H, I] or u8 [E_local, H, I/2] */
-    qsfi_tensor1 down_scale_tiled;     /* NVFP4 only */
+    qsfi_tensor1 down_scale_tiled;     /* NVFP4 / FP8 only */
     qsfi_tensor1 down_global_scale;    /* NVFP4 only, f32 [E_local] */
     /* optional shared expert (data == NULL on shared_gate_up_weight: none); same dtype family */
     qsfi_tensor3 shared_gate_up_weight;       /* [1, 2*Is, H] (or packed) */

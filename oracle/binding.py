@@ -277,3 +277,55 @@ def moe_nvfp4(hidden_packed, hidden_scale, ids, weights, gu, d, *, act_global=1.
                          _p(sd[2]), C.c_int64(s_inter), _p(hb), _p(gate_w), _p(tl), C.c_int64(n),
                          _p(out))
     return out
+
+
+def fp8_quantize_act(x):
+    """bf16 [rows, k] -> (e4m3 codes u8 [rows, k], f32 scales [rows, k/128])."""
+    x = _c(x, np.uint16)
+    rows, k = x.shape
+    assert k % 128 == 0
+    codes = np.empty((rows, k), np.uint8)
+    scale = np.empty((rows, k // 128), np.float32)
+    lib().qs3o_fp8_quantize_act(_p(x), C.c_int64(rows), C.c_int64(k), _p(codes), _p(scale))
+    return codes, scale
+
+
+def fp8_quantize_weight(w):
+    """bf16 [experts, rows, k] -> (e4m3 codes, f32 scales [experts, ceil(rows/128), k/128])."""
+    w = _c(w, np.uint16)
+    e, rows, k = w.shape
+    assert k % 128 == 0
+    codes = np.empty((e, rows, k), np.uint8)
+    scale = np.empty((e, (rows + 127) // 128, k // 128), np.float32)
+    lib().qs3o_fp8_quantize_weight(_p(w), C.c_int64(e), C.c_int64(rows), C.c_int64(k), _p(codes), _p(scale))
+    return codes, scale
+
+
+def fp8_dequantize(codes, scale):
+    """float32 values of e4m3 codes [..., rows, k] with [..., ceil(rows/128) or rows, k/128] scales."""
+    codes = np.asarray(codes, np.uint8)
+    vals = e4m3_to_f32(codes)
+    s = np.repeat(np.asarray(scale, np.float32), 128, axis=-1)
+    if s.shape[-2] != codes.shape[-2]:
+        s = np.repeat(s, 128, axis=-2)[..., : codes.shape[-2], :]
+    return (vals * s).astype(np.float32)
+
+
+def moe_fp8(hidden_codes, hidden_scale, ids, weights, gu, d, *, local_offset=0, token_list=None):
+    """``gu`` / ``d`` are (codes, scale) pairs of the expert weights."""
+    hc = _c(hidden_codes, np.uint8)
+    hs = _c(hidden_scale, np.float32)
+    ids = _c(ids, np.int32)
+    weights = _c(weights, np.float32)
+    guc, gus = _c(gu[0], np.uint8), _c(gu[1], np.float32)
+    dc, ds = _c(d[0], np.uint8), _c(d[1], np.float32)
+    t, h = hc.shape
+    e, two_i, _ = guc.shape
+    k = ids.shape[1]
+    tl = _c(token_list, np.int32)
+    n = t if tl is None else tl.size
+    out = np.empty((n, h), np.uint16)
+    lib().qs3o_moe_fp8(_p(hc), _p(hs), _p(ids), _p(weights), _p(guc), _p(gus), _p(dc), _p(ds),
+                       C.c_int64(t), C.c_int64(h), C.c_int64(two_i // 2), C.c_int64(k),
+                       C.c_int64(local_offset), C.c_int64(e), _p(tl), C.c_int64(n), _p(out))
+    return out

@@ -656,3 +656,144 @@ QS3O_API void qs3o_moe_nvfp4(
         }
     }
 }
+
+// ---- FP8 block-scaled path (this repository's convention; upstream has no FP8 MoE
+// surface at all, only the dtype enum values in qs_tensor.h:20-24, so parity is
+// unpinned here as well) --------------------------------------------------------------
+//   activations: e4m3 codes, one f32 scale per token per 128 consecutive elements
+//   weights:     e4m3 codes, one f32 scale per 128 x 128 block (rows x k)
+//   scale = max(amax / 448, 1e-30);  code = e4m3_rn_sat(x * (1 / scale))
+
+namespace {
+
+inline float fp8_scale(float amax)
+{
+    return std::max(amax / 448.0f, 1.0e-30f);
+}
+
+void fp8_quantize_group(const float* x, int64_t n, uint8_t* codes, float* scale)
+{
+    float amax = 0.0f;
+    for (int64_t i = 0; i < n; ++i)
+        amax = std::max(amax, std::fabs(x[i]));
+    const float s = fp8_scale(amax);
+    const float inv = 1.0f / s;
+    for (int64_t i = 0; i < n; ++i)
+        codes[i] = f32_to_e4m3(x[i] * inv);
+    *scale = s;
+}
+
+// y[j] = sum_kb (a_scale[kb] * w_scale[j / 128][kb]) * sum_{k in kb} a[k] * w[j][k]
+// for rows j of one expert matrix [rows, k]; the inner sums are exact (double).
+void fp8_matvec(const uint8_t* a, const float* a_scale, const uint8_t* w, const float* w_scale,
+                int64_t rows, int64_t k, const float* lut, float* y)
+{
+    const int64_t kb_n = k / 128;
+    for (int64_t j = 0; j < rows; ++j) {
+        const uint8_t* wr = w + j * k;
+        const float* ws = w_scale + (j / 128) * kb_n;
+        float acc = 0.0f;
+        for (int64_t kb = 0; kb < kb_n; ++kb) {
+            double part = 0.0;
+            for (int64_t i = kb * 128; i < (kb + 1) * 128; ++i)
+                part += static_cast<double>(lut[a[i]]) * static_cast<double>(lut[wr[i]]);
+            acc += static_cast<float>(part) * (ws[kb] * a_scale[kb]);
+        }
+        y[j] = acc;
+    }
+}
+
+} // namespace
+
+// codes u8 [rows, k], scales f32 [rows, k / 128]; k % 128 == 0.
+QS3O_API void
+qs3o_fp8_quantize_act(const uint16_t* x, int64_t rows, int64_t k, uint8_t* codes, float* scales)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        float v[128];
+        for (int64_t g = 0; g < k / 128; ++g) {
+            for (int64_t i = 0; i < 128; ++i)
+                v[i] = bf16_to_f32(x[r * k + g * 128 + i]);
+            fp8_quantize_group(v, 128, codes + r * k + g * 128, scales + r * (k / 128) + g);
+        }
+    }
+}
+
+// codes u8 [experts, rows, k], scales f32 [experts, ceil(rows / 128), k / 128].
+QS3O_API void qs3o_fp8_quantize_weight(
+    const uint16_t* w, int64_t experts, int64_t rows, int64_t k, uint8_t* codes, float* scales
+)
+{
+    const int64_t rb_n = (rows + 127) / 128, kb_n = k / 128;
+#pragma omp parallel for schedule(static) collapse(2)
+    for (int64_t e = 0; e < experts; ++e) {
+        for (int64_t rb = 0; rb < rb_n; ++rb) {
+            const int64_t r1 = std::min(rows, (rb + 1) * 128);
+            for (int64_t kb = 0; kb < kb_n; ++kb) {
+                float amax = 0.0f;
+                for (int64_t r = rb * 128; r < r1; ++r)
+                    for (int64_t i = kb * 128; i < (kb + 1) * 128; ++i)
+                        amax = std::max(amax, std::fabs(bf16_to_f32(w[(e * rows + r) * k + i])));
+                const float s = fp8_scale(amax);
+                const float inv = 1.0f / s;
+                for (int64_t r = rb * 128; r < r1; ++r)
+                    for (int64_t i = kb * 128; i < (kb + 1) * 128; ++i)
+                        codes[(e * rows + r) * k + i]
+                            = f32_to_e4m3(bf16_to_f32(w[(e * rows + r) * k + i]) * inv);
+                scales[(e * rb_n + rb) * kb_n + kb] = s;
+            }
+        }
+    }
+}
+
+// Routed experts on FP8 operands, this repository's chain:
+//   Y1 = blockscaled(xq . Wgu_q)            f32, no bf16 rounding
+//   act = g * sigmoid(g) * u                f32
+//   aq = quantise(act) per token per 128 features
+//   Y2 = bf16(blockscaled(aq . Wd_q))
+//   out[t] = bf16(sum_k w[t,k] * f32(Y2))
+QS3O_API void qs3o_moe_fp8(
+    const uint8_t* hidden_codes, const float* hidden_scale, const int32_t* ids, const float* weights,
+    const uint8_t* gu_codes, const float* gu_scale, const uint8_t* d_codes, const float* d_scale,
+    int64_t num_tokens, int64_t hidden_size, int64_t inter, int64_t top_k, int64_t local_offset,
+    int64_t local_experts, const int32_t* token_list, int64_t n_list, uint16_t* out
+)
+{
+    float lut[256];
+    for (int c = 0; c < 256; ++c)
+        lut[c] = e4m3_to_f32(static_cast<uint8_t>(c));
+    const int64_t n = token_list ? n_list : num_tokens;
+    const int64_t hb = hidden_size / 128, ib = inter / 128, gub = (2 * inter + 127) / 128;
+#pragma omp parallel
+    {
+        std::vector<float> y1(2 * inter), act(inter), as(ib), y2(hidden_size), acc(hidden_size);
+        std::vector<uint8_t> aq(inter);
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t li = 0; li < n; ++li) {
+            const int64_t t = token_list ? token_list[li] : li;
+            std::fill(acc.begin(), acc.end(), 0.0f);
+            for (int64_t k = 0; k < top_k; ++k) {
+                const int64_t local = static_cast<int64_t>(ids[t * top_k + k]) - local_offset;
+                if (local < 0 || local >= local_experts)
+                    continue;
+                fp8_matvec(hidden_codes + t * hidden_size, hidden_scale + t * hb,
+                           gu_codes + local * 2 * inter * hidden_size, gu_scale + local * gub * hb,
+                           2 * inter, hidden_size, lut, y1.data());
+                for (int64_t i = 0; i < inter; ++i) {
+                    const float g = y1[i];
+                    act[i] = g * (1.0f / (1.0f + std::exp(-g))) * y1[inter + i];
+                }
+                for (int64_t g = 0; g < ib; ++g)
+                    fp8_quantize_group(act.data() + g * 128, 128, aq.data() + g * 128, as.data() + g);
+                fp8_matvec(aq.data(), as.data(), d_codes + local * hidden_size * inter,
+                           d_scale + local * hb * ib, hidden_size, inter, lut, y2.data());
+                const float wgt = weights[t * top_k + k];
+                for (int64_t h = 0; h < hidden_size; ++h)
+                    acc[h] += wgt * round_bf16(y2[h]);
+            }
+            for (int64_t h = 0; h < hidden_size; ++h)
+                out[li * hidden_size + h] = f32_to_bf16(acc[h]);
+        }
+    }
+}

@@ -42,6 +42,7 @@ DTYPE_U8 = 12
 MOE_BACKEND_STAGED_BF16 = 1
 MOE_BACKEND_FUSED_BF16 = 2
 MOE_BACKEND_NVFP4 = 3
+MOE_BACKEND_FP8_BLOCKSCALE = 100  # QS3_MOE_BACKEND_FP8_BLOCKSCALE
 MOE_ROUTE_PRECOMPUTED_TOPK = 0
 MOE_ROUTE_ROUTER_LOGITS = 1
 ROUTER_SCORE_SOFTMAX = 0
@@ -205,6 +206,21 @@ class RouteSortStaticDesc(C.Structure):
 
 # Every symbol include/qs3_moe.h declares: (restype, argtypes)
 _P = C.POINTER
+class Fp8QuantizeWeightDesc(C.Structure):
+    _fields_ = [("weight", Tensor3), ("codes", Tensor3), ("scale", Tensor3)]
+
+
+class Fp8QuantizeActDesc(C.Structure):
+    _fields_ = [("x", Tensor2), ("codes", Tensor2), ("scale", Tensor2), ("rows", C.c_uint32)]
+
+
+class MoeFp8ExecuteDesc(C.Structure):
+    _fields_ = [("hidden", Tensor2), ("hidden_scale", Tensor2), ("topk_ids", Tensor2),
+                ("topk_weights", Tensor2), ("gate_up_weight", Tensor3), ("gate_up_weight_scale", Tensor3),
+                ("down_weight", Tensor3), ("down_weight_scale", Tensor3), ("out", Tensor2),
+                ("workspace", Tensor1), ("num_tokens", C.c_uint32)]
+
+
 _SIGNATURES = {
     "qsfi_status_string": (C.c_char_p, [C.c_int]),
     "qsfi_context_create": (C.c_int, [_P(ContextDesc), _P(C.c_void_p)]),
@@ -248,6 +264,9 @@ _SIGNATURES = {
     "qs3_moe_profile_begin": (C.c_int, [C.c_void_p]),
     "qs3_moe_profile_end": (C.c_int, [C.c_void_p, _P(C.c_int32), _P(C.c_float), C.c_uint32,
                                       _P(C.c_uint32)]),
+    "qs3_fp8_quantize_weight": (C.c_int, [C.c_void_p, _P(Fp8QuantizeWeightDesc)]),
+    "qs3_fp8_quantize_act": (C.c_int, [C.c_void_p, _P(Fp8QuantizeActDesc)]),
+    "qsfi_moe_execute_fp8": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeFp8ExecuteDesc)]),
     "qs3_tensor_peak_probe": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, _P(C.c_double)]),
 }
 

@@ -74,7 +74,7 @@ template <typename T> bool contiguous3(const T& t)
 struct RouteTables {
     int32_t* counts;       // [E] routes per local expert
     int32_t* indptr;       // [E+1] exclusive scan of counts
-    int32_t* pad_indptr;   // [E+1] exclusive scan of counts rounded up to kTileM
+    int32_t* pad_indptr;   // [E+1] exclusive scan of counts rounded up to tile_rows
     int32_t* route_rows;   // [R] dense row of a route (-1: expert not local)
     int32_t* route_prows;  // [R] row in the padded layout (-1: expert not local)
     int32_t* row_tokens;   // [R] token of a dense row
@@ -87,11 +87,13 @@ struct RouteTables {
     uint32_t max_tiles;
     uint32_t max_pad_rows;
     uint32_t route_blocks;
+    uint32_t tile_rows;    // rows of one tile: expert segments are padded to a multiple of it
 };
 
 size_t route_tables_bytes(uint32_t routes, uint32_t experts);
 // Carves the tables out of `base` (may be NULL for sizing); returns bytes used.
-size_t route_tables_carve(char* base, uint32_t routes, uint32_t experts, RouteTables* out);
+size_t route_tables_carve(char* base, uint32_t routes, uint32_t experts, RouteTables* out,
+                          uint32_t tile_rows = kTileM);
 // Counting sort of the routes by local expert, stable in route index.
 cudaError_t launch_route_sort(const int32_t* topk_ids, const float* topk_weights, uint32_t routes,
                               uint32_t top_k, uint32_t local_offset, uint32_t experts,
@@ -109,6 +111,10 @@ qsfi_status validate_router_desc(const qscu_router_topk_desc* d);
 cudaError_t launch_gather_bf16(const __nv_bfloat16* hidden, const int32_t* route_prows,
                                uint32_t routes, uint32_t top_k, uint32_t hidden_size,
                                __nv_bfloat16* expanded, cudaStream_t stream);
+
+// dst[prow(route), :] = src[route / top_k, :] for rows of row_bytes (a multiple of 4) bytes.
+cudaError_t launch_gather_rows(const void* src, uint32_t row_bytes, const int32_t* route_prows, uint32_t routes,
+                               uint32_t top_k, void* dst, cudaStream_t stream);
 
 struct CombineParams {
     const int32_t* route_prows;   // [T*K]
@@ -193,6 +199,35 @@ cudaError_t launch_nvfp4_gather_packed(const uint8_t* hidden_packed, const uint8
                                        const int32_t* route_prows, uint32_t routes, uint32_t top_k,
                                        uint32_t hidden_size, uint8_t* packed, uint8_t* scale_tiled,
                                        cudaStream_t stream, int src_scale_tiled = 0);
+
+// ---- FP8 (e4m3, 128 x 128 weight blocks, per-token 128-element activation groups) ----
+// Rows of one token tile of the FP8 grouped GEMM for this many routes over this many experts.
+uint32_t fp8_tile_rows(uint32_t routes, uint32_t experts);
+// codes[prow] / scales[prow] = quantise(x[route / top_k]); route_prows NULL: dense, prow = route.
+cudaError_t launch_fp8_gather_quantize(const __nv_bfloat16* x, const int32_t* route_prows, uint32_t routes,
+                                       uint32_t top_k, uint32_t k, uint8_t* codes, float* scales,
+                                       cudaStream_t stream);
+cudaError_t launch_fp8_quantize_weight(const __nv_bfloat16* w, uint32_t experts, uint32_t rows, uint32_t k,
+                                       uint8_t* codes, float* scales, cudaStream_t stream);
+struct Fp8Gemm {
+    const uint8_t* x;        // e4m3 [x_rows, k], rows in the padded (tile_rows) layout
+    const float* x_scale;    // [x_rows, k / 128]
+    uint64_t x_rows;
+    const uint8_t* w;        // e4m3 [groups, gated ? 2n : n, k]
+    const float* w_scale;    // [groups, ceil(rows / 128), k / 128]
+    uint32_t groups, n, k;
+    int gated;               // 1: out = quantise(silu(gate) * up) as e4m3 [x_rows, n] + out_scale
+    const int32_t* tile_expert;
+    const int32_t* tile_row0;
+    const int32_t* tile_nrows;
+    const int32_t* total_tiles;
+    uint32_t max_tiles;
+    uint32_t est_tiles;      // host-side estimate of *total_tiles, sizes the feature splits
+    uint32_t tile_rows;      // 16 or 32
+    void* out;               // gated: u8 [x_rows, n]; else bf16 [x_rows, n]
+    float* out_scale;        // gated: f32 [x_rows, n / 128]
+};
+cudaError_t launch_fp8_gemm(const Fp8Gemm& g, cudaStream_t stream, const char** why_unsupported);
 
 // ---- device helpers ---------------------------------------------------------------
 #ifdef __CUDACC__

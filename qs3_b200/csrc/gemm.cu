@@ -216,11 +216,6 @@ enum : uint32_t {
     ERR_AS_ACC_EMPTY_WAIT = 0x52000005u,
 };
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 template <bool GATED, int EPI>
 __global__ void __launch_bounds__(kAsThreads, 1)
 gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -695,6 +690,14 @@ TcParams make_params(const GemmProblem& g)
 }
 
 } // namespace
+
+bool make_operand_map(CUtensorMap* map, bool bytes_type, const void* base, uint64_t inner_elems, uint64_t rows,
+                      uint64_t pitch_bytes, uint32_t box_rows)
+{
+    return make_map(map, bytes_type, base, inner_elems, rows, pitch_bytes, box_rows);
+}
+
+uint32_t device_sm_count() { return sm_count(); }
 
 bool gemm_tc_supported(const GemmProblem& g)
 {

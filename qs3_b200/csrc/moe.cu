@@ -121,6 +121,38 @@ Nvfp4Workspace carve_nvfp4(char* base, const qsfi_moe_plan_desc& d, uint32_t num
     return w;
 }
 
+bool is_fp8_plan(const qsfi_moe_plan_desc& d)
+{
+    return static_cast<int>(d.backend) == QS3_MOE_BACKEND_FP8_BLOCKSCALE;
+}
+
+struct Fp8Workspace {
+    RouteTables rt;    // token tiles of fp8_tile_rows rows
+    uint8_t* xq;       // [pad_rows, H] e4m3
+    float* xq_s;       // [pad_rows, H/128]
+    uint8_t* act;      // [pad_rows, I] e4m3
+    float* act_s;      // [pad_rows, I/128]
+    __nv_bfloat16* y2; // [pad_rows, H]
+    size_t bytes;
+};
+
+Fp8Workspace carve_fp8(char* base, const qsfi_moe_plan_desc& d, uint32_t num_tokens)
+{
+    Fp8Workspace w {};
+    const uint32_t routes = num_tokens * d.top_k;
+    size_t off = route_tables_carve(base, routes, d.local_num_experts, &w.rt,
+                                    fp8_tile_rows(routes, d.local_num_experts));
+    const size_t rows = w.rt.max_pad_rows;
+    const size_t h = d.hidden_size, i = d.intermediate_size;
+    w.xq = carve<uint8_t>(base, off, rows * h);
+    w.xq_s = carve<float>(base, off, rows * (h / 128));
+    w.act = carve<uint8_t>(base, off, rows * i);
+    w.act_s = carve<float>(base, off, rows * (i / 128));
+    w.y2 = carve<__nv_bfloat16>(base, off, rows * h);
+    w.bytes = align_up(off, kWorkspaceAlign);
+    return w;
+}
+
 // Extra buffers of the whole-layer call, carved after the routed-expert workspace.
 struct LayerExtra {
     float* logits;          // [T, E]
@@ -223,6 +255,16 @@ qsfi_status validate_plan_desc(qsfi_context* ctx, const qsfi_moe_plan_desc* d)
             return set_invalid_arg(ctx, "NVFP4 MoE requires hidden_size and intermediate_size divisible by 16");
         return QSFI_STATUS_OK;
     }
+    if (is_fp8_plan(*d)) {
+        if (d->activation_dtype != QSFI_DTYPE_FP8_E4M3 || d->weight_dtype != QSFI_DTYPE_FP8_E4M3
+            || d->output_dtype != QSFI_DTYPE_BF16)
+            return set_invalid_arg(ctx, "FP8 MoE plan requires fp8_e4m3 activation/weight and bf16 output dtypes");
+        if (d->hidden_size % 128 != 0 || d->intermediate_size % 128 != 0)
+            return set_invalid_arg(ctx, "FP8 MoE requires hidden_size and intermediate_size divisible by 128");
+        if (d->hidden_size > 4096 || d->intermediate_size > 4096)
+            return set_unsupported(ctx, "FP8 MoE supports hidden_size and intermediate_size up to 4096");
+        return QSFI_STATUS_OK;
+    }
     return set_unsupported(ctx, "unsupported MoE backend");
 }
 
@@ -236,7 +278,9 @@ qsfi_status validate_limits(qsfi_context* ctx, const qsfi_moe_plan_desc& p, uint
     if (p.hidden_size > i32max || 2ull * p.intermediate_size > i32max)
         return set_unsupported(ctx, "MoE dimensions exceed int32 grouped-GEMM limits");
     RouteTables rt {};
-    route_tables_carve(nullptr, static_cast<uint32_t>(routes), p.local_num_experts, &rt);
+    route_tables_carve(nullptr, static_cast<uint32_t>(routes), p.local_num_experts, &rt,
+                       is_fp8_plan(p) ? fp8_tile_rows(static_cast<uint32_t>(routes), p.local_num_experts)
+                                      : static_cast<uint32_t>(kTileM));
     if (rt.max_tiles > 65535)
         return set_unsupported(ctx, "MoE launch grid is too large");
     return QSFI_STATUS_OK;
@@ -373,6 +417,58 @@ qsfi_status run_routed_nvfp4(qsfi_context* ctx, const qsfi_moe_plan_desc& p, con
     return gemm_or_error(ctx, g2, "NVFP4 MoE down GEMM");
 }
 
+// Routed experts on FP8 operands; activation rows are already in w.xq / w.xq_s.
+qsfi_status run_routed_fp8(qsfi_context* ctx, const qsfi_moe_plan_desc& p, const Fp8Workspace& w,
+                           uint32_t num_tokens, const uint8_t* gu, const float* gu_scale, const uint8_t* down,
+                           const float* down_scale)
+{
+    const uint32_t routes = num_tokens * p.top_k;
+    const auto run = [&](const Fp8Gemm& g, const char* op) {
+        const char* why = nullptr;
+        cudaError_t err = launch_fp8_gemm(g, ctx->stream, &why);
+        if (err == cudaErrorNotSupported && why != nullptr)
+            return set_unsupported(ctx, "%s: %s", op, why);
+        if (err != cudaSuccess && why != nullptr)
+            return set_error(ctx, QSFI_STATUS_BACKEND_ERROR, QSFI_ERROR_SOURCE_QSFI, static_cast<int32_t>(err),
+                             "%s: %s", op, why);
+        return set_cuda_error(ctx, err, op);
+    };
+    Fp8Gemm g {};
+    g.x_rows = w.rt.max_pad_rows;
+    g.groups = p.local_num_experts;
+    g.tile_expert = w.rt.tile_expert;
+    g.tile_row0 = w.rt.tile_row0;
+    g.tile_nrows = w.rt.tile_nrows;
+    g.total_tiles = w.rt.total_tiles;
+    g.max_tiles = w.rt.max_tiles;
+    g.tile_rows = w.rt.tile_rows;
+    g.est_tiles = std::min(p.local_num_experts, routes) + routes / w.rt.tile_rows;
+    stage_mark(ctx->stream, STAGE_GATE_UP_GEMM);
+    Fp8Gemm g1 = g;
+    g1.x = w.xq;
+    g1.x_scale = w.xq_s;
+    g1.w = gu;
+    g1.w_scale = gu_scale;
+    g1.n = p.intermediate_size;
+    g1.k = p.hidden_size;
+    g1.gated = 1;
+    g1.out = w.act;
+    g1.out_scale = w.act_s;
+    qsfi_status status = run(g1, "FP8 MoE gate_up GEMM");
+    if (status != QSFI_STATUS_OK)
+        return status;
+    stage_mark(ctx->stream, STAGE_DOWN_GEMM);
+    Fp8Gemm g2 = g;
+    g2.x = w.act;
+    g2.x_scale = w.act_s;
+    g2.w = down;
+    g2.w_scale = down_scale;
+    g2.n = p.hidden_size;
+    g2.k = p.intermediate_size;
+    g2.out = w.y2;
+    return run(g2, "FP8 MoE down GEMM");
+}
+
 qsfi_status validate_routing_tensors(qsfi_context* ctx, const qsfi_moe_plan_desc& p, uint32_t num_tokens,
                                      const qsfi_tensor2& ids, const qsfi_tensor2& weights,
                                      const qsfi_tensor2& out)
@@ -464,6 +560,10 @@ qsfi_status qsfi_moe_workspace_size(qsfi_context* ctx, const qsfi_moe_plan* plan
         if (!upstream_bf16_workspace_bytes(p, num_tokens, &upstream))
             return set_invalid_arg(ctx, "MoE workspace element count overflows size_t");
         *device_bytes = std::max(upstream, carve_bf16(nullptr, p, num_tokens).bytes);
+        return QSFI_STATUS_OK;
+    }
+    if (is_fp8_plan(p)) {
+        *device_bytes = carve_fp8(nullptr, p, num_tokens).bytes;
         return QSFI_STATUS_OK;
     }
     *device_bytes = carve_nvfp4(nullptr, p, num_tokens, true).bytes;
@@ -728,8 +828,9 @@ qsfi_status qs3_moe_layer_workspace_size(qsfi_context* ctx, const qsfi_moe_plan*
     if (static_cast<uint64_t>(num_tokens) * p.top_k > 0x7fffffffull)
         return set_invalid_arg(ctx, "MoE expanded route count overflows size_t");
     const bool nvfp4 = p.backend == QSFI_MOE_BACKEND_FLASHINFER_NVFP4;
-    const size_t base = nvfp4 ? carve_nvfp4(nullptr, p, num_tokens, false).bytes
-                              : carve_bf16(nullptr, p, num_tokens).bytes;
+    const size_t base = is_fp8_plan(p) ? carve_fp8(nullptr, p, num_tokens).bytes
+        : nvfp4                        ? carve_nvfp4(nullptr, p, num_tokens, false).bytes
+                                       : carve_bf16(nullptr, p, num_tokens).bytes;
     *device_bytes = carve_layer(nullptr, base, p, num_tokens, shared_intermediate_size, nvfp4).bytes;
     return QSFI_STATUS_OK;
 }
@@ -746,11 +847,14 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         return set_invalid_arg(ctx, "plan/desc is null");
     const qsfi_moe_plan_desc& p = plan->desc;
     const bool nvfp4 = p.backend == QSFI_MOE_BACKEND_FLASHINFER_NVFP4;
+    const bool fp8 = is_fp8_plan(p);
     if (d->num_tokens == 0 || d->num_tokens > p.max_num_tokens)
         return set_invalid_arg(ctx, "invalid MoE num_tokens");
     const int64_t t = d->num_tokens, h = p.hidden_size, i = p.intermediate_size, e = p.local_num_experts;
     const uint32_t is = d->shared_intermediate_size;
     const bool shared = d->shared_gate_up_weight.data != nullptr;
+    if (fp8 && shared)
+        return set_unsupported(ctx, "FP8 MoE layer does not take a shared expert");
 
     status = validate_tensor(ctx, d->hidden, "hidden", QSFI_DTYPE_BF16);
     if (status != QSFI_STATUS_OK)
@@ -776,7 +880,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         return set_unsupported(ctx, "unsupported router score");
     if (!std::isfinite(d->routed_scaling_factor) || d->routed_scaling_factor <= 0.0f)
         return set_invalid_arg(ctx, "routed_scaling_factor must be finite and positive");
-    const qsfi_dtype wdt = nvfp4 ? QSFI_DTYPE_U8 : QSFI_DTYPE_BF16;
+    const qsfi_dtype wdt = nvfp4 ? QSFI_DTYPE_U8 : fp8 ? QSFI_DTYPE_FP8_E4M3 : QSFI_DTYPE_BF16;
     const int64_t kdiv = nvfp4 ? 2 : 1;
     status = validate_tensor(ctx, d->gate_up_weight, "gate_up_weight", wdt);
     if (status != QSFI_STATUS_OK)
@@ -825,6 +929,15 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
                     < qs3_nvfp4_tiled_scale_bytes(h, is)))
             return set_invalid_arg(ctx, "NVFP4 MoE layer needs tiled shared-expert scales of the right size");
     }
+    if (fp8) {
+        const uint64_t gu_scales = static_cast<uint64_t>(e) * (2 * i / 128) * (h / 128);
+        const uint64_t d_scales = static_cast<uint64_t>(e) * (h / 128) * (i / 128);
+        if (d->gate_up_scale_tiled.data == nullptr || d->down_scale_tiled.data == nullptr
+            || d->gate_up_scale_tiled.dtype != QSFI_DTYPE_F32 || d->down_scale_tiled.dtype != QSFI_DTYPE_F32
+            || static_cast<uint64_t>(d->gate_up_scale_tiled.shape[0]) < gu_scales
+            || static_cast<uint64_t>(d->down_scale_tiled.shape[0]) < d_scales)
+            return set_invalid_arg(ctx, "FP8 MoE layer needs f32 block scales of the right size");
+    }
     size_t need = 0;
     status = qs3_moe_layer_workspace_size(ctx, plan, d->num_tokens, shared ? is : 0, &need);
     if (status != QSFI_STATUS_OK)
@@ -846,15 +959,19 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
     const uint32_t routes = d->num_tokens * p.top_k;
     Bf16Workspace wb {};
     Nvfp4Workspace wn {};
+    Fp8Workspace wf {};
     size_t routed_bytes = 0;
-    if (nvfp4) {
+    if (fp8) {
+        wf = carve_fp8(base, p, d->num_tokens);
+        routed_bytes = wf.bytes;
+    } else if (nvfp4) {
         wn = carve_nvfp4(base, p, d->num_tokens, false);
         routed_bytes = wn.bytes;
     } else {
         wb = carve_bf16(base, p, d->num_tokens);
         routed_bytes = wb.bytes;
     }
-    const RouteTables& rt = nvfp4 ? wn.rt : wb.rt;
+    const RouteTables& rt = fp8 ? wf.rt : nvfp4 ? wn.rt : wb.rt;
     LayerExtra x = carve_layer(base, routed_bytes, p, d->num_tokens, shared ? is : 0, nvfp4);
     const __nv_bfloat16* hidden = static_cast<const __nv_bfloat16*>(d->hidden.data);
 
@@ -893,7 +1010,21 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         return set_cuda_error(ctx, err, "MoE routing");
 
     const __nv_bfloat16* y2 = nullptr;
-    if (nvfp4) {
+    if (fp8) {
+        // 4. quantise the routed rows straight from the bf16 tokens; 5./6. grouped GEMMs
+        stage_mark(st, STAGE_GATHER);
+        err = launch_fp8_gather_quantize(hidden, rt.route_prows, routes, p.top_k, p.hidden_size, wf.xq, wf.xq_s,
+                                         st);
+        if (err != cudaSuccess)
+            return set_cuda_error(ctx, err, "FP8 MoE gather");
+        status = run_routed_fp8(ctx, p, wf, d->num_tokens, static_cast<const uint8_t*>(d->gate_up_weight.data),
+                                static_cast<const float*>(d->gate_up_scale_tiled.data),
+                                static_cast<const uint8_t*>(d->down_weight.data),
+                                static_cast<const float*>(d->down_scale_tiled.data));
+        if (status != QSFI_STATUS_OK)
+            return status;
+        y2 = wf.y2;
+    } else if (nvfp4) {
         // 4. quantise every token once (token order), then gather the codes by expert;
         //    5./6. grouped GEMMs
         stage_mark(st, STAGE_GATHER);
@@ -1419,6 +1550,177 @@ qsfi_status qs3_moe_ep_finish(qsfi_context* ctx, const qsfi_moe_plan* plan, cons
         return set_cuda_error(ctx, launch_combine(cp, st), "qs3_moe_ep_finish");
     }
     return QSFI_STATUS_OK;
+}
+
+// ---- FP8 block-scaled path ------------------------------------------------------------
+
+qsfi_status qs3_fp8_quantize_weight(qsfi_context* ctx, const qs3_fp8_quantize_weight_desc* d)
+{
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (d == nullptr)
+        return set_invalid_arg(ctx, "desc is null");
+    status = validate_tensor(ctx, d->weight, "weight", QSFI_DTYPE_BF16);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_tensor(ctx, d->codes, "codes", QSFI_DTYPE_FP8_E4M3);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_tensor(ctx, d->scale, "scale", QSFI_DTYPE_F32);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    const int64_t e = d->weight.shape[0], rows = d->weight.shape[1], k = d->weight.shape[2];
+    if (!contiguous3(d->weight) || !contiguous3(d->codes) || !contiguous3(d->scale))
+        return set_invalid_arg(ctx, "FP8 weight quantiser tensors must be contiguous");
+    if (k % 128 != 0 || e > 65535 || (rows + 127) / 128 > 65535)
+        return set_invalid_arg(ctx, "FP8 weight quantiser needs k divisible by 128");
+    if (d->codes.shape[0] != e || d->codes.shape[1] != rows || d->codes.shape[2] != k || d->scale.shape[0] != e
+        || d->scale.shape[1] != (rows + 127) / 128 || d->scale.shape[2] != k / 128)
+        return set_invalid_arg(ctx, "FP8 weight quantiser tensor shape mismatch");
+    if (!aligned16(d->weight.data) || !aligned16(d->codes.data))
+        return set_invalid_arg(ctx, "FP8 weight quantiser tensors must be 16-byte aligned");
+    return set_cuda_error(ctx,
+                          launch_fp8_quantize_weight(static_cast<const __nv_bfloat16*>(d->weight.data),
+                                                     static_cast<uint32_t>(e), static_cast<uint32_t>(rows),
+                                                     static_cast<uint32_t>(k), static_cast<uint8_t*>(d->codes.data),
+                                                     static_cast<float*>(d->scale.data), ctx->stream),
+                          "qs3_fp8_quantize_weight");
+}
+
+qsfi_status qs3_fp8_quantize_act(qsfi_context* ctx, const qs3_fp8_quantize_act_desc* d)
+{
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (d == nullptr)
+        return set_invalid_arg(ctx, "desc is null");
+    status = validate_tensor(ctx, d->x, "x", QSFI_DTYPE_BF16);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_tensor(ctx, d->codes, "codes", QSFI_DTYPE_FP8_E4M3);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_tensor(ctx, d->scale, "scale", QSFI_DTYPE_F32);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    const int64_t rows = d->rows, k = d->x.shape[1];
+    if (!contiguous2(d->x) || !contiguous2(d->codes) || !contiguous2(d->scale))
+        return set_invalid_arg(ctx, "FP8 activation quantiser tensors must be contiguous");
+    if (rows == 0 || k % 128 != 0 || d->x.shape[0] < rows || d->codes.shape[0] < rows || d->codes.shape[1] != k
+        || d->scale.shape[0] < rows || d->scale.shape[1] != k / 128)
+        return set_invalid_arg(ctx, "FP8 activation quantiser tensor shape mismatch");
+    if ((reinterpret_cast<uintptr_t>(d->x.data) & 7u) != 0 || (reinterpret_cast<uintptr_t>(d->codes.data) & 3u) != 0)
+        return set_invalid_arg(ctx, "FP8 activation quantiser tensors must be 8-byte aligned");
+    return set_cuda_error(ctx,
+                          launch_fp8_gather_quantize(static_cast<const __nv_bfloat16*>(d->x.data), nullptr,
+                                                     static_cast<uint32_t>(rows), 1, static_cast<uint32_t>(k),
+                                                     static_cast<uint8_t*>(d->codes.data),
+                                                     static_cast<float*>(d->scale.data), ctx->stream),
+                          "qs3_fp8_quantize_act");
+}
+
+qsfi_status qsfi_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, const qsfi_moe_fp8_execute_desc* desc)
+{
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    if (plan == nullptr || desc == nullptr)
+        return set_invalid_arg(ctx, "plan/desc is null");
+    const qsfi_moe_plan_desc& p = plan->desc;
+    if (!is_fp8_plan(p))
+        return set_invalid_arg(ctx, "qsfi_moe_execute_fp8 requires an FP8 block-scaled MoE plan");
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (desc->num_tokens == 0 || desc->num_tokens > p.max_num_tokens)
+        return set_invalid_arg(ctx, "invalid MoE num_tokens");
+    const int64_t t = desc->num_tokens, h = p.hidden_size, i = p.intermediate_size, e = p.local_num_experts;
+    status = validate_tensor(ctx, desc->hidden, "hidden", QSFI_DTYPE_FP8_E4M3);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_tensor(ctx, desc->hidden_scale, "hidden_scale", QSFI_DTYPE_F32);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_tensor(ctx, desc->gate_up_weight, "gate_up_weight", QSFI_DTYPE_FP8_E4M3);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_tensor(ctx, desc->gate_up_weight_scale, "gate_up_weight_scale", QSFI_DTYPE_F32);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_tensor(ctx, desc->down_weight, "down_weight", QSFI_DTYPE_FP8_E4M3);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_tensor(ctx, desc->down_weight_scale, "down_weight_scale", QSFI_DTYPE_F32);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_routing_tensors(ctx, p, desc->num_tokens, desc->topk_ids, desc->topk_weights, desc->out);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (!contiguous2(desc->hidden) || !contiguous2(desc->hidden_scale) || !contiguous3(desc->gate_up_weight)
+        || !contiguous3(desc->gate_up_weight_scale) || !contiguous3(desc->down_weight)
+        || !contiguous3(desc->down_weight_scale))
+        return set_invalid_arg(ctx, "FP8 MoE tensors must be contiguous");
+    if (desc->hidden.shape[0] != t || desc->hidden.shape[1] != h || desc->hidden_scale.shape[0] != t
+        || desc->hidden_scale.shape[1] != h / 128)
+        return set_invalid_arg(ctx, "FP8 MoE hidden tensor shape mismatch");
+    if (desc->gate_up_weight.shape[0] != e || desc->gate_up_weight.shape[1] != 2 * i
+        || desc->gate_up_weight.shape[2] != h || desc->gate_up_weight_scale.shape[0] != e
+        || desc->gate_up_weight_scale.shape[1] != 2 * i / 128 || desc->gate_up_weight_scale.shape[2] != h / 128
+        || desc->down_weight.shape[0] != e || desc->down_weight.shape[1] != h || desc->down_weight.shape[2] != i
+        || desc->down_weight_scale.shape[0] != e || desc->down_weight_scale.shape[1] != h / 128
+        || desc->down_weight_scale.shape[2] != i / 128)
+        return set_invalid_arg(ctx, "FP8 MoE expert weight shape mismatch");
+    size_t need = 0;
+    status = qsfi_moe_workspace_size(ctx, plan, desc->num_tokens, &need);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_workspace(ctx, desc->workspace, need);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    status = validate_limits(ctx, p, desc->num_tokens);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (!aligned16(desc->hidden.data) || !aligned16(desc->out.data) || !aligned16(desc->gate_up_weight.data)
+        || !aligned16(desc->down_weight.data))
+        return set_invalid_arg(ctx, "FP8 MoE tensors must be 16-byte aligned");
+
+    Fp8Workspace w = carve_fp8(static_cast<char*>(desc->workspace.data), p, desc->num_tokens);
+    const uint32_t routes = desc->num_tokens * p.top_k;
+    cudaStream_t st = ctx->stream;
+    cudaError_t err = launch_route_sort(static_cast<const int32_t*>(desc->topk_ids.data),
+                                        static_cast<const float*>(desc->topk_weights.data), routes, p.top_k,
+                                        p.local_expert_offset, p.local_num_experts, w.rt, st);
+    // gather the quantised token rows (codes and their scales) into expert order
+    if (err == cudaSuccess)
+        err = launch_gather_rows(desc->hidden.data, static_cast<uint32_t>(h), w.rt.route_prows, routes, p.top_k,
+                                 w.xq, st);
+    if (err == cudaSuccess)
+        err = launch_gather_rows(desc->hidden_scale.data, static_cast<uint32_t>(h / 128 * 4), w.rt.route_prows,
+                                 routes, p.top_k, w.xq_s, st);
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "FP8 MoE routing");
+    status = run_routed_fp8(ctx, p, w, desc->num_tokens, static_cast<const uint8_t*>(desc->gate_up_weight.data),
+                            static_cast<const float*>(desc->gate_up_weight_scale.data),
+                            static_cast<const uint8_t*>(desc->down_weight.data),
+                            static_cast<const float*>(desc->down_weight_scale.data));
+    if (status != QSFI_STATUS_OK)
+        return status;
+    CombineParams cp {};
+    cp.route_prows = w.rt.route_prows;
+    cp.topk_weights = static_cast<const float*>(desc->topk_weights.data);
+    cp.expert_out = w.y2;
+    cp.out = static_cast<__nv_bfloat16*>(desc->out.data);
+    cp.num_tokens = desc->num_tokens;
+    cp.top_k = p.top_k;
+    cp.hidden_size = p.hidden_size;
+    return set_cuda_error(ctx, launch_combine(cp, st), "qsfi_moe_execute_fp8");
 }
 
 } // extern "C"

@@ -12,14 +12,6 @@ using namespace tc;
 
 enum ProbeKind { PROBE_BF16 = 0, PROBE_FP8 = 1, PROBE_NVFP4 = 2 };
 
-__device__ __forceinline__ void tc_mma_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc)
-{
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
-                 "l"(a), "l"(b), "r"(idesc), "r"(acc)
-                 : "memory");
-}
-
 // One CTA per SM: A tile 128 rows x 128 bytes, B tile n rows x 128 bytes, 128-byte swizzle
 // layout (contents are pseudo-random bytes; the result is never read). Each iteration
 // issues the MMAs that consume one 128-byte k-block: 4 instructions of K = 32 bytes.

@@ -96,8 +96,9 @@ route_scan_kernel(int32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_
             }
             rt.counts[e] = count;
         }
-        const int tiles = (count + kTileM - 1) / kTileM;
-        int v[3] = { count, tiles * kTileM, tiles };
+        const int tile_rows = static_cast<int>(rt.tile_rows);
+        const int tiles = (count + tile_rows - 1) / tile_rows;
+        int v[3] = { count, tiles * tile_rows, tiles };
         int incl[3];
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
@@ -136,8 +137,8 @@ route_scan_kernel(int32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_
             rt.pad_indptr[e] = excl[1];
             for (int m = 0; m < tiles; ++m) {
                 rt.tile_expert[excl[2] + m] = static_cast<int32_t>(e);
-                rt.tile_row0[excl[2] + m] = excl[1] + m * kTileM;
-                rt.tile_nrows[excl[2] + m] = min(kTileM, count - m * kTileM);
+                rt.tile_row0[excl[2] + m] = excl[1] + m * tile_rows;
+                rt.tile_nrows[excl[2] + m] = min(tile_rows, count - m * tile_rows);
             }
         }
         __syncthreads();
@@ -225,6 +226,23 @@ gather_bf16_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__
     uint4* dst = expanded + static_cast<size_t>(prow) * vec_per_row;
     for (uint32_t i = threadIdx.x & 31; i < vec_per_row; i += 32)
         dst[i] = src[i];
+}
+
+// Same gather for rows whose length is only a multiple of 4 bytes.
+__global__ void __launch_bounds__(256)
+gather_words_kernel(const uint32_t* __restrict__ src, const int32_t* __restrict__ route_prows,
+                    uint32_t routes, uint32_t top_k, uint32_t words_per_row, uint32_t* __restrict__ dst)
+{
+    const uint32_t route = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (route >= routes)
+        return;
+    const int prow = route_prows[route];
+    if (prow < 0)
+        return;
+    const uint32_t* s = src + static_cast<size_t>(route / top_k) * words_per_row;
+    uint32_t* d = dst + static_cast<size_t>(prow) * words_per_row;
+    for (uint32_t i = threadIdx.x & 31; i < words_per_row; i += 32)
+        d[i] = s[i];
 }
 
 // out[t, :] = bf16(sum_k w[t,k] * f32(Y2[prow(t,k), :])) (+ shared-expert term).
@@ -437,14 +455,15 @@ cudaError_t launch_ep_rank_routes(int32_t* rows, float* weights, uint32_t tokens
     return cudaGetLastError();
 }
 
-size_t route_tables_carve(char* base, uint32_t routes, uint32_t experts, RouteTables* out)
+size_t route_tables_carve(char* base, uint32_t routes, uint32_t experts, RouteTables* out, uint32_t tile_rows)
 {
     RouteTables rt {};
     size_t off = 0;
     const uint64_t seg = routes < experts ? routes : experts; // experts that can hold a row
-    const uint64_t max_pad_rows = align_up(routes, kTileM) + seg * kTileM;
+    const uint64_t max_pad_rows = align_up(routes, tile_rows) + seg * tile_rows;
+    rt.tile_rows = tile_rows;
     rt.max_pad_rows = static_cast<uint32_t>(max_pad_rows);
-    rt.max_tiles = static_cast<uint32_t>(max_pad_rows / kTileM);
+    rt.max_tiles = static_cast<uint32_t>(max_pad_rows / tile_rows);
     rt.route_blocks = (routes + kSortChunk - 1) / kSortChunk;
     rt.counts = carve<int32_t>(base, off, experts);
     rt.indptr = carve<int32_t>(base, off, experts + 1);
@@ -498,6 +517,23 @@ cudaError_t launch_route_sort(const int32_t* topk_ids, const float* topk_weights
     route_place_kernel<<<rt.route_blocks, kSortWarps * 32, smem, stream>>>(
         topk_ids, topk_weights, routes, top_k, local_offset, experts, rt);
     note_launch(3);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const void* src, uint32_t row_bytes, const int32_t* route_prows, uint32_t routes,
+                               uint32_t top_k, void* dst, cudaStream_t stream)
+{
+    if (row_bytes % 4 != 0)
+        return cudaErrorInvalidValue;
+    const bool vec16 = row_bytes % 16 == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+    if (vec16)
+        gather_bf16_kernel<<<(routes + 7) / 8, 256, 0, stream>>>(static_cast<const uint4*>(src), route_prows, routes,
+                                                                top_k, row_bytes / 16, static_cast<uint4*>(dst));
+    else
+        gather_words_kernel<<<(routes + 7) / 8, 256, 0, stream>>>(static_cast<const uint32_t*>(src), route_prows,
+                                                                 routes, top_k, row_bytes / 4,
+                                                                 static_cast<uint32_t*>(dst));
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -627,6 +663,7 @@ extern "C" qsfi_status qs3_moe_route_sort_static(qsfi_context* ctx, const qs3_ro
     RouteTables rt {};
     size_t off = 0;
     const uint64_t seg = routes < experts ? routes : experts;
+    rt.tile_rows = kTileM;
     rt.max_pad_rows = static_cast<uint32_t>(align_up(routes, kTileM) + seg * kTileM);
     rt.max_tiles = rt.max_pad_rows / kTileM;
     rt.route_blocks = (routes + kSortChunk - 1) / kSortChunk;

@@ -49,6 +49,15 @@ struct TcParams {
     uint32_t debug;     // timing experiments only (QS3_GEMM_DEBUG): 1 no loads, 2 no MMAs, 4 no epilogue
 };
 
+// Host helpers defined beside the GEMM launchers. make_operand_map: 2-D tensor map over a
+// row-major [rows, inner] operand (bf16 elements, or bytes when `bytes_type`), box =
+// 128 bytes x box_rows with the 128-byte swizzle.
+} // namespace tc
+bool make_operand_map(CUtensorMap* map, bool bytes_type, const void* base, uint64_t inner_elems, uint64_t rows,
+                      uint64_t pitch_bytes, uint32_t box_rows);
+uint32_t device_sm_count();
+namespace tc {
+
 // ---- PTX wrappers -------------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -65,6 +74,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
@@ -152,6 +166,15 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d, uint64_t a, uint64_t b, 
 {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
+                 "l"(a), "l"(b), "r"(idesc), "r"(acc)
+                 : "memory");
+}
+
+// e4m3 x e4m3 (formats are in the instruction descriptor), K = 32 elements per instruction
+__device__ __forceinline__ void tc_mma_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
                  "l"(a), "l"(b), "r"(idesc), "r"(acc)
                  : "memory");
 }

@@ -119,6 +119,7 @@ class MoePlanConfig:
 
     def to_c(self) -> capi.MoePlanDesc:
         nv = self.backend == capi.MOE_BACKEND_NVFP4
+        f8 = self.backend == capi.MOE_BACKEND_FP8_BLOCKSCALE
         d = capi.MoePlanDesc()
         d.backend = self.backend
         d.route_mode = self.route_mode
@@ -129,7 +130,7 @@ class MoePlanConfig:
         d.top_k = self.top_k
         d.local_expert_offset = self.local_expert_offset
         d.local_num_experts = self.num_experts if self.local_num_experts is None else self.local_num_experts
-        default = capi.DTYPE_NVFP4_E2M1 if nv else capi.DTYPE_BF16
+        default = capi.DTYPE_NVFP4_E2M1 if nv else capi.DTYPE_FP8_E4M3 if f8 else capi.DTYPE_BF16
         d.activation_dtype = default if self.activation_dtype is None else self.activation_dtype
         d.weight_dtype = default if self.weight_dtype is None else self.weight_dtype
         d.output_dtype = self.output_dtype
@@ -378,6 +379,59 @@ def nvfp4_tile_scales(ctx: Context, scale_linear: torch.Tensor, gated: bool) -> 
 
 
 @dataclass
+class Fp8Weight:
+    """Prepared FP8 weight: e4m3 codes and one f32 scale per 128 x 128 block."""
+    codes: torch.Tensor  # u8 (e4m3 codes) [E, rows, k]
+    scale: torch.Tensor  # f32 [E, ceil(rows/128), k/128]
+
+
+def fp8_quantize_weight(ctx: Context, weight: torch.Tensor) -> Fp8Weight:
+    """``qs3_fp8_quantize_weight``: bf16 [E, rows, k] -> e4m3 codes + 128 x 128 block scales."""
+    e, rows, k = weight.shape
+    codes = torch.empty((e, rows, k), dtype=torch.uint8, device=weight.device)
+    scale = torch.empty((e, (rows + 127) // 128, k // 128), dtype=torch.float32, device=weight.device)
+    d = capi.Fp8QuantizeWeightDesc()
+    d.weight = _desc(weight, 3)
+    d.codes = _desc(codes, 3, capi.DTYPE_FP8_E4M3)
+    d.scale = _desc(scale, 3)
+    ctx.check(ctx._lib.qs3_fp8_quantize_weight(ctx.handle, C.byref(d)))
+    return Fp8Weight(codes, scale)
+
+
+def fp8_quantize_act(ctx: Context, x: torch.Tensor):
+    """``qs3_fp8_quantize_act``: bf16 [rows, k] -> (e4m3 codes u8 [rows, k], f32 [rows, k/128])."""
+    rows, k = x.shape
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((rows, k // 128), dtype=torch.float32, device=x.device)
+    d = capi.Fp8QuantizeActDesc()
+    d.x = _desc(x, 2)
+    d.codes = _desc(codes, 2, capi.DTYPE_FP8_E4M3)
+    d.scale = _desc(scale, 2)
+    d.rows = rows
+    ctx.check(ctx._lib.qs3_fp8_quantize_act(ctx.handle, C.byref(d)))
+    return codes, scale
+
+
+def moe_execute_fp8(plan: MoePlan, hidden_codes, hidden_scale, topk_ids, topk_weights, gate_up: Fp8Weight,
+                    down: Fp8Weight, out, workspace, num_tokens=None):
+    """``qsfi_moe_execute_fp8``: routed experts on FP8 block-scaled operands."""
+    ctx = plan.ctx
+    d = capi.MoeFp8ExecuteDesc()
+    d.hidden = _desc(hidden_codes, 2, capi.DTYPE_FP8_E4M3)
+    d.hidden_scale = _desc(hidden_scale, 2)
+    d.topk_ids = _desc(topk_ids, 2)
+    d.topk_weights = _desc(topk_weights, 2)
+    d.gate_up_weight = _desc(gate_up.codes, 3, capi.DTYPE_FP8_E4M3)
+    d.gate_up_weight_scale = _desc(gate_up.scale, 3)
+    d.down_weight = _desc(down.codes, 3, capi.DTYPE_FP8_E4M3)
+    d.down_weight_scale = _desc(down.scale, 3)
+    d.out = _desc(out, 2)
+    d.workspace = _desc(workspace, 1)
+    d.num_tokens = hidden_codes.shape[0] if num_tokens is None else num_tokens
+    ctx.check(ctx._lib.qsfi_moe_execute_fp8(ctx.handle, plan.handle, C.byref(d)))
+
+
+@dataclass
 class SharedExpert:
     """Shared-expert weights of one layer (upstream src/model.rs:963-968)."""
     gate_up: object          # bf16 [1, 2*Is, H] tensor or Nvfp4Weight
@@ -393,7 +447,8 @@ def moe_layer_execute(plan: MoePlan, hidden, router_weight, gate_up, down, out, 
                       router_logits=None, num_tokens=None):
     """``qs3_moe_layer_execute``: the whole layer of upstream ``execute_moe_mlp``
     (src/model.rs:2072-2228) in one call. ``gate_up`` / ``down`` are bf16 tensors for
-    a bf16 plan and :class:`Nvfp4Weight` for an NVFP4 plan."""
+    a bf16 plan, :class:`Nvfp4Weight` for an NVFP4 plan and :class:`Fp8Weight` for an FP8
+    block-scaled plan."""
     ctx = plan.ctx
     d = capi.MoeLayerDesc()
     d.hidden = _desc(hidden, 2)
@@ -405,6 +460,9 @@ def moe_layer_execute(plan: MoePlan, hidden, router_weight, gate_up, down, out, 
             setattr(d, f"{prefix}_weight", _desc(w.packed, 3))
             setattr(d, f"{prefix}_scale_tiled", _desc(w.scale_tiled, 1))
             setattr(d, f"{prefix}_global_scale", _desc(w.global_scale, 1))
+        elif isinstance(w, Fp8Weight):
+            setattr(d, f"{prefix}_weight", _desc(w.codes, 3, capi.DTYPE_FP8_E4M3))
+            setattr(d, f"{prefix}_scale_tiled", _desc(w.scale.reshape(-1), 1))
         else:
             setattr(d, f"{prefix}_weight", _desc(w, 3))
 

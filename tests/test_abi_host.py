@@ -106,6 +106,12 @@ def test_plan_validation(lib, ctx):
         (dict(backend=capi.MOE_BACKEND_FUSED_BF16), capi.STATUS_UNSUPPORTED, "unsupported MoE backend"),
         (dict(backend=capi.MOE_BACKEND_NVFP4), capi.STATUS_INVALID_ARGUMENT, "nvfp4 activation/weight"),
         (dict(top_k=40, num_experts=64, local_num_experts=64), capi.STATUS_UNSUPPORTED, "top_k"),
+        (dict(backend=capi.MOE_BACKEND_FP8_BLOCKSCALE), capi.STATUS_INVALID_ARGUMENT, "fp8_e4m3 activation/weight"),
+        (dict(backend=capi.MOE_BACKEND_FP8_BLOCKSCALE, activation_dtype=capi.DTYPE_FP8_E4M3,
+              weight_dtype=capi.DTYPE_FP8_E4M3, hidden_size=192), capi.STATUS_INVALID_ARGUMENT,
+         "divisible by 128"),
+        (dict(backend=capi.MOE_BACKEND_FP8_BLOCKSCALE, activation_dtype=capi.DTYPE_FP8_E4M3,
+              weight_dtype=capi.DTYPE_FP8_E4M3, hidden_size=8192), capi.STATUS_UNSUPPORTED, "up to 4096"),
     ):
         assert lib.qsfi_moe_plan_create(ctx, C.byref(_plan_desc(**kw)), C.byref(plan)) == status, kw
         assert frag in _message(lib, ctx)[1], kw
@@ -115,6 +121,14 @@ def test_plan_validation(lib, ctx):
                                     C.byref(plan)) == capi.STATUS_OK
     lib.qsfi_moe_plan_destroy(plan)
     lib.qsfi_moe_plan_destroy(None)  # legal, like upstream
+    # FP8 block-scaled plans (no upstream counterpart): workspace scales with 16-row token tiles
+    fp8 = _plan_desc(backend=capi.MOE_BACKEND_FP8_BLOCKSCALE, activation_dtype=capi.DTYPE_FP8_E4M3,
+                     weight_dtype=capi.DTYPE_FP8_E4M3)
+    assert lib.qsfi_moe_plan_create(ctx, C.byref(fp8), C.byref(plan)) == capi.STATUS_OK
+    n = C.c_size_t(0)
+    assert lib.qsfi_moe_workspace_size(ctx, plan, 16, C.byref(n)) == capi.STATUS_OK
+    assert n.value % 256 == 0 and n.value > 16 * 2 * (256 + 128 + 2 * 256)
+    lib.qsfi_moe_plan_destroy(plan)
 
 
 def _upstream_workspace(tokens, hidden, inter, experts, top_k):

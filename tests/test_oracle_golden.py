@@ -152,3 +152,59 @@ def test_tiled_scale_layout_is_a_bijection(oracle):
         for r, kb in ((0, 0), (33, 5), (rows - 1, k // 16 - 1)):
             tr = oracle.lib().qs3o_gated_tiled_row(r, gated) if gated else r
             assert idx[r, kb] == oracle.lib().qs3o_tiled_scale_offset(tr, kb, k)
+
+
+def test_fp8_quantise_round_trip(oracle):
+    rng = np.random.default_rng(6)
+    x = bf16(rng.standard_normal((5, 256), dtype=np.float32))
+    codes, scale = oracle.fp8_quantize_act(x)
+    # the group maximum maps onto the top of the e4m3 grid and the relative error of a
+    # normal e4m3 value is at most 2^-4
+    deq = oracle.fp8_dequantize(codes, scale)
+    amax = np.abs(f32(x)).reshape(5, 2, 128).max(axis=-1)
+    assert np.allclose(scale, amax / 448.0, rtol=1e-6)
+    assert np.all(np.abs(deq - f32(x)) <= np.abs(f32(x)) * 2.0 ** -4 + np.repeat(scale, 128, axis=-1) * 2.0 ** -9)
+    # all-zero group: floor scale, zero codes
+    z = np.zeros((1, 128), np.uint16)
+    cz, sz = oracle.fp8_quantize_act(z)
+    assert not cz.any() and sz[0, 0] == np.float32(1e-30)
+    # weights: one scale per 128 x 128 block, a partial last row block included
+    w = bf16(rng.standard_normal((2, 192, 256), dtype=np.float32) * 0.02)
+    cw, sw = oracle.fp8_quantize_weight(w)
+    assert sw.shape == (2, 2, 2)
+    assert np.isclose(sw[1, 1, 0], np.abs(f32(w[1, 128:, :128])).max() / 448.0, rtol=1e-6)
+    dq = oracle.fp8_dequantize(cw, sw)
+    assert np.linalg.norm(dq - f32(w)) / np.linalg.norm(f32(w)) < 0.04
+
+
+def test_fp8_moe_matches_dequantised_float64(oracle):
+    """The FP8 chain against plain float64 algebra on the dequantised operands, with the
+    oracle's own intermediate quantisation applied through its quantiser."""
+    rng = np.random.default_rng(7)
+    t, h, i, e, k = 6, 256, 128, 4, 2
+    hidden = bf16(rng.standard_normal((t, h), dtype=np.float32))
+    gu = bf16(rng.standard_normal((e, 2 * i, h), dtype=np.float32) * 0.05)
+    dn = bf16(rng.standard_normal((e, h, i), dtype=np.float32) * 0.05)
+    ids = np.stack([rng.permutation(e)[:k] for _ in range(t)]).astype(np.int32)
+    ids[0, 1] = -1  # an unfilled slot is skipped
+    w = rng.random((t, k)).astype(np.float32)
+    hc, hs = oracle.fp8_quantize_act(hidden)
+    guq, dnq = oracle.fp8_quantize_weight(gu), oracle.fp8_quantize_weight(dn)
+    out = f32(oracle.moe_fp8(hc, hs, ids, w, guq, dnq))
+    x = oracle.fp8_dequantize(hc, hs).astype(np.float64)
+    gu_d = oracle.fp8_dequantize(*guq).astype(np.float64)
+    dn_d = oracle.fp8_dequantize(*dnq).astype(np.float64)
+    want = np.zeros((t, h))
+    for tok in range(t):
+        for j in range(k):
+            ex = ids[tok, j]
+            if ex < 0:
+                continue
+            y1 = gu_d[ex] @ x[tok]
+            act = (y1[:i] / (1.0 + np.exp(-y1[:i])) * y1[i:]).astype(np.float32)
+            # quantise the f32 activation with the same rule (group of 128 == whole row here)
+            s = max(np.abs(act).max() / np.float32(448.0), np.float32(1e-30))
+            q = np.array([oracle.lib().qs3o_e4m3_to_f32(oracle.lib().qs3o_f32_to_e4m3(float(np.float32(v) * (np.float32(1.0) / s))))
+                          for v in act], np.float64) * float(s)
+            want[tok] += float(w[tok, j]) * (dn_d[ex] @ q)
+    assert np.linalg.norm(out - want) / np.linalg.norm(want) < 5e-3
