@@ -8,7 +8,8 @@ grouped gate_up GEMM + SwiGLU -> grouped down GEMM -> shared expert -> combine) 
 one batch of synthetic tokens. At N = 1 the workload is the NVFP4 prefill layer
 (8192 tokens, hidden 2048, 512 experts, top-10 + shared expert, Zipf-skewed router);
 at N > 1 it is the expert-parallel variant with 4096 tokens per rank (weak scaling),
-launched one process per GPU by torch.distributed.run.
+launched one process per GPU by torch.distributed.run. `--workload decode_fp8` (N = 1)
+times the FP8 block-scaled decode batch instead (64 tokens, 128 experts, top-8).
 
 Prints ONE JSON line on rank 0. `value` is device-timed (CUDA events, max over
 ranks) with inputs resident in HBM; `e2e` goes through the same C-ABI call with the
@@ -108,6 +109,8 @@ class ClockSampler:
 def _host_copies(data, ops):
     """numpy copies of what the CPU oracle needs (weights in the declared linear layout)."""
     def triple(q):
+        if isinstance(q, ops.Fp8Weight):
+            return (q.codes.cpu().numpy(), q.scale.cpu().numpy())
         return (q.packed.cpu().numpy(), q.scale_linear.cpu().numpy(), q.global_scale.cpu().numpy())
 
     import torch
@@ -129,6 +132,9 @@ def _oracle_layer(orc, host, cfg, tokens):
     hid = host["hidden"][tokens]
     logits = orc.gemm_bf16(hid, host["router"], "f32")
     ids, w = orc.router_topk(logits, cfg.top_k, 0, True, 1.0, host["bias"])
+    if cfg.fp8:
+        hc, hs = orc.fp8_quantize_act(hid)
+        return orc.moe_fp8(hc, hs, ids, w, host["gu"], host["d"]), ids
     hp, hs = orc.nvfp4_quantize_act(hid, 1.0)
     return orc.moe_nvfp4(hp, hs, ids, w, host["gu"], host["d"], shared=host["shared"], hidden_bf16=hid), ids
 
@@ -152,12 +158,24 @@ def time_oracle(host, cfg, target_seconds=12.0, max_tokens=4096):
 
 # ----------------------------------------------------------------------- main legs ---
 
+def _workload(args):
+    """The layer configuration the flags select: at N = 1 the NVFP4 prefill layer unless
+    --workload names the FP8 decode batch; at N > 1 the expert-parallel NVFP4 layer."""
+    from qs3_b200 import workload
+    if args.gpus == 1:
+        return workload.DECODE_FP8 if args.workload == "decode_fp8" else workload.PREFILL_NVFP4
+    if args.workload != "prefill_nvfp4":
+        raise SystemExit("only the NVFP4 layer runs expert-parallel")
+    return workload.EP_NVFP4
+
+
 def _config(cfg, world):
     """The `config` object of the JSON line, identical for both arms."""
+    weights_gb = cfg.experts * 3 * cfg.inter * cfg.hidden * (0.5625 if cfg.nvfp4 else 1.0 if cfg.fp8 else 2.0) / 1e9
     return {"workload": cfg.name, "tokens_per_gpu": cfg.tokens, "hidden": cfg.hidden, "experts": cfg.experts,
             "top_k": cfg.top_k, "intermediate": cfg.inter, "shared_intermediate": cfg.shared_inter,
             "router_bias": f"zipf(s={cfg.zipf_s})", "parallelism": "single" if world == 1 else f"ep{world}",
-            "l2_policy": "inputs_exceed_l2 (expert weights ~0.9 GB per pass)"}
+            "l2_policy": f"inputs_exceed_l2 (expert weights ~{weights_gb:.1f} GB per pass)"}
 
 
 def run_reference(args, rank, world):
@@ -166,7 +184,7 @@ def run_reference(args, rank, world):
         return
     import torch
     from qs3_b200 import ops, workload
-    cfg = workload.PREFILL_NVFP4 if args.gpus == 1 else workload.EP_NVFP4
+    cfg = _workload(args)
     ctx = ops.Context(0)
     data = workload.LayerData(cfg, ctx, seed=0)
     host = _host_copies(data, ops)
@@ -184,7 +202,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1000.0 * dt, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "nvfp4", "data": "synthetic",
+        "dtype": cfg.dtype_name, "data": "synthetic",
         "config": _config(cfg, args.gpus),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": f"first {n} tokens of the batch per step, whole layer on the CPU oracle"},
@@ -205,7 +223,7 @@ def run_ours(args, rank, world, local_rank):
     ctx.validate_target()
 
     if world == 1:
-        cfg = workload.PREFILL_NVFP4
+        cfg = _workload(args)
         if args.tokens or args.experts:
             # reduced case for profiler captures only (never a reported bench value)
             import dataclasses
@@ -280,7 +298,7 @@ def run_ours(args, rank, world, local_rank):
     line = {
         "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg.dtype_name,
         "data": "synthetic",
         "config": _config(cfg, world),
         "e2e": {"value": e2e_value, "unit": "tokens/s",
@@ -382,18 +400,30 @@ class SingleGpuLayer:
         counts = torch.bincount(self.ids.flatten().long(), minlength=cfg.experts)
         hit = int((counts > 0).sum().item())
         routes = cfg.tokens * cfg.top_k
-        gu_bytes, _ = self.data.weight_bytes_per_expert()
-        act_in = routes * (cfg.hidden // 2 + cfg.hidden // 16)
-        act_out = routes * (cfg.inter // 2 + cfg.inter // 16)
+        gu_bytes, d_bytes = self.data.weight_bytes_per_expert()
+        flops = 2.0 * routes * 2 * cfg.inter * cfg.hidden
+        if cfg.fp8:
+            act_in = routes * (cfg.hidden + cfg.hidden // 128 * 4)
+            act_out = routes * (cfg.inter + cfg.inter // 128 * 4)
+            kernel, nominal, key = "gemm_fp8_kernel<16, gated>", 4.5e15, "tensor_frac_of_nominal_fp8"
+        else:
+            act_in = routes * (cfg.hidden // 2 + cfg.hidden // 16)
+            act_out = routes * (cfg.inter // 2 + cfg.inter // 16)
+            kernel, nominal, key = "gemm_tc_astat_kernel<gated, swiglu_nvfp4>", 9e15, "tensor_frac_of_nominal_fp4"
         algo = hit * gu_bytes + act_in + act_out
         achieved = algo / (ms * 1e-3) / 1e9
-        flops = 2.0 * routes * 2 * cfg.inter * cfg.hidden
-        return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
-                "frac": achieved / hbm_gbs, "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
-                "kernel": "gemm_tc_kernel<nvfp4, gated, swiglu_nvfp4>", "kernel_ms": ms,
-                "algorithmic_bytes": algo, "experts_hit": hit,
-                "max_rows_per_expert": int(counts.max().item()),
-                "tensor_tflops": flops / (ms * 1e-3) / 1e12, "tensor_frac_of_nominal_fp4": flops / (ms * 1e-3) / 9e15}
+        out = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
+               "frac": achieved / hbm_gbs, "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
+               "kernel": kernel, "kernel_ms": ms, "algorithmic_bytes": algo, "experts_hit": hit,
+               "max_rows_per_expert": int(counts.max().item()),
+               "tensor_tflops": flops / (ms * 1e-3) / 1e12, key: flops / (ms * 1e-3) / nominal}
+        ms2 = stage_ms.get("down_gemm")
+        if ms2:
+            algo2 = hit * d_bytes + act_out + routes * cfg.hidden * 2
+            out["down_gemm"] = {"kernel_ms": ms2, "algorithmic_bytes": algo2,
+                                "achieved": algo2 / (ms2 * 1e-3) / 1e9,
+                                "frac": algo2 / (ms2 * 1e-3) / 1e9 / hbm_gbs}
+        return out
 
 
 def main():
@@ -402,6 +432,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="prefill_nvfp4", choices=["prefill_nvfp4", "decode_fp8"],
+                    help="N = 1 only: the FP8 decode batch (64 tokens, 128 experts, top-8) instead of the headline layer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernels-only", action="store_true",
                     help="only the device-timed loop (for profiler captures; prints no valid bench line)")

@@ -25,6 +25,11 @@ class LayerConfig:
     shared_inter: int = 0
     nvfp4: bool = True
     zipf_s: float = 0.0
+    fp8: bool = False   # e4m3 experts with 128 x 128 block scales (nvfp4 must then be False)
+
+    @property
+    def dtype_name(self) -> str:
+        return "nvfp4" if self.nvfp4 else "fp8" if self.fp8 else "bf16"
 
 
 # Qwen3-Next-shaped prefill layer: 8192 tokens, 512 experts, top-10 + shared expert, NVFP4
@@ -32,6 +37,8 @@ PREFILL_NVFP4 = LayerConfig("qwen3next_moe_prefill_nvfp4", 8192, 2048, 512, 10, 
 # per-rank slice of the expert-parallel configuration (4096 tokens per rank)
 EP_NVFP4 = LayerConfig("qwen3next_moe_ep_nvfp4", 4096, 2048, 512, 10, 512, 512, True, 1.1)
 TINY_BF16 = LayerConfig("tiny_bf16", 16, 256, 8, 2, 128, 0, False, 0.0)
+# Qwen3-30B-A3B-shaped decode batch: 64 tokens, 128 experts, top-8, FP8 block-scaled, no shared expert
+DECODE_FP8 = LayerConfig("qwen3_30b_a3b_moe_decode_fp8", 64, 2048, 128, 8, 768, 0, False, 0.0, True)
 
 
 def _normal_bf16(shape, std, gen, device, chunk_rows=64):
@@ -87,6 +94,12 @@ class LayerData:
                 self.shared = ops.SharedExpert(ops.nvfp4_quantize_weight(ctx, sgu, True),
                                                ops.nvfp4_quantize_weight(ctx, sdn, False), sgate, s)
             torch.cuda.synchronize(dev)
+        elif cfg.fp8:
+            if s:
+                raise ValueError("the FP8 layer takes no shared expert")
+            self.gate_up = ops.fp8_quantize_weight(ctx, gate_up)
+            self.down = ops.fp8_quantize_weight(ctx, down)
+            torch.cuda.synchronize(dev)
         else:
             self.gate_up, self.down = gate_up, down
             if s:
@@ -105,7 +118,8 @@ class LayerData:
         return ops.MoePlan(ctx, ops.MoePlanConfig(
             max_num_tokens=max_tokens or cfg.tokens, hidden_size=cfg.hidden, intermediate_size=cfg.inter,
             num_experts=cfg.experts, top_k=cfg.top_k, local_expert_offset=first, local_num_experts=count,
-            backend=capi.MOE_BACKEND_NVFP4 if cfg.nvfp4 else capi.MOE_BACKEND_STAGED_BF16,
+            backend=capi.MOE_BACKEND_NVFP4 if cfg.nvfp4
+            else capi.MOE_BACKEND_FP8_BLOCKSCALE if cfg.fp8 else capi.MOE_BACKEND_STAGED_BF16,
             route_mode=capi.MOE_ROUTE_ROUTER_LOGITS))
 
     def weight_bytes_per_expert(self):
@@ -114,4 +128,7 @@ class LayerData:
         if cfg.nvfp4:
             return (2 * cfg.inter * cfg.hidden // 2 + 2 * cfg.inter * cfg.hidden // 16,
                     cfg.hidden * cfg.inter // 2 + cfg.hidden * cfg.inter // 16)
+        if cfg.fp8:
+            blocks = (2 * cfg.inter // 128) * (cfg.hidden // 128)
+            return 2 * cfg.inter * cfg.hidden + 4 * blocks, cfg.hidden * cfg.inter + 2 * blocks
         return 2 * cfg.inter * cfg.hidden * 2, cfg.hidden * cfg.inter * 2
