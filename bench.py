@@ -169,12 +169,15 @@ def _workload(args):
     return workload.EP_NVFP4
 
 
-def _config(cfg, world):
+def _config(cfg, world, placement="balanced"):
     """The `config` object of the JSON line, identical for both arms."""
     weights_gb = cfg.experts * 3 * cfg.inter * cfg.hidden * (0.5625 if cfg.nvfp4 else 1.0 if cfg.fp8 else 2.0) / 1e9
     return {"workload": cfg.name, "tokens_per_gpu": cfg.tokens, "hidden": cfg.hidden, "experts": cfg.experts,
             "top_k": cfg.top_k, "intermediate": cfg.inter, "shared_intermediate": cfg.shared_inter,
             "router_bias": f"zipf(s={cfg.zipf_s})", "parallelism": "single" if world == 1 else f"ep{world}",
+            "expert_placement": "all local" if world == 1 else
+            ("contiguous blocks of expert ids" if placement == "contiguous" else
+             "even counts per rank, load-balanced on a calibration batch (longest-processing-time rule)"),
             "l2_policy": f"inputs_exceed_l2 (expert weights ~{weights_gb:.1f} GB per pass)"}
 
 
@@ -203,7 +206,7 @@ def run_reference(args, rank, world):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1000.0 * dt, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": cfg.dtype_name, "data": "synthetic",
-        "config": _config(cfg, args.gpus),
+        "config": _config(cfg, args.gpus, args.placement),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": f"first {n} tokens of the batch per step, whole layer on the CPU oracle"},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -235,7 +238,8 @@ def run_ours(args, rank, world, local_rank):
         from qs3_b200 import ep
         cfg = workload.EP_NVFP4
         per = cfg.experts // world
-        data = workload.LayerData(cfg, ctx, seed=0, expert_range=(rank * per, per), token_seed=rank + 1)
+        data = workload.LayerData(cfg, ctx, seed=0, expert_range=(rank * per, per), token_seed=rank + 1,
+                                  balance_world=0 if args.placement == "contiguous" else world)
         layer = ep.ExpertParallelLayer(ctx, data, rank, world)
 
     def barrier():
@@ -300,7 +304,7 @@ def run_ours(args, rank, world, local_rank):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg.dtype_name,
         "data": "synthetic",
-        "config": _config(cfg, world),
+        "config": _config(cfg, world, args.placement),
         "e2e": {"value": e2e_value, "unit": "tokens/s",
                 "h2d_bytes_per_step": h_in.numel() * 2 * world, "d2h_bytes_per_step": h_out.numel() * 2 * world},
         "gpu_launches": launches,
@@ -434,6 +438,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill_nvfp4", choices=["prefill_nvfp4", "decode_fp8"],
                     help="N = 1 only: the FP8 decode batch (64 tokens, 128 experts, top-8) instead of the headline layer")
+    ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
+                    help="N > 1: how the experts are assigned to ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernels-only", action="store_true",
                     help="only the device-timed loop (for profiler captures; prints no valid bench line)")

@@ -3,6 +3,8 @@
 // scatter_hidden / finalize (qsfi_moe.cu:327-409,465-492).
 #include "common.cuh"
 
+#include <algorithm>
+
 #include <mutex>
 
 namespace qs3 {
@@ -246,24 +248,37 @@ gather_words_kernel(const uint32_t* __restrict__ src, const int32_t* __restrict_
 }
 
 // out[t, :] = bf16(sum_k w[t,k] * f32(Y2[prow(t,k), :])) (+ shared-expert term).
-// One warp per token; k ascending and f32 accumulation as upstream finalize_kernel
-// (qsfi_moe.cu:465-492). Each lane owns 8-element chunks of the row.
+// One block per token, one 8-element chunk of the row per thread and step; k ascending and
+// f32 accumulation as upstream finalize_kernel (qsfi_moe.cu:465-492). Loads of up to four
+// routes are issued together so that their latencies overlap.
 __global__ void __launch_bounds__(256) combine_kernel(CombineParams p)
 {
-    const uint32_t token = blockIdx.x * 8 + (threadIdx.x >> 5);
-    const uint32_t lane = threadIdx.x & 31;
-    if (token >= p.num_tokens)
-        return;
+    __shared__ int s_row[32];
+    __shared__ float s_w[32];
+    __shared__ float s_dot[8];
+    __shared__ int s_any;
+    const uint32_t token = blockIdx.x;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t vec_per_row = p.hidden_size / 8;
 
-    float gate = 0.0f;
+    if (threadIdx.x < 32) {
+        int row = -1;
+        if (threadIdx.x < p.top_k) {
+            row = p.route_prows[static_cast<size_t>(token) * p.top_k + threadIdx.x];
+            s_row[threadIdx.x] = row;
+            s_w[threadIdx.x] = p.topk_weights[static_cast<size_t>(token) * p.top_k + threadIdx.x];
+        }
+        const int any = __any_sync(0xffffffffu, row >= 0);
+        if (threadIdx.x == 0)
+            s_any = any;
+    }
+    float dot = 0.0f;
     if (p.shared_out != nullptr) {
         // gate logit x . w_gate in f32 (upstream computes it as an N = 1 GEMM,
         // src/model.rs:2218-2226)
         const uint4* x = reinterpret_cast<const uint4*>(p.hidden) + static_cast<size_t>(token) * vec_per_row;
         const uint4* w = reinterpret_cast<const uint4*>(p.gate_w);
-        float dot = 0.0f;
-        for (uint32_t i = lane; i < vec_per_row; i += 32) {
+        for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
             const uint4 xv = x[i], wv = w[i];
             const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
             const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
@@ -276,43 +291,49 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p)
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
             dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0)
+            s_dot[warp] = dot;
+    }
+    __syncthreads();
+    if (p.skip_empty && !s_any)
+        return; // no local route: the row stays unwritten and is never read
+    float gate = 0.0f;
+    if (p.shared_out != nullptr) {
+        dot = 0.0f;
+        for (uint32_t w = 0; w < blockDim.x / 32; ++w) // fixed order: the same sum in every thread
+            dot += s_dot[w];
         gate = sigmoid_fast(dot);
     }
 
-    // routing of this token: lane k holds route k
-    int my_row = -1;
-    float my_w = 0.0f;
-    if (lane < p.top_k) {
-        my_row = p.route_prows[static_cast<size_t>(token) * p.top_k + lane];
-        my_w = p.topk_weights[static_cast<size_t>(token) * p.top_k + lane];
-    }
-    if (p.skip_empty && __all_sync(0xffffffffu, my_row < 0))
-        return; // no local route: the row stays unwritten and is never read
     const uint4* y2 = reinterpret_cast<const uint4*>(p.expert_out);
     uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
-    // the trip count is warp-uniform: the shuffles below need every lane
-    for (uint32_t i0 = 0; i0 < vec_per_row; i0 += 32) {
-        const uint32_t i = i0 + lane;
-        const bool active = i < vec_per_row;
+    for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
             acc[j] = 0.0f;
-        for (uint32_t k = 0; k < p.top_k; ++k) {
-            const int row = __shfl_sync(0xffffffffu, my_row, k);
-            const float w = __shfl_sync(0xffffffffu, my_w, k);
-            if (row < 0 || !active)
-                continue;
-            const uint4 v = y2[static_cast<size_t>(row) * vec_per_row + i];
-            const uint32_t vs[4] = { v.x, v.y, v.z, v.w };
+        for (uint32_t k0 = 0; k0 < p.top_k; k0 += 4) {
+            uint4 v[4];
+            float w[4];
+            int row[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                acc[2 * j] += w * bf16_bits_to_f32(vs[j] & 0xffffu);
-                acc[2 * j + 1] += w * bf16_bits_to_f32(vs[j] >> 16);
+            for (uint32_t q = 0; q < 4; ++q) {
+                row[q] = k0 + q < p.top_k ? s_row[k0 + q] : -1;
+                w[q] = row[q] >= 0 ? s_w[k0 + q] : 0.0f;
+                v[q] = row[q] >= 0 ? y2[static_cast<size_t>(row[q]) * vec_per_row + i] : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (uint32_t q = 0; q < 4; ++q) {
+                if (row[q] < 0)
+                    continue; // a skipped route adds nothing (not even a signed zero)
+                const uint32_t vs[4] = { v[q].x, v[q].y, v[q].z, v[q].w };
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[2 * j] += w[q] * bf16_bits_to_f32(vs[j] & 0xffffu);
+                    acc[2 * j + 1] += w[q] * bf16_bits_to_f32(vs[j] >> 16);
+                }
             }
         }
-        if (!active)
-            continue;
         if (p.shared_out != nullptr) {
             const uint4 s = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
             const uint32_t ss[4] = { s.x, s.y, s.z, s.w };
@@ -550,7 +571,10 @@ cudaError_t launch_gather_bf16(const __nv_bfloat16* hidden, const int32_t* route
 
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream)
 {
-    combine_kernel<<<(p.num_tokens + 7) / 8, 256, 0, stream>>>(p);
+    if (p.num_tokens == 0)
+        return cudaSuccess;
+    const uint32_t threads = std::min(256u, std::max(32u, (p.hidden_size / 8 + 31) / 32 * 32));
+    combine_kernel<<<p.num_tokens, threads, 0, stream>>>(p);
     note_launch();
     return cudaGetLastError();
 }

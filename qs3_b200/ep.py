@@ -41,6 +41,28 @@ def expert_block(rank: int, world: int, num_experts: int):
     return rank * per, per
 
 
+def balanced_placement(counts, world: int):
+    """Static expert placement from routing statistics: a permutation ``placement`` of the
+    expert ids such that rank r owns ``placement[r*per:(r+1)*per]`` (``per`` experts each)
+    and the per-rank sums of ``counts`` (routes seen per expert on a calibration batch) are
+    as even as the longest-processing-time rule makes them: experts in descending count go
+    to the least-loaded rank that still has a free slot. Ties keep ascending expert id, so
+    every rank computes the same placement from the same counts."""
+    counts = [int(c) for c in counts]
+    n = len(counts)
+    if n % world != 0:
+        raise ValueError("num_experts must be divisible by the number of ranks")
+    per = n // world
+    order = sorted(range(n), key=lambda e: (-counts[e], e))
+    loads = [0] * world
+    slots = [[] for _ in range(world)]
+    for e in order:
+        r = min((r for r in range(world) if len(slots[r]) < per), key=lambda r: (loads[r], r))
+        slots[r].append(e)
+        loads[r] += counts[e]
+    return [e for r in range(world) for e in sorted(slots[r])]
+
+
 class CudaBackend:
     """The three compute phases on this rank's GPU through the C ABI."""
 
@@ -253,6 +275,11 @@ class ExpertParallelLayer:
         hidden = self.data.hidden
         for _ in range(iters):
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
+            if self.cuda and self.world > 1:
+                # ranks start each pass together, so "dispatch" holds the gather itself and
+                # "combine_exchange" the wait for the slowest rank's experts phase
+                dist.barrier(group=self.group)
+                torch.cuda.synchronize()
             ev[0].record()
             packed, scale, ids, wts = b.route(hidden)
             ev[1].record()

@@ -57,10 +57,18 @@ class LayerData:
 
     ``expert_range`` = (first, count) keeps only that slice of the routed experts on
     this device (expert parallelism); router and shared expert are always whole.
+    ``placement`` (optional, a permutation of the expert ids) stores logical expert
+    ``placement[p]`` at physical position ``p``: router rows, router bias and expert
+    weights are laid out in physical order, so every id the layer reports is a physical
+    one and ``expert_range`` slices physical positions. This is how a weight loader
+    spreads hot experts over ranks. ``balance_world`` = n > 1 derives the placement here:
+    the router is run on a seeded calibration batch (the same on every rank, plain tensor
+    ops at set-up time) and ``ep.balanced_placement`` evens the per-rank route counts.
     """
 
     def __init__(self, cfg: LayerConfig, ctx: ops.Context, seed: int = 0, expert_range=None,
-                 token_seed: int | None = None, keep_bf16: bool = False):
+                 token_seed: int | None = None, keep_bf16: bool = False, placement=None,
+                 balance_world: int = 0, calibration_tokens: int = 8192):
         dev = torch.device("cuda", ctx.device)
         self.cfg = cfg
         first, count = expert_range if expert_range is not None else (0, cfg.experts)
@@ -73,15 +81,36 @@ class LayerData:
         if cfg.zipf_s > 0:
             perm = torch.randperm(cfg.experts, generator=gw, device=dev)
             self.bias = (-cfg.zipf_s * torch.log1p(perm.to(torch.float32))).contiguous()
+        logical = list(range(cfg.experts))
+        if placement is None and balance_world > 1:
+            from .ep import balanced_placement
+            gc = torch.Generator(device=dev)
+            gc.manual_seed(1000 * seed + 999)
+            x = _normal_bf16((calibration_tokens, h), 1.0, gc, dev, chunk_rows=1024)
+            logits = x.float() @ self.router.float().t()
+            if self.bias is not None:
+                logits += self.bias
+            ids = logits.topk(cfg.top_k, dim=1).indices
+            counts = torch.bincount(ids.flatten(), minlength=cfg.experts).cpu().tolist()
+            placement = balanced_placement(counts, balance_world)
+            del x, logits, ids
+        if placement is not None:
+            logical = [int(e) for e in placement]
+            if sorted(logical) != list(range(cfg.experts)):
+                raise ValueError("placement must be a permutation of the expert ids")
+            index = torch.tensor(logical, dtype=torch.long, device=dev)
+            self.router = self.router.index_select(0, index).contiguous()
+            if self.bias is not None:
+                self.bias = self.bias.index_select(0, index).contiguous()
+        self.placement = logical
         # routed experts: generate every expert so that all ranks agree, keep the local slice
         gate_up = torch.empty((count, 2 * i, h), dtype=torch.bfloat16, device=dev)
         down = torch.empty((count, h, i), dtype=torch.bfloat16, device=dev)
-        for e in range(cfg.experts):
+        for pos in range(first, first + count):
             ge = torch.Generator(device=dev)
-            ge.manual_seed(1000 * seed + 100 + e)
-            if first <= e < first + count:
-                gate_up[e - first] = (torch.randn((2 * i, h), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
-                down[e - first] = (torch.randn((h, i), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
+            ge.manual_seed(1000 * seed + 100 + logical[pos])
+            gate_up[pos - first] = (torch.randn((2 * i, h), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
+            down[pos - first] = (torch.randn((h, i), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
         self.shared = None
         if s:
             sgu = _normal_bf16((1, 2 * s, h), 0.02, gw, dev)

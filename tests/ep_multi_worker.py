@@ -24,15 +24,20 @@ def main():
     ctx = ops.Context(local)
     cfg = workload.LayerConfig("ep_multi", 512, 512, 32, 4, 256, 256, True, 1.1)
     first, count = ep.expert_block(rank, world, cfg.experts)
-    part = workload.LayerData(cfg, ctx, seed=9, expert_range=(first, count), token_seed=rank + 1)
+    balance = world if os.environ.get("QS3_TEST_BALANCED") == "1" else 0
+    part = workload.LayerData(cfg, ctx, seed=9, expert_range=(first, count), token_seed=rank + 1,
+                              balance_world=balance)
     layer = ep.ExpertParallelLayer(ctx, part, rank, world)
     for _ in range(3):
         out = layer.step()
     torch.cuda.synchronize()
     got = to_np(out)
 
-    full = workload.LayerData(cfg, ctx, seed=9, token_seed=rank + 1)
+    full = workload.LayerData(cfg, ctx, seed=9, token_seed=rank + 1, placement=part.placement)
     assert torch.equal(full.hidden, part.hidden)
+    assert torch.equal(full.router, part.router)
+    if balance:
+        assert part.placement != list(range(cfg.experts))
     plan = full.plan(ctx)
     ws = torch.empty(plan.layer_workspace_size(cfg.tokens, cfg.shared_inter), dtype=torch.uint8, device="cuda")
     ref = torch.empty((cfg.tokens, cfg.hidden), dtype=torch.bfloat16, device="cuda")
@@ -48,7 +53,7 @@ def main():
     assert np.max(np.abs(f32(got) - want)) <= 2.0 ** -5 * np.max(np.abs(want))
     dist.barrier()
     if rank == 0:
-        print(f"EP_MULTI_OK world={world} rel_l2={err:.3e} combine={layer.combine_mode}")
+        print(f"EP_MULTI_OK world={world} rel_l2={err:.3e} combine={layer.combine_mode} balanced={bool(balance)}")
     dist.destroy_process_group()
 
 

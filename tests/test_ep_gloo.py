@@ -147,3 +147,25 @@ def test_expert_block_partition():
     assert [ep.expert_block(r, 4, 512) for r in range(4)] == [(0, 128), (128, 128), (256, 128), (384, 128)]
     with pytest.raises(ValueError):
         ep.expert_block(0, 3, 512)
+
+
+def test_balanced_placement_evens_rank_loads():
+    """Static placement from routing statistics: a permutation with equal expert counts per
+    rank whose per-rank load is far more even than contiguous blocks under a skewed load."""
+    from qs3_b200.ep import balanced_placement
+    rng = np.random.default_rng(3)
+    counts = (40000.0 / (1.0 + rng.permutation(64)) ** 1.1).astype(np.int64)
+    for world in (2, 4, 8):
+        place = balanced_placement(counts, world)
+        assert sorted(place) == list(range(64))
+        per = 64 // world
+        loads = [int(counts[place[r * per:(r + 1) * per]].sum()) for r in range(world)]
+        blocks = [int(counts[r * per:(r + 1) * per].sum()) for r in range(world)]
+        assert max(loads) <= max(blocks)
+        # as even as equal expert counts allow: the rank of the hottest expert also has to
+        # take per - 1 others, at best the coldest ones
+        floor = max(sum(loads) / world, int(counts.max() + np.sort(counts)[:per - 1].sum()))
+        assert max(loads) <= 1.05 * floor
+        assert balanced_placement(counts, world) == place          # deterministic
+    with pytest.raises(ValueError):
+        balanced_placement(counts, 5)
