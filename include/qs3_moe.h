@@ -608,8 +608,10 @@ qsfi_status qs3_moe_profile_end(
  * upstream: every SM issues `iters` x 4 back-to-back 128 x n MMAs (K = 32 bytes each) on
  * operands resident in shared memory, timed with CUDA events on the context's stream.
  * kind 0 = bf16 (kind::f16), 1 = fp8 e4m3 (kind::f8f6f4), 2 = NVFP4 block-scaled
- * (kind::mxf4nvf4, scale_vec::4X). n is a multiple of 16 in [16, 256]. Returns dense
- * TFLOP/s. Used as the denominator of the reported tensor-pipe fractions. */
+ * (kind::mxf4nvf4, scale_vec::4X). n is a multiple of 16 in [16, 256]. kind + 16: CTA
+ * pairs (clusters of two) issue cta_group::2 instructions of 256 x n instead (n a multiple
+ * of 32). Returns dense TFLOP/s. Used as the denominator of the reported tensor-pipe
+ * fractions. */
 qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, uint32_t n, uint32_t iters, double* tflops);
 
 #ifdef __cplusplus

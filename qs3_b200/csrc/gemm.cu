@@ -374,9 +374,11 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                             const uint32_t sfb_cols = tmem_sfb + 16 * sf_flip;
                             sf_flip ^= 1;
                             const uint32_t sf_smem = sb + kbs * kTileBytes + q * kSfBytes;
+                            if (!(p.debug & 8u)) {
 #pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j)
-                                tc_cp_scales(sfb_cols + 4 * j, scale_desc(sf_smem + j * 512));
+                                for (uint32_t j = 0; j < 4; ++j)
+                                    tc_cp_scales(sfb_cols + 4 * j, scale_desc(sf_smem + j * 512));
+                            }
                             const uint64_t da = operand_desc(a_addr + kb * kTileBytes);
                             const uint64_t db = operand_desc(sb + q * kTileBytes);
 #pragma unroll

@@ -5,6 +5,8 @@
 // figures; it is not part of the MoE data path.
 #include "tcgen05.cuh"
 
+#include <cooperative_groups.h>
+
 namespace qs3 {
 namespace {
 
@@ -88,6 +90,101 @@ tensor_peak_kernel(int kind, uint32_t n, uint32_t iters, uint32_t* err)
     }
 }
 
+// The same loop with CTA pairs: a cluster of two CTAs issues cta_group::2 instructions of
+// 256 x n (128 rows of A and n / 2 rows of B from each CTA's shared memory; each CTA's
+// tensor memory receives its 128 rows of the result). Only the first CTA of the pair
+// issues; the other one provides its shared and tensor memory.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+tensor_peak_pair_kernel(int kind, uint32_t n, uint32_t iters, uint32_t* err)
+{
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t cta_rank = cluster.block_rank();
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* a_tile = smem;
+    uint8_t* b_tile = smem + kTileBytes;                 // n / 2 <= 128 rows
+    uint8_t* sf_tile = b_tile + 2 * kTileBytes;
+    uint64_t* done_bar = reinterpret_cast<uint64_t*>(sf_tile + 1024);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    uint32_t x = 0x9e3779b9u * (blockIdx.x + 1) + threadIdx.x;
+    for (uint32_t i = threadIdx.x; i < 3 * kTileBytes / 4; i += blockDim.x) {
+        x = x * 1664525u + 1013904223u;
+        reinterpret_cast<uint32_t*>(smem)[i] = x & 0x37373737u;
+    }
+    for (uint32_t i = threadIdx.x; i < 512; i += blockDim.x)
+        sf_tile[i] = 0x38;
+    if (threadIdx.x == 0) {
+        mbar_init(done_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    cluster.sync(); // both CTAs are resident before the paired allocation
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster.sync();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (cta_rank == 0 && threadIdx.x == 0) {
+        const uint32_t nm = ((n >> 3) << 17) | ((256u >> 4) << 24);
+        const uint32_t idesc = kind == PROBE_BF16 ? ((1u << 4) | (1u << 7) | (1u << 10) | nm)
+            : kind == PROBE_FP8                  ? ((1u << 4) | nm)
+                                                 : ((1u << 7) | (1u << 10) | nm);
+        const uint64_t da = operand_desc(smem_u32(a_tile));
+        const uint64_t db = operand_desc(smem_u32(b_tile));
+        const uint32_t sfa = tmem_base + 256, sfb = tmem_base + 272;
+        if (kind == PROBE_NVFP4) {
+            for (uint32_t c = 0; c < 12; ++c)
+                asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(sfa + 4 * c),
+                             "l"(scale_desc(smem_u32(sf_tile)))
+                             : "memory");
+        }
+        for (uint32_t it = 0; it < iters; ++it) {
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                const uint32_t acc = (it | j) != 0 ? 1u : 0u;
+                if (kind == PROBE_BF16)
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
+                                 "l"(da + 2 * j), "l"(db + 2 * j), "r"(idesc), "r"(acc)
+                                 : "memory");
+                else if (kind == PROBE_FP8)
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                 "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
+                                 "l"(da + 2 * j), "l"(db + 2 * j), "r"(idesc), "r"(acc)
+                                 : "memory");
+                else
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                 "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X"
+                                 " [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_base),
+                                 "l"(da + 2 * j), "l"(db + 2 * j), "r"(idesc), "r"(acc), "r"(sfa), "r"(sfb)
+                                 : "memory");
+            }
+        }
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                         smem_u32(done_bar))
+                     : "memory");
+        mbar_wait<true>(done_bar, 0, abort_flag, err, 0x53000002u);
+    }
+    tc_fence_before();
+    cluster.sync(); // the pair's tensor memory is idle in both CTAs
+    if (threadIdx.x < 32) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
+                     : "memory");
+    }
+}
+
 } // namespace
 } // namespace qs3
 
@@ -102,8 +199,10 @@ extern "C" qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, u
     qsfi_status status = activate_context(ctx);
     if (status != QSFI_STATUS_OK)
         return status;
-    if (kind > 2 || n < 16 || n > 256 || n % 16 != 0 || iters == 0 || iters > (1u << 22))
-        return set_invalid_arg(ctx, "peak probe: kind in {0,1,2}, n a multiple of 16 in [16, 256], iters in [1, 2^22]");
+    const bool pair = (kind & 16u) != 0; // + 16: CTA pairs issuing cta_group::2 instructions of 256 x n
+    kind &= ~16u;
+    if (kind > 2 || n < 16 || n > 256 || n % 16 != 0 || iters == 0 || iters > (1u << 22) || (pair && n % 32 != 0))
+        return set_invalid_arg(ctx, "peak probe: kind in {0,1,2} (+16), n a multiple of 16 in [16, 256], iters in [1, 2^22]");
     int dev = 0, sms = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err == cudaSuccess)
@@ -112,6 +211,11 @@ extern "C" qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, u
     if (err == cudaSuccess)
         err = cudaFuncSetAttribute(tensor_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(smem));
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(tensor_peak_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(smem));
+    if (pair)
+        sms &= ~1; // whole pairs only
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     if (err == cudaSuccess)
         err = cudaEventCreate(&e0);
@@ -120,9 +224,15 @@ extern "C" qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, u
     if (err != cudaSuccess)
         return set_cuda_error(ctx, err, "peak probe setup");
     uint32_t* errw = device_error_word();
-    tensor_peak_kernel<<<sms, 128, smem, ctx->stream>>>(static_cast<int>(kind), n, 64, errw); // warm-up
+    const auto launch = [&](uint32_t count) {
+        if (pair)
+            tensor_peak_pair_kernel<<<sms, 128, smem, ctx->stream>>>(static_cast<int>(kind), n, count, errw);
+        else
+            tensor_peak_kernel<<<sms, 128, smem, ctx->stream>>>(static_cast<int>(kind), n, count, errw);
+    };
+    launch(64); // warm-up
     cudaEventRecord(e0, ctx->stream);
-    tensor_peak_kernel<<<sms, 128, smem, ctx->stream>>>(static_cast<int>(kind), n, iters, errw);
+    launch(iters);
     cudaEventRecord(e1, ctx->stream);
     note_launch(2);
     err = cudaEventSynchronize(e1);
@@ -135,7 +245,8 @@ extern "C" qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, u
         return set_cuda_error(ctx, err, "peak probe");
     // K elements per instruction: 32 bytes of K -> 16 bf16, 32 fp8, 64 fp4
     const double k_per_mma = kind == 0 ? 16.0 : kind == 1 ? 32.0 : 64.0;
-    const double flops = 2.0 * 128.0 * n * k_per_mma * 4.0 * iters * sms;
+    // a pair instruction is 256 x n and is issued by every second CTA
+    const double flops = 2.0 * (pair ? 256.0 * 0.5 : 128.0) * n * k_per_mma * 4.0 * iters * sms;
     *tflops = flops / (static_cast<double>(ms) * 1e-3) / 1e12;
     return QSFI_STATUS_OK;
 }

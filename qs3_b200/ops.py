@@ -547,9 +547,12 @@ def profile_end(ctx: Context):
 PEAK_KINDS = {"bf16": 0, "fp8": 1, "nvfp4": 2}
 
 
-def tensor_peak_probe(ctx: Context, kind: str = "nvfp4", n: int = 256, iters: int = 20000) -> float:
+def tensor_peak_probe(ctx: Context, kind: str = "nvfp4", n: int = 256, iters: int = 20000,
+                      pair: bool = False) -> float:
     """Dense TFLOP/s of back-to-back ``tcgen05.mma`` (128 x n tiles, operands resident in
-    shared memory) on every SM: the tensor-pipe ceiling for one operand format."""
+    shared memory) on every SM: the tensor-pipe ceiling for one operand format. ``pair``:
+    CTA pairs issuing ``cta_group::2`` instructions of 256 x n instead."""
     out = C.c_double(0.0)
-    ctx.check(ctx._lib.qs3_tensor_peak_probe(ctx.handle, PEAK_KINDS[kind], n, iters, C.byref(out)))
+    ctx.check(ctx._lib.qs3_tensor_peak_probe(ctx.handle, PEAK_KINDS[kind] + (16 if pair else 0), n, iters,
+                                             C.byref(out)))
     return float(out.value)
