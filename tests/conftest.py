@@ -24,3 +24,12 @@ def golden():
     import json
     with open(os.path.join(ROOT, "tests", "golden", "reference_cases.json")) as f:
         return json.load(f)
+
+
+@pytest.fixture(scope="session")
+def seeded():
+    """Committed CPU-oracle vectors of small seeded layers (tests/golden/make_golden.py)."""
+    import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", "seeded_cases.npz")
+    with np.load(path) as z:
+        return {k: z[k] for k in z.files}

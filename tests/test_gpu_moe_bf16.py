@@ -147,3 +147,33 @@ def test_whole_layer_matches_oracle(ops, oracle, cfg):
     if s:
         ref = oracle.shared_expert_bf16(d["hidden"], d["sh_gate_up"], d["sh_down"], d["sh_gate"], ref)
     _check(to_np(out), ref)
+
+
+@pytest.mark.parametrize("name,shape", [("tiny_bf16", (0, 16, 256, 8, 2, 128)),
+                                        ("small_bf16", (1, 48, 128, 16, 4, 64))])
+def test_committed_seeded_vectors(ops, seeded, name, shape):
+    """Whole bf16 layer against the committed fixtures: expert ids, counts, indptr and the
+    permutation bit-exact, output rel-L2 <= 1e-2 (the tiny case is the CPU-runnable
+    configuration of the benchmark list: 16 tokens, 8 experts, top-2, seed 0)."""
+    seed, t, h, e, k, i = shape
+    d = make_moe_inputs(seed, t, h, e, i)
+    ctx = ops.Context()
+    plan = ops.MoePlan(ctx, ops.MoePlanConfig(max_num_tokens=t, hidden_size=h, intermediate_size=i,
+                                              num_experts=e, top_k=k))
+    ws = torch.zeros(plan.layer_workspace_size(t, 0), dtype=torch.uint8, device="cuda")
+    out = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+    ids_t = torch.empty((t, k), dtype=torch.int32, device="cuda")
+    w_t = torch.empty((t, k), dtype=torch.float32, device="cuda")
+    ops.moe_layer_execute(plan, to_dev(d["hidden"]), to_dev(d["router"]), to_dev(d["gate_up"]),
+                          to_dev(d["down"]), out, ws, topk_ids=ids_t, topk_weights=w_t)
+    torch.cuda.synchronize()
+    assert ctx.read_device_error() == 0
+    assert np.array_equal(to_np(ids_t), seeded[f"{name}/ids"])
+    assert np.allclose(to_np(w_t), seeded[f"{name}/weights"], atol=1e-5, rtol=0)
+    counts, indptr, route_rows, row_tokens, _ = (to_np(x) for x in plan.routing_tables(ws, t))
+    assert np.array_equal(counts, seeded[f"{name}/counts"])
+    assert np.array_equal(indptr, seeded[f"{name}/indptr"])
+    assert np.array_equal(route_rows, seeded[f"{name}/route_rows"])
+    assert np.array_equal(row_tokens, seeded[f"{name}/row_tokens"])
+    assert rel_l2(to_np(out), seeded[f"{name}/out"]) <= 1e-2
+    assert max_abs(to_np(out), seeded[f"{name}/out"]) <= 2.0 ** -6 * np.max(np.abs(f32(seeded[f"{name}/out"])))

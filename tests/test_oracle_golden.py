@@ -208,3 +208,18 @@ def test_fp8_moe_matches_dequantised_float64(oracle):
                           for v in act], np.float64) * float(s)
             want[tok] += float(w[tok, j]) * (dn_d[ex] @ q)
     assert np.linalg.norm(out - want) / np.linalg.norm(want) < 5e-3
+
+
+def test_seeded_golden_vectors_are_reproduced(oracle, seeded):
+    """The committed vectors are what the oracle computes today (bit for bit)."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "make_golden", os.path.join(os.path.dirname(__file__), "golden", "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    import helpers
+    for name, args in mg.CASES.items():
+        case = mg.build_case(oracle, helpers, *args)
+        for key, val in case.items():
+            assert np.array_equal(np.asarray(val), seeded[f"{name}/{key}"]), (name, key)
