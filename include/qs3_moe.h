@@ -532,6 +532,22 @@ qsfi_status qs3_moe_ep_finish_workspace_size(
 );
 qsfi_status qs3_moe_ep_finish(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_ep_finish_desc* desc);
 
+/* Dispatch by pulling: every rank keeps the outputs of qs3_moe_ep_route (codes, scales, ids,
+ * weights of its own tokens) in one peer-mapped block; this call copies up to four
+ * segments of the blocks of ALL ranks into local buffers laid out [num_ranks, segment] with
+ * plain peer loads over NVLink, i.e. an all-gather without a collective library. The
+ * caller orders it after every rank finished writing its block (a barrier on the stream)
+ * and does not let a rank overwrite its block before all ranks ran this call. */
+typedef struct {
+    const qsfi_device_ptr* peer_blocks; /* [num_ranks] base of rank r's block as mapped on this device */
+    uint64_t segment_offset[4];         /* byte offset of segment j inside a block, multiple of 16 */
+    uint64_t segment_bytes[4];          /* bytes of segment j per rank, multiple of 16 */
+    qsfi_device_ptr dst[4];             /* local destination of segment j, num_ranks * segment_bytes[j] bytes */
+    uint32_t num_ranks;                 /* <= 32 */
+    uint32_t num_segments;              /* <= 4 */
+} qs3_moe_ep_pull_tokens_desc;
+qsfi_status qs3_moe_ep_pull_tokens(qsfi_context* ctx, const qs3_moe_ep_pull_tokens_desc* desc);
+
 /* Routing tables of the last execute on this workspace, for parity checks:
  * copies of counts[E_local], indptr[E_local+1], route_rows[T*K] (-1: not local),
  * row_tokens[R_local], row_scales[R_local] (upstream qsfi_moe.cu:26-31). Device

@@ -221,6 +221,12 @@ class MoeFp8ExecuteDesc(C.Structure):
                 ("workspace", Tensor1), ("num_tokens", C.c_uint32)]
 
 
+class MoeEpPullTokensDesc(C.Structure):
+    _fields_ = [("peer_blocks", _P(C.c_void_p)), ("segment_offset", C.c_uint64 * 4),
+                ("segment_bytes", C.c_uint64 * 4), ("dst", C.c_void_p * 4), ("num_ranks", C.c_uint32),
+                ("num_segments", C.c_uint32)]
+
+
 _SIGNATURES = {
     "qsfi_status_string": (C.c_char_p, [C.c_int]),
     "qsfi_context_create": (C.c_int, [_P(ContextDesc), _P(C.c_void_p)]),
@@ -259,6 +265,7 @@ _SIGNATURES = {
     "qs3_moe_ep_finish_workspace_size": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
                                                    _P(C.c_size_t)]),
     "qs3_moe_ep_finish": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeEpFinishDesc)]),
+    "qs3_moe_ep_pull_tokens": (C.c_int, [C.c_void_p, _P(MoeEpPullTokensDesc)]),
     "qs3_moe_read_device_error": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
     "qs3_moe_launch_count": (C.c_uint64, []),
     "qs3_moe_profile_begin": (C.c_int, [C.c_void_p]),

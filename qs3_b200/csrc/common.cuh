@@ -140,6 +140,14 @@ struct EpPullParams {
     uint32_t num_tokens, top_k, hidden_size, num_ranks, my_rank, experts_per_rank;
 };
 cudaError_t launch_ep_pull_combine(const EpPullParams& p, cudaStream_t stream);
+struct EpPullTokensParams {
+    const uint8_t* peer[32];    // every rank's symmetric token block (peer-mapped)
+    uint64_t seg_offset[4];     // byte offset of segment j inside a token block
+    uint64_t seg_bytes[4];      // bytes of segment j per rank (multiple of 16)
+    uint8_t* dst[4];            // local buffer of segment j: [num_ranks, seg_bytes[j]]
+    uint32_t num_ranks, num_segments;
+};
+cudaError_t launch_ep_pull_tokens(const EpPullTokensParams& p, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
 cudaError_t launch_ep_rank_routes(int32_t* rows, float* weights, uint32_t tokens, uint32_t ranks,
                                   cudaStream_t stream);

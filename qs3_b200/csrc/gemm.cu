@@ -247,8 +247,8 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     uint8_t* a_panel = smem;
     uint8_t* sfa_stage = a_panel + kb_count * kTileBytes;
     uint8_t* ring = sfa_stage + kb_count * kSfBytes;
-    uint8_t* staging = ring + stages * kbs * kAsStageBytes; // 32 KB output tile, only with p.tma_store
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + (p.tma_store ? 2 * kTileBytes : 0));
+    uint8_t* staging = ring + stages * kbs * kAsStageBytes; // two 32 KB output tiles, only with p.tma_store
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + (p.tma_store ? 4 * kTileBytes : 0));
     uint64_t* empty_bar = full_bar + kAsMaxStages;
     uint64_t* acc_full = empty_bar + kAsMaxStages;
     uint64_t* acc_empty = acc_full + 2;
@@ -414,30 +414,35 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 // end are padding rows of the same expert, rows past the tensor are clipped.
                 const uint32_t quad = warp & 3, half = warp >> 2;
                 const uint32_t r = quad * 32 + lane;
-                if (warp == 0 && lane == 0) // the previous tile's stores must have left smem
-                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                uint8_t* stage_buf = staging + (local & 1) * 2 * kTileBytes; // two staging tiles alternate
+                if (warp == 0 && lane == 0) // the store issued two tiles ago must have left this buffer
+                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                 float scale = p.alpha == 0.0f ? 1.0f : p.alpha;
                 if (p.group_scale != nullptr)
                     scale *= p.group_scale[expert];
-                uint8_t* row_smem = staging + half * kTileBytes + r * 128;
+                // this warp's 64 columns in one go, then the accumulator is free again
+                uint32_t v[4][16];
 #pragma unroll
-                for (uint32_t c = 0; c < 4; ++c) {
-                    uint32_t v[16];
-                    tc_ld16(tmem_base + buf * kBN + ((quad * 32) << 16) + half * 64 + c * 16, v);
-                    tc_ld_wait();
-                    uint32_t w[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        w[i] = pack_bf16x2(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
-                    *reinterpret_cast<uint4*>(row_smem + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-                    *reinterpret_cast<uint4*>(row_smem + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-                }
-                // accumulator is free again; publish the staged tile to the async proxy
+                for (uint32_t c = 0; c < 4; ++c)
+                    tc_ld16(tmem_base + buf * kBN + ((quad * 32) << 16) + half * 64 + c * 16, v[c]);
+                tc_ld_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0)
                     mbar_arrive(&acc_empty[buf]);
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                uint8_t* row_smem = stage_buf + half * kTileBytes + r * 128;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        w[i] = pack_bf16x2(__uint_as_float(v[c][2 * i]) * scale,
+                                           __uint_as_float(v[c][2 * i + 1]) * scale);
+                    *reinterpret_cast<uint4*>(row_smem + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(row_smem + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+                // publish the staged tile to the async proxy
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (warp == 0 && lane == 0) {
@@ -446,7 +451,7 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                         if (n0 + h2 * 64 < static_cast<int>(p.n))
                             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                                              reinterpret_cast<uint64_t>(&map_o)),
-                                         "r"(smem_u32(staging + h2 * kTileBytes)), "r"(n0 + h2 * 64), "r"(row0)
+                                         "r"(smem_u32(stage_buf + h2 * kTileBytes)), "r"(n0 + h2 * 64), "r"(row0)
                                          : "memory");
                     }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -610,7 +615,7 @@ cudaError_t launch_astat(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
     // two k-blocks per ring stage: one barrier round trip of the single issuing thread
     // costs about as much as four 128x128x64 MMAs, so stages carry eight of them
     const uint32_t kbs = tp.k_blocks % 2 == 0 ? 2u : 1u;
-    const size_t staging = tp.tma_store ? 2 * kTileBytes : 0;
+    const size_t staging = tp.tma_store ? 4 * kTileBytes : 0;
     uint32_t stages = static_cast<uint32_t>((kSmemBudget - panel - staging) / (kbs * kAsStageBytes));
     stages = std::min<uint32_t>(stages, kAsMaxStages);
     const size_t smem = panel + staging + static_cast<size_t>(stages) * kbs * kAsStageBytes + 1024 + 512;

@@ -1552,6 +1552,37 @@ qsfi_status qs3_moe_ep_finish(qsfi_context* ctx, const qsfi_moe_plan* plan, cons
     return QSFI_STATUS_OK;
 }
 
+qsfi_status qs3_moe_ep_pull_tokens(qsfi_context* ctx, const qs3_moe_ep_pull_tokens_desc* d)
+{
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (d == nullptr || d->peer_blocks == nullptr)
+        return set_invalid_arg(ctx, "desc/peer_blocks is null");
+    if (d->num_ranks == 0 || d->num_ranks > 32 || d->num_segments == 0 || d->num_segments > 4)
+        return set_invalid_arg(ctx, "expert-parallel pull: 1..32 ranks and 1..4 segments");
+    EpPullTokensParams p {};
+    p.num_ranks = d->num_ranks;
+    p.num_segments = d->num_segments;
+    for (uint32_t r = 0; r < d->num_ranks; ++r) {
+        if (d->peer_blocks[r] == nullptr || !aligned16(d->peer_blocks[r]))
+            return set_invalid_arg(ctx, "expert-parallel pull: peer blocks must be non-null and 16-byte aligned");
+        p.peer[r] = static_cast<const uint8_t*>(d->peer_blocks[r]);
+    }
+    for (uint32_t j = 0; j < d->num_segments; ++j) {
+        if (d->dst[j] == nullptr || !aligned16(d->dst[j]) || d->segment_offset[j] % 16 != 0
+            || d->segment_bytes[j] % 16 != 0)
+            return set_invalid_arg(ctx, "expert-parallel pull: segments must be 16-byte aligned and sized");
+        p.seg_offset[j] = d->segment_offset[j];
+        p.seg_bytes[j] = d->segment_bytes[j];
+        p.dst[j] = static_cast<uint8_t*>(d->dst[j]);
+    }
+    return set_cuda_error(ctx, launch_ep_pull_tokens(p, ctx->stream), "qs3_moe_ep_pull_tokens");
+}
+
 // ---- FP8 block-scaled path ------------------------------------------------------------
 
 qsfi_status qs3_fp8_quantize_weight(qsfi_context* ctx, const qs3_fp8_quantize_weight_desc* d)

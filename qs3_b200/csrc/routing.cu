@@ -385,27 +385,29 @@ template <typename T> T* carve(char* base, size_t& offset, size_t count)
 // exchanging the partial sums first and then running combine_kernel on the copies.
 __global__ void __launch_bounds__(256) ep_pull_combine_kernel(EpPullParams p)
 {
-    const uint32_t token = blockIdx.x * 8 + (threadIdx.x >> 5);
-    const uint32_t lane = threadIdx.x & 31;
-    if (token >= p.num_tokens)
-        return;
+    __shared__ uint32_t s_active;
+    __shared__ float s_dot[8];
+    const uint32_t token = blockIdx.x;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t vec_per_row = p.hidden_size / 8;
 
     // which ranks hold a partial sum for this token
-    uint32_t mine = 0;
-    if (lane < p.top_k) {
-        const int id = p.topk_ids[static_cast<size_t>(token) * p.top_k + lane];
-        if (id >= 0 && static_cast<uint32_t>(id) / p.experts_per_rank < p.num_ranks)
-            mine = 1u << (static_cast<uint32_t>(id) / p.experts_per_rank);
+    if (threadIdx.x < 32) {
+        uint32_t mine = 0;
+        if (lane < p.top_k) {
+            const int id = p.topk_ids[static_cast<size_t>(token) * p.top_k + lane];
+            if (id >= 0 && static_cast<uint32_t>(id) / p.experts_per_rank < p.num_ranks)
+                mine = 1u << (static_cast<uint32_t>(id) / p.experts_per_rank);
+        }
+        const uint32_t any = __reduce_or_sync(0xffffffffu, mine);
+        if (lane == 0)
+            s_active = any;
     }
-    const uint32_t active = __reduce_or_sync(0xffffffffu, mine);
-
-    float gate = 0.0f;
+    float dot = 0.0f;
     if (p.shared_out != nullptr) {
         const uint4* x = reinterpret_cast<const uint4*>(p.hidden) + static_cast<size_t>(token) * vec_per_row;
         const uint4* w = reinterpret_cast<const uint4*>(p.gate_w);
-        float dot = 0.0f;
-        for (uint32_t i = lane; i < vec_per_row; i += 32) {
+        for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
             const uint4 xv = x[i], wv = w[i];
             const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
             const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
@@ -418,25 +420,47 @@ __global__ void __launch_bounds__(256) ep_pull_combine_kernel(EpPullParams p)
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
             dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0)
+            s_dot[warp] = dot;
+    }
+    __syncthreads();
+    const uint32_t active = s_active;
+    float gate = 0.0f;
+    if (p.shared_out != nullptr) {
+        dot = 0.0f;
+        for (uint32_t w = 0; w < blockDim.x / 32; ++w)
+            dot += s_dot[w];
         gate = sigmoid_fast(dot);
     }
 
     const size_t row = static_cast<size_t>(p.my_rank) * p.num_tokens + token;
     uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
-    for (uint32_t i = lane; i < vec_per_row; i += 32) {
+    for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
             acc[j] = 0.0f;
-        for (uint32_t r = 0; r < p.num_ranks; ++r) {
-            if (!((active >> r) & 1u))
-                continue;
-            const uint4 v = reinterpret_cast<const uint4*>(p.peer[r])[row * vec_per_row + i];
-            const uint32_t vs[4] = { v.x, v.y, v.z, v.w };
+        // the peer loads of up to eight ranks are issued together: NVLink latency overlaps
+        for (uint32_t r0 = 0; r0 < p.num_ranks; r0 += 8) {
+            uint4 v[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                acc[2 * j] += bf16_bits_to_f32(vs[j] & 0xffffu);
-                acc[2 * j + 1] += bf16_bits_to_f32(vs[j] >> 16);
+            for (uint32_t q = 0; q < 8; ++q) {
+                const uint32_t r = r0 + q;
+                v[q] = (r < p.num_ranks && ((active >> r) & 1u))
+                    ? reinterpret_cast<const uint4*>(p.peer[r])[row * vec_per_row + i]
+                    : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (uint32_t q = 0; q < 8; ++q) {
+                const uint32_t r = r0 + q;
+                if (r >= p.num_ranks || !((active >> r) & 1u))
+                    continue;
+                const uint32_t vs[4] = { v[q].x, v[q].y, v[q].z, v[q].w };
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[2 * j] += bf16_bits_to_f32(vs[j] & 0xffffu);
+                    acc[2 * j + 1] += bf16_bits_to_f32(vs[j] >> 16);
+                }
             }
         }
         if (p.shared_out != nullptr) {
@@ -458,11 +482,50 @@ __global__ void __launch_bounds__(256) ep_pull_combine_kernel(EpPullParams p)
     }
 }
 
+// dst_j[r * bytes_j ...] = peer block r, segment j: every rank copies the token blocks of all
+// ranks (its own included) out of the ranks' symmetric buffers with plain 16-byte peer loads.
+// Grid: (chunks, ranks, segments).
+__global__ void __launch_bounds__(256) ep_pull_tokens_kernel(EpPullTokensParams p)
+{
+    const uint32_t r = blockIdx.y, seg = blockIdx.z;
+    const uint64_t vecs = p.seg_bytes[seg] / 16;
+    const uint4* src = reinterpret_cast<const uint4*>(p.peer[r] + p.seg_offset[seg]);
+    uint4* dst = reinterpret_cast<uint4*>(p.dst[seg] + static_cast<uint64_t>(r) * p.seg_bytes[seg]);
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i0 = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < vecs; i0 += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (i0 + q * stride < vecs)
+                v[q] = src[i0 + q * stride];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (i0 + q * stride < vecs)
+                dst[i0 + q * stride] = v[q];
+    }
+}
+
 } // namespace
 
 cudaError_t launch_ep_pull_combine(const EpPullParams& p, cudaStream_t stream)
 {
-    ep_pull_combine_kernel<<<(p.num_tokens + 7) / 8, 256, 0, stream>>>(p);
+    if (p.num_tokens == 0)
+        return cudaSuccess;
+    const uint32_t threads = std::min(256u, std::max(32u, (p.hidden_size / 8 + 31) / 32 * 32));
+    ep_pull_combine_kernel<<<p.num_tokens, threads, 0, stream>>>(p);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_pull_tokens(const EpPullTokensParams& p, cudaStream_t stream)
+{
+    if (p.num_ranks == 0 || p.num_segments == 0)
+        return cudaSuccess;
+    uint64_t largest = 0;
+    for (uint32_t j = 0; j < p.num_segments; ++j)
+        largest = std::max<uint64_t>(largest, p.seg_bytes[j]);
+    const uint32_t chunks = static_cast<uint32_t>(std::min<uint64_t>(64, std::max<uint64_t>(1, largest / 16 / 1024)));
+    ep_pull_tokens_kernel<<<dim3(chunks, p.num_ranks, p.num_segments), 256, 0, stream>>>(p);
     note_launch();
     return cudaGetLastError();
 }

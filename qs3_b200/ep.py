@@ -9,17 +9,21 @@ Per layer and rank (T tokens per rank, n ranks):
                With top-10 routing a token already reaches 5.9 of 8 ranks on average, so
                replicating it to all ranks costs at most 1/0.74 of a de-duplicated
                all-to-all and needs no host-side count exchange or synchronisation.
+               "pull": the route outputs live in a peer-mapped block; after a barrier over the
+               ranks' signal pads every rank copies all blocks with plain peer loads
+               (qs3_moe_ep_pull_tokens). "nccl": one coalesced group of all-gathers.
   3. experts   the rank's experts over all n*T tokens; routes to other ranks' experts are
                skipped (local_expert_offset), so row t holds the rank's partial sum
-  4. combine   "pull": after a one-element all-reduce as barrier, the owner of a token reads
+  4. combine   "pull": after a second barrier, the owner of a token reads
                the partial sums straight out of the other ranks' buffers (symmetric memory,
                plain peer loads over NVLink) and only for ranks the token has a route to;
                "nccl": all-to-all of the partial sums back to the token owners
-  5. finish    shared expert (issued while the exchanges run) + sum of the n partials in
+  5. finish    shared expert (on a side stream while the dispatch runs) + sum of the n partials in
                ascending rank order in f32 + sigmoid-gated shared term, one bf16 rounding
 
-The collectives are NCCL over NVLink/NVSwitch through ``torch.distributed`` on a
-separate communication stream; compute kernels never wait on another rank themselves.
+The barriers are those of ``torch.distributed._symmetric_memory`` (NCCL collectives through
+``torch.distributed`` on a separate communication stream when peer mapping is unavailable);
+the kernels of this library never wait on another rank themselves.
 The compute steps are behind a small backend interface so that the exchange logic can
 be exercised on CPU ranks (gloo) with a stand-in backend supplied by the tests.
 """
@@ -89,6 +93,20 @@ class CudaBackend:
         ctx.check(ctx._lib.qs3_moe_ep_finish_workspace_size(ctx.handle, self.plan.handle, t, world,
                                                             cfg.shared_inter, C.byref(n)))
         self.ws_finish = torch.empty(n.value, dtype=u8, device=dev)
+
+    def bind_route_outputs(self, packed, scale, ids, wts):
+        """Let ``route`` write into caller-owned tensors (a peer-mapped block)."""
+        self.packed, self.scale, self.ids, self.wts = packed, scale, ids, wts
+
+    def pull_tokens(self, peer_blocks, offsets, sizes, dsts):
+        """All-gather by peer loads: segment j of every rank's block -> dsts[j][rank]."""
+        d = capi.MoeEpPullTokensDesc()
+        self._peer_blocks = (self.C.c_void_p * len(peer_blocks))(*peer_blocks)
+        d.peer_blocks = self._peer_blocks
+        for j, (off, size, dst) in enumerate(zip(offsets, sizes, dsts)):
+            d.segment_offset[j], d.segment_bytes[j], d.dst[j] = off, size, dst.data_ptr()
+        d.num_ranks, d.num_segments = len(peer_blocks), len(offsets)
+        self.ctx.check(self.ctx._lib.qs3_moe_ep_pull_tokens(self.ctx.handle, self.C.byref(d)))
 
     def route(self, hidden):
         d = capi.MoeEpRouteDesc()
@@ -166,7 +184,8 @@ class CudaBackend:
 class ExpertParallelLayer:
     """Drives one layer across the ranks of the default process group."""
 
-    def __init__(self, ctx, data, rank: int, world: int, backend=None, group=None, combine="auto"):
+    def __init__(self, ctx, data, rank: int, world: int, backend=None, group=None, combine="auto",
+                 dispatch="auto"):
         self.rank, self.world, self.group = rank, world, group
         self.data = data
         cfg = data.cfg
@@ -188,20 +207,36 @@ class ExpertParallelLayer:
         # when that cannot be set up the partial sums are exchanged with an NCCL all-to-all.
         self.peer_ptrs = None
         self.partial = None
+        self.token_block = None
         if self.cuda and world > 1 and combine != "nccl":
             try:
                 import torch.distributed._symmetric_memory as symm
-                self.partial = symm.empty((n * t, h), dtype=bf, device=dev)
-                hdl = symm.rendezvous(self.partial, dist.group.WORLD if group is None else group)
-                self.peer_ptrs = [int(ptr) for ptr in hdl.buffer_ptrs]
+                # one peer-mapped block per rank: [partial sums | codes | scales | ids | weights]
+                sizes = [n * t * h * 2, t * (h // 2), t * (h // 16), t * k * 4, t * k * 4]
+                offs, total = [], 0
+                for sz in sizes:
+                    offs.append(total)
+                    total += (sz + 255) // 256 * 256
+                self._sym = symm.empty((total,), dtype=u8, device=dev)
+                hdl = symm.rendezvous(self._sym, dist.group.WORLD if group is None else group)
                 self._symm_handle = hdl
+                base = [int(ptr) for ptr in hdl.buffer_ptrs]
+                self.partial = self._sym[offs[0]:offs[0] + sizes[0]].view(bf).view(n * t, h)
+                self.peer_ptrs = [b + offs[0] for b in base]
+                if dispatch != "nccl" and hasattr(self.backend, "bind_route_outputs"):
+                    seg = lambda j, dt, shape: self._sym[offs[j]:offs[j] + sizes[j]].view(dt).view(shape)
+                    self.backend.bind_route_outputs(seg(1, u8, (t, h // 2)), seg(2, u8, (t, h // 16)),
+                                                    seg(3, i32, (t, k)), seg(4, f32, (t, k)))
+                    self.token_block = dict(peers=base, offsets=offs[1:], sizes=sizes[1:])
             except Exception as exc:  # no peer mapping on this system: exchange copies instead
                 if combine == "pull":
                     raise
                 self.partial, self.peer_ptrs, self.combine_note = None, None, f"nccl ({type(exc).__name__})"
+                self.token_block = None
         if self.partial is None:
             self.partial = torch.empty((n * t, h), dtype=bf, device=dev)
         self.combine_mode = "pull" if self.peer_ptrs is not None else "nccl"
+        self.dispatch_mode = "pull" if self.token_block is not None else "nccl"
         self.flag = torch.zeros(1, dtype=f32, device=dev) if self.cuda else None
         self.recv = torch.empty((n, t, h), dtype=bf, device=dev)        # partial sums of my tokens, per rank
         self.out = torch.empty((t, h), dtype=bf, device=dev)
@@ -222,6 +257,14 @@ class ExpertParallelLayer:
             for dst, src in pairs:
                 dist.all_gather_into_tensor(dst, src, group=self.group)
 
+    def _dispatch_pull(self):
+        """Barrier over the ranks' signal pads (every rank's route outputs are in its block),
+        then copy all blocks here with peer loads."""
+        tb = self.token_block
+        self._symm_handle.barrier(channel=0)
+        self.backend.pull_tokens(tb["peers"], tb["offsets"], tb["sizes"],
+                                 (self.g_packed, self.g_scale, self.g_ids, self.g_wts))
+
     def _combine(self):
         dist.all_to_all_single(self.recv.view(self.world * self.cfg.tokens, -1), self.partial, group=self.group)
 
@@ -238,15 +281,31 @@ class ExpertParallelLayer:
             b.finish(hidden, self.recv, out)
             return out
         main = torch.cuda.current_stream()
-        self.ev[0].record(main)
-        with torch.cuda.stream(self.comm):
-            self.comm.wait_event(self.ev[0])
-            self._dispatch(packed, scale, ids, wts)
-            self.ev[1].record(self.comm)
-        b.shared_expert(hidden)              # overlaps the dispatch
-        main.wait_event(self.ev[1])
         pull = self.combine_mode == "pull"
+        self.ev[0].record(main)
+        if self.dispatch_mode == "pull":
+            # shared expert on the side stream while barrier + peer copies run on the main one
+            self.comm.wait_event(self.ev[0])
+            self.ctx.set_stream(self.comm.cuda_stream)
+            b.shared_expert(hidden)
+            self.ctx.set_stream(main.cuda_stream)
+            self.ev[1].record(self.comm)
+            self._dispatch_pull()
+        else:
+            with torch.cuda.stream(self.comm):
+                self.comm.wait_event(self.ev[0])
+                self._dispatch(packed, scale, ids, wts)
+                self.ev[1].record(self.comm)
+            b.shared_expert(hidden)              # overlaps the dispatch
+            main.wait_event(self.ev[1])
         b.experts(self.g_packed, self.g_scale, self.g_ids, self.g_wts, self.partial, skip_empty=pull)
+        if pull and self.dispatch_mode == "pull":
+            # every rank's partial sums are complete once all ranks passed this barrier; the
+            # barrier of the next step's dispatch keeps anyone from overwriting a buffer early
+            self._symm_handle.barrier(channel=1)
+            main.wait_event(self.ev[1])
+            b.finish_pull(hidden, self.peer_ptrs, ids, out)
+            return out
         self.ev[2].record(main)
         with torch.cuda.stream(self.comm):
             self.comm.wait_event(self.ev[2])
@@ -283,14 +342,19 @@ class ExpertParallelLayer:
             ev[0].record()
             packed, scale, ids, wts = b.route(hidden)
             ev[1].record()
-            self._dispatch(packed, scale, ids, wts)
+            if self.dispatch_mode == "pull":
+                self._dispatch_pull()
+            else:
+                self._dispatch(packed, scale, ids, wts)
             ev[2].record()
             b.shared_expert(hidden)
             ev[3].record()
             pull = self.combine_mode == "pull"
             b.experts(self.g_packed, self.g_scale, self.g_ids, self.g_wts, self.partial, skip_empty=pull)
             ev[4].record()
-            if pull:
+            if pull and self.dispatch_mode == "pull":
+                self._symm_handle.barrier(channel=1)
+            elif pull:
                 dist.all_reduce(self.flag, group=self.group)
             else:
                 self._combine()
