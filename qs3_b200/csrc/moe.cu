@@ -1317,9 +1317,11 @@ qsfi_status qs3_moe_execute_nvfp4_prepared(qsfi_context* ctx, const qsfi_moe_pla
     Nvfp4Workspace w = carve_nvfp4(static_cast<char*>(d->workspace.data), p, d->num_tokens, false);
     const uint32_t routes = d->num_tokens * p.top_k;
     cudaStream_t st = ctx->stream;
+    stage_mark(st, STAGE_ROUTE_SORT);
     cudaError_t err = launch_route_sort(static_cast<const int32_t*>(d->topk_ids.data),
                                         static_cast<const float*>(d->topk_weights.data), routes, p.top_k,
                                         p.local_expert_offset, p.local_num_experts, w.rt, st);
+    stage_mark(st, STAGE_GATHER);
     if (err == cudaSuccess)
         err = launch_nvfp4_gather_packed(static_cast<const uint8_t*>(d->hidden_packed.data),
                                          static_cast<const uint8_t*>(d->hidden_scale.data), w.rt.route_prows,
@@ -1345,7 +1347,10 @@ qsfi_status qs3_moe_execute_nvfp4_prepared(qsfi_context* ctx, const qsfi_moe_pla
     cp.top_k = p.top_k;
     cp.hidden_size = p.hidden_size;
     cp.skip_empty = (d->flags & 1u) != 0;
-    return set_cuda_error(ctx, launch_combine(cp, st), "qs3_moe_execute_nvfp4_prepared");
+    stage_mark(st, STAGE_COMBINE);
+    err = launch_combine(cp, st);
+    stage_mark(st, STAGE_END);
+    return set_cuda_error(ctx, err, "qs3_moe_execute_nvfp4_prepared");
 }
 
 qsfi_status qs3_moe_ep_finish_workspace_size(qsfi_context* ctx, const qsfi_moe_plan* plan, uint32_t num_tokens,

@@ -248,113 +248,148 @@ gather_words_kernel(const uint32_t* __restrict__ src, const int32_t* __restrict_
 }
 
 // out[t, :] = bf16(sum_k w[t,k] * f32(Y2[prow(t,k), :])) (+ shared-expert term).
-// One block per token, one 8-element chunk of the row per thread and step; k ascending and
-// f32 accumulation as upstream finalize_kernel (qsfi_moe.cu:465-492). Loads of up to four
-// routes are issued together so that their latencies overlap.
-__global__ void __launch_bounds__(256) combine_kernel(CombineParams p)
+// Four tokens per block, 64 threads per token; a thread owns two 8-element chunks of the row
+// per step and issues the loads of up to four routes for both chunks together (eight 16-byte
+// loads in flight), so that tokens with one or two local routes (expert parallelism) still
+// keep the memory system busy. k ascending and f32 accumulation as upstream finalize_kernel
+// (qsfi_moe.cu:465-492).
+constexpr uint32_t kCombineTokens = 4;
+constexpr uint32_t kCombineGroup = 64;
+
+__device__ __forceinline__ void accumulate_row(float* acc, const uint4& v, float w)
 {
-    __shared__ int s_row[32];
-    __shared__ float s_w[32];
-    __shared__ float s_dot[8];
-    __shared__ int s_any;
-    const uint32_t token = blockIdx.x;
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t vs[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += w * bf16_bits_to_f32(vs[j] & 0xffffu);
+        acc[2 * j + 1] += w * bf16_bits_to_f32(vs[j] >> 16);
+    }
+}
+
+__global__ void __launch_bounds__(kCombineTokens* kCombineGroup, 4) combine_kernel(CombineParams p)
+{
+    __shared__ int s_row[kCombineTokens][32];
+    __shared__ float s_w[kCombineTokens][32];
+    __shared__ float s_dot[kCombineTokens][kCombineGroup / 32];
+    __shared__ int s_any[kCombineTokens];
+    const uint32_t group = threadIdx.x / kCombineGroup, gl = threadIdx.x % kCombineGroup;
+    const uint32_t token = blockIdx.x * kCombineTokens + group;
+    const bool live = token < p.num_tokens;
+    const uint32_t lane = threadIdx.x & 31;
     const uint32_t vec_per_row = p.hidden_size / 8;
 
-    if (threadIdx.x < 32) {
+    if (gl < 32) {
+        // the token's routes that have a row here, compacted in ascending k
         int row = -1;
-        if (threadIdx.x < p.top_k) {
-            row = p.route_prows[static_cast<size_t>(token) * p.top_k + threadIdx.x];
-            s_row[threadIdx.x] = row;
-            s_w[threadIdx.x] = p.topk_weights[static_cast<size_t>(token) * p.top_k + threadIdx.x];
+        float wgt = 0.0f;
+        if (live && gl < p.top_k) {
+            row = p.route_prows[static_cast<size_t>(token) * p.top_k + gl];
+            wgt = p.topk_weights[static_cast<size_t>(token) * p.top_k + gl];
         }
-        const int any = __any_sync(0xffffffffu, row >= 0);
-        if (threadIdx.x == 0)
-            s_any = any;
+        const uint32_t valid = __ballot_sync(0xffffffffu, row >= 0);
+        if (row >= 0) {
+            const uint32_t slot = __popc(valid & ((1u << gl) - 1u));
+            s_row[group][slot] = row;
+            s_w[group][slot] = wgt;
+        }
+        if (gl == 0)
+            s_any[group] = __popc(valid);
     }
     float dot = 0.0f;
     if (p.shared_out != nullptr) {
         // gate logit x . w_gate in f32 (upstream computes it as an N = 1 GEMM,
         // src/model.rs:2218-2226)
-        const uint4* x = reinterpret_cast<const uint4*>(p.hidden) + static_cast<size_t>(token) * vec_per_row;
-        const uint4* w = reinterpret_cast<const uint4*>(p.gate_w);
-        for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
-            const uint4 xv = x[i], wv = w[i];
-            const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
-            const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
+        if (live) {
+            const uint4* x = reinterpret_cast<const uint4*>(p.hidden) + static_cast<size_t>(token) * vec_per_row;
+            const uint4* w = reinterpret_cast<const uint4*>(p.gate_w);
+            for (uint32_t i = gl; i < vec_per_row; i += kCombineGroup) {
+                const uint4 xv = x[i], wv = w[i];
+                const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
+                const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                dot += bf16_bits_to_f32(xs[j] & 0xffffu) * bf16_bits_to_f32(ws[j] & 0xffffu);
-                dot += bf16_bits_to_f32(xs[j] >> 16) * bf16_bits_to_f32(ws[j] >> 16);
+                for (int j = 0; j < 4; ++j) {
+                    dot += bf16_bits_to_f32(xs[j] & 0xffffu) * bf16_bits_to_f32(ws[j] & 0xffffu);
+                    dot += bf16_bits_to_f32(xs[j] >> 16) * bf16_bits_to_f32(ws[j] >> 16);
+                }
             }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
             dot += __shfl_xor_sync(0xffffffffu, dot, o);
         if (lane == 0)
-            s_dot[warp] = dot;
+            s_dot[group][gl / 32] = dot;
     }
     __syncthreads();
-    if (p.skip_empty && !s_any)
+    if (!live || (p.skip_empty && !s_any[group]))
         return; // no local route: the row stays unwritten and is never read
     float gate = 0.0f;
     if (p.shared_out != nullptr) {
         dot = 0.0f;
-        for (uint32_t w = 0; w < blockDim.x / 32; ++w) // fixed order: the same sum in every thread
-            dot += s_dot[w];
+#pragma unroll
+        for (uint32_t w = 0; w < kCombineGroup / 32; ++w) // fixed order: the same sum in every thread
+            dot += s_dot[group][w];
         gate = sigmoid_fast(dot);
     }
 
     const uint4* y2 = reinterpret_cast<const uint4*>(p.expert_out);
     uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
-    for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
-        float acc[8];
+    const uint32_t n_valid = static_cast<uint32_t>(s_any[group]);
+    for (uint32_t i0 = gl; i0 < vec_per_row; i0 += 2 * kCombineGroup) {
+        const uint32_t i1 = i0 + kCombineGroup;
+        const bool two = i1 < vec_per_row;
+        float acc0[8], acc1[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            acc[j] = 0.0f;
-        for (uint32_t k0 = 0; k0 < p.top_k; k0 += 4) {
-            uint4 v[4];
+            acc0[j] = acc1[j] = 0.0f;
+        for (uint32_t k0 = 0; k0 < n_valid; k0 += 4) {
+            uint4 v0[4], v1[4];
             float w[4];
             int row[4];
 #pragma unroll
             for (uint32_t q = 0; q < 4; ++q) {
-                row[q] = k0 + q < p.top_k ? s_row[k0 + q] : -1;
-                w[q] = row[q] >= 0 ? s_w[k0 + q] : 0.0f;
-                v[q] = row[q] >= 0 ? y2[static_cast<size_t>(row[q]) * vec_per_row + i] : make_uint4(0, 0, 0, 0);
+                row[q] = k0 + q < n_valid ? s_row[group][k0 + q] : -1;
+                w[q] = row[q] >= 0 ? s_w[group][k0 + q] : 0.0f;
+                const uint4* src = y2 + static_cast<size_t>(row[q] >= 0 ? row[q] : 0) * vec_per_row;
+                v0[q] = row[q] >= 0 ? src[i0] : make_uint4(0, 0, 0, 0);
+                v1[q] = (row[q] >= 0 && two) ? src[i1] : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
             for (uint32_t q = 0; q < 4; ++q) {
                 if (row[q] < 0)
                     continue; // a skipped route adds nothing (not even a signed zero)
-                const uint32_t vs[4] = { v[q].x, v[q].y, v[q].z, v[q].w };
+                accumulate_row(acc0, v0[q], w[q]);
+                accumulate_row(acc1, v1[q], w[q]);
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float* acc = h == 0 ? acc0 : acc1;
+            const uint32_t i = h == 0 ? i0 : i1;
+            if (h == 1 && !two)
+                break;
+            if (p.shared_out != nullptr) {
+                const uint4 sv
+                    = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
+                const uint32_t ss[4] = { sv.x, sv.y, sv.z, sv.w };
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[2 * j] += w[q] * bf16_bits_to_f32(vs[j] & 0xffffu);
-                    acc[2 * j + 1] += w[q] * bf16_bits_to_f32(vs[j] >> 16);
+                    float a0 = acc[2 * j], a1 = acc[2 * j + 1];
+                    if (p.round_before_shared) { // upstream rounds the routed sum to bf16 first
+                        a0 = __bfloat162float(__float2bfloat16(a0));
+                        a1 = __bfloat162float(__float2bfloat16(a1));
+                    }
+                    acc[2 * j] = a0 + gate * bf16_bits_to_f32(ss[j] & 0xffffu);
+                    acc[2 * j + 1] = a1 + gate * bf16_bits_to_f32(ss[j] >> 16);
                 }
             }
-        }
-        if (p.shared_out != nullptr) {
-            const uint4 s = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
-            const uint32_t ss[4] = { s.x, s.y, s.z, s.w };
+            uint32_t o[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float a0 = acc[2 * j], a1 = acc[2 * j + 1];
-                if (p.round_before_shared) { // upstream rounds the routed sum to bf16 first
-                    a0 = __bfloat162float(__float2bfloat16(a0));
-                    a1 = __bfloat162float(__float2bfloat16(a1));
-                }
-                acc[2 * j] = a0 + gate * bf16_bits_to_f32(ss[j] & 0xffffu);
-                acc[2 * j + 1] = a1 + gate * bf16_bits_to_f32(ss[j] >> 16);
+                const __nv_bfloat162 r = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                o[j] = *reinterpret_cast<const uint32_t*>(&r);
             }
+            out[i] = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        uint32_t o[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const __nv_bfloat162 r = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-            o[j] = *reinterpret_cast<const uint32_t*>(&r);
-        }
-        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -636,8 +671,8 @@ cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream)
 {
     if (p.num_tokens == 0)
         return cudaSuccess;
-    const uint32_t threads = std::min(256u, std::max(32u, (p.hidden_size / 8 + 31) / 32 * 32));
-    combine_kernel<<<p.num_tokens, threads, 0, stream>>>(p);
+    combine_kernel<<<(p.num_tokens + kCombineTokens - 1) / kCombineTokens, kCombineTokens * kCombineGroup, 0,
+                     stream>>>(p);
     note_launch();
     return cudaGetLastError();
 }

@@ -350,8 +350,14 @@ class ExpertParallelLayer:
             b.shared_expert(hidden)
             ev[3].record()
             pull = self.combine_mode == "pull"
+            sub = self.cuda and hasattr(b, "ctx")
+            if sub:
+                ops.profile_begin(b.ctx)
             b.experts(self.g_packed, self.g_scale, self.g_ids, self.g_wts, self.partial, skip_empty=pull)
             ev[4].record()
+            if sub:  # stages inside the experts phase, recorded by the library
+                for name, ms in ops.profile_end(b.ctx):
+                    acc.setdefault("experts/" + name, []).append(ms)
             if pull and self.dispatch_mode == "pull":
                 self._symm_handle.barrier(channel=1)
             elif pull:
@@ -367,7 +373,7 @@ class ExpertParallelLayer:
             torch.cuda.synchronize()
             for i, name in enumerate(names):
                 acc[name].append(ev[i].elapsed_time(ev[i + 1]))
-        return {k: statistics.mean(v) for k, v in acc.items()}
+        return {k: statistics.mean(v) for k, v in acc.items() if v}
 
     def roofline(self, stage_ms, hbm_gbs, peak_kind):
         """Dominant phase at n > 1: the local experts. Bytes = this rank's expert weights that
