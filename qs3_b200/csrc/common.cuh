@@ -27,6 +27,11 @@ struct qsfi_context {
 
 struct qsfi_moe_plan {
     qsfi_moe_plan_desc desc;
+    // Side stream of the whole-layer call, created on first use: the token quantiser and the
+    // shared expert run there beside the router chain (fork / join with the three events).
+    mutable cudaStream_t side_stream = nullptr;
+    mutable cudaEvent_t ev_fork = nullptr, ev_quant = nullptr, ev_shared = nullptr;
+    mutable int side_state = 0; // 0 not tried, 1 ready, -1 unavailable
 };
 
 namespace qs3 {
@@ -55,6 +60,7 @@ enum Stage {
     STAGE_GATHER = 4, STAGE_GATE_UP_GEMM = 5, STAGE_DOWN_GEMM = 6, STAGE_SHARED = 7, STAGE_COMBINE = 8
 };
 void stage_mark(cudaStream_t stream, int stage);
+bool stage_recording();
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

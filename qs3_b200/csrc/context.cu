@@ -118,6 +118,8 @@ struct StageRecorder {
 };
 static StageRecorder g_rec;
 
+bool stage_recording() { return g_rec.on; }
+
 void stage_mark(cudaStream_t stream, int stage)
 {
     if (!g_rec.on || g_rec.count >= 64)

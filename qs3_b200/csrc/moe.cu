@@ -309,16 +309,38 @@ GemmProblem grouped_problem(const RouteTables& rt, uint32_t groups)
     return g;
 }
 
-qsfi_status gemm_or_error(qsfi_context* ctx, const GemmProblem& g, const char* op)
+qsfi_status gemm_on_stream(qsfi_context* ctx, const GemmProblem& g, const char* op, cudaStream_t stream)
 {
     const char* why = nullptr;
-    cudaError_t err = launch_gemm(g, ctx->stream, &why);
+    cudaError_t err = launch_gemm(g, stream, &why);
     if (err == cudaErrorNotSupported && why != nullptr)
         return set_unsupported(ctx, "%s: %s", op, why);
     if (err != cudaSuccess && why != nullptr)
         return set_error(ctx, QSFI_STATUS_BACKEND_ERROR, QSFI_ERROR_SOURCE_QSFI, static_cast<int32_t>(err),
                          "%s: %s", op, why);
     return set_cuda_error(ctx, err, op);
+}
+
+qsfi_status gemm_or_error(qsfi_context* ctx, const GemmProblem& g, const char* op)
+{
+    return gemm_on_stream(ctx, g, op, ctx->stream);
+}
+
+// Side stream and events of a plan (see qsfi_moe_plan); false when they cannot be had, in
+// which case the layer runs on the context's stream alone.
+bool plan_side_stream(const qsfi_moe_plan* plan)
+{
+    if (plan->side_state == 0) {
+        plan->side_state = -1;
+        if (cudaStreamCreateWithFlags(&plan->side_stream, cudaStreamNonBlocking) == cudaSuccess
+            && cudaEventCreateWithFlags(&plan->ev_fork, cudaEventDisableTiming) == cudaSuccess
+            && cudaEventCreateWithFlags(&plan->ev_quant, cudaEventDisableTiming) == cudaSuccess
+            && cudaEventCreateWithFlags(&plan->ev_shared, cudaEventDisableTiming) == cudaSuccess)
+            plan->side_state = 1;
+        else
+            cudaGetLastError();
+    }
+    return plan->side_state == 1;
 }
 
 // Routed experts in bf16 on rows already described by `rt`:
@@ -538,6 +560,16 @@ qsfi_status qsfi_moe_plan_create(qsfi_context* ctx, const qsfi_moe_plan_desc* de
 
 void qsfi_moe_plan_destroy(qsfi_moe_plan* plan)
 {
+    if (plan == nullptr)
+        return;
+    if (plan->ev_fork != nullptr)
+        cudaEventDestroy(plan->ev_fork);
+    if (plan->ev_quant != nullptr)
+        cudaEventDestroy(plan->ev_quant);
+    if (plan->ev_shared != nullptr)
+        cudaEventDestroy(plan->ev_shared);
+    if (plan->side_stream != nullptr)
+        cudaStreamDestroy(plan->side_stream);
     delete plan;
 }
 
@@ -975,6 +1007,78 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
     LayerExtra x = carve_layer(base, routed_bytes, p, d->num_tokens, shared ? is : 0, nvfp4);
     const __nv_bfloat16* hidden = static_cast<const __nv_bfloat16*>(d->hidden.data);
 
+    // NVFP4 shared expert as a dense problem over the tokens in natural order (A operand:
+    // the tokens quantised once in x.sh_xq)
+    const auto run_shared_nvfp4 = [&](cudaStream_t stream) -> qsfi_status {
+        const float ga = d->act_global_scale == 0.0f ? 1.0f : d->act_global_scale;
+        const float ga2 = d->act2_global_scale == 0.0f ? 1.0f : d->act2_global_scale;
+        GemmProblem s1 {};
+        s1.nvfp4 = 1;
+        s1.a = x.sh_xq;
+        s1.a_rows = d->num_tokens;
+        s1.a_pitch_bytes = h / 2;
+        s1.a_scale_tiled = x.sh_xq_sf;
+        s1.b = d->shared_gate_up_weight.data;
+        s1.b_pitch_bytes = h / 2;
+        s1.b_scale_tiled = static_cast<const uint8_t*>(d->shared_gate_up_scale_tiled.data);
+        s1.groups = 1;
+        s1.n = is;
+        s1.k = p.hidden_size;
+        s1.gated = 1;
+        s1.epilogue = EPI_SWIGLU_NVFP4;
+        s1.out = x.sh_actq;
+        s1.out_pitch_elems = is / 2;
+        s1.out_scale_tiled = x.sh_actq_sf;
+        s1.alpha = ga;
+        s1.group_scale = static_cast<const float*>(d->shared_gate_up_global_scale.data);
+        s1.out_global_scale = ga2;
+        qsfi_status st1 = gemm_on_stream(ctx, s1, "NVFP4 shared gate_up GEMM", stream);
+        if (st1 != QSFI_STATUS_OK)
+            return st1;
+        GemmProblem s2 {};
+        s2.nvfp4 = 1;
+        s2.a = x.sh_actq;
+        s2.a_rows = d->num_tokens;
+        s2.a_pitch_bytes = is / 2;
+        s2.a_scale_tiled = x.sh_actq_sf;
+        s2.b = d->shared_down_weight.data;
+        s2.b_pitch_bytes = is / 2;
+        s2.b_scale_tiled = static_cast<const uint8_t*>(d->shared_down_scale_tiled.data);
+        s2.groups = 1;
+        s2.n = p.hidden_size;
+        s2.k = is;
+        s2.epilogue = EPI_STORE_BF16;
+        s2.out = x.sh_out;
+        s2.out_pitch_elems = p.hidden_size;
+        s2.alpha = ga2;
+        s2.group_scale = static_cast<const float*>(d->shared_down_global_scale.data);
+        return gemm_on_stream(ctx, s2, "NVFP4 shared down GEMM", stream);
+    };
+    // With a shared expert, the token quantiser and the shared expert's two GEMMs depend on
+    // the tokens only: they run on the plan's side stream beside the router chain (logits
+    // GEMM, top-k, sort) and join the main stream where their results are consumed. The
+    // per-stage recorder needs one timeline, so a profiled call stays on the main stream.
+    const bool fork = nvfp4 && shared && !stage_recording() && plan_side_stream(plan);
+    if (fork) {
+        cudaStream_t side = plan->side_stream;
+        cudaError_t ferr = cudaEventRecord(plan->ev_fork, st);
+        if (ferr == cudaSuccess)
+            ferr = cudaStreamWaitEvent(side, plan->ev_fork, 0);
+        if (ferr == cudaSuccess)
+            ferr = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
+                                                d->act_global_scale, x.sh_xq, x.sh_xq_sf, side);
+        if (ferr == cudaSuccess)
+            ferr = cudaEventRecord(plan->ev_quant, side);
+        if (ferr != cudaSuccess)
+            return set_cuda_error(ctx, ferr, "NVFP4 MoE layer fork");
+        status = run_shared_nvfp4(side);
+        if (status != QSFI_STATUS_OK)
+            return status;
+        ferr = cudaEventRecord(plan->ev_shared, side);
+        if (ferr != cudaSuccess)
+            return set_cuda_error(ctx, ferr, "NVFP4 MoE layer fork");
+    }
+
     stage_mark(st, STAGE_ROUTER_GEMM);
     // 1. router logits: f32 [T, E] = hidden . router_weight^T  (src/model.rs:2082-2090)
     float* logits = d->router_logits.data != nullptr ? static_cast<float*>(d->router_logits.data) : x.logits;
@@ -1028,8 +1132,11 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         // 4. quantise every token once (token order), then gather the codes by expert;
         //    5./6. grouped GEMMs
         stage_mark(st, STAGE_GATHER);
-        err = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
-                                           d->act_global_scale, x.sh_xq, x.sh_xq_sf, st);
+        if (fork)
+            err = cudaStreamWaitEvent(st, plan->ev_quant, 0);
+        else
+            err = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
+                                               d->act_global_scale, x.sh_xq, x.sh_xq_sf, st);
         if (err == cudaSuccess)
             err = launch_nvfp4_gather_packed(x.sh_xq, x.sh_xq_sf, rt.route_prows, routes, p.top_k,
                                              p.hidden_size, wn.xq, wn.xq_sf, st, 1);
@@ -1047,53 +1154,17 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
             return status;
         y2 = wn.y2;
         if (shared) {
-            // 7. shared expert as a dense problem over the tokens in natural order
+            // 7. shared expert
             stage_mark(st, STAGE_SHARED);
-            const float ga = d->act_global_scale == 0.0f ? 1.0f : d->act_global_scale;
-            const float ga2 = d->act2_global_scale == 0.0f ? 1.0f : d->act2_global_scale;
-            GemmProblem s1 {};
-            s1.nvfp4 = 1;
-            s1.a = x.sh_xq;
-            s1.a_rows = d->num_tokens;
-            s1.a_pitch_bytes = h / 2;
-            s1.a_scale_tiled = x.sh_xq_sf;
-            s1.b = d->shared_gate_up_weight.data;
-            s1.b_pitch_bytes = h / 2;
-            s1.b_scale_tiled = static_cast<const uint8_t*>(d->shared_gate_up_scale_tiled.data);
-            s1.groups = 1;
-            s1.n = is;
-            s1.k = p.hidden_size;
-            s1.gated = 1;
-            s1.epilogue = EPI_SWIGLU_NVFP4;
-            s1.out = x.sh_actq;
-            s1.out_pitch_elems = is / 2;
-            s1.out_scale_tiled = x.sh_actq_sf;
-            s1.alpha = ga;
-            s1.group_scale = static_cast<const float*>(d->shared_gate_up_global_scale.data);
-            s1.out_global_scale = ga2;
-            status = gemm_or_error(ctx, s1, "NVFP4 shared gate_up GEMM");
-            if (status != QSFI_STATUS_OK)
-                return status;
-            GemmProblem s2 {};
-            s2.nvfp4 = 1;
-            s2.a = x.sh_actq;
-            s2.a_rows = d->num_tokens;
-            s2.a_pitch_bytes = is / 2;
-            s2.a_scale_tiled = x.sh_actq_sf;
-            s2.b = d->shared_down_weight.data;
-            s2.b_pitch_bytes = is / 2;
-            s2.b_scale_tiled = static_cast<const uint8_t*>(d->shared_down_scale_tiled.data);
-            s2.groups = 1;
-            s2.n = p.hidden_size;
-            s2.k = is;
-            s2.epilogue = EPI_STORE_BF16;
-            s2.out = x.sh_out;
-            s2.out_pitch_elems = p.hidden_size;
-            s2.alpha = ga2;
-            s2.group_scale = static_cast<const float*>(d->shared_down_global_scale.data);
-            status = gemm_or_error(ctx, s2, "NVFP4 shared down GEMM");
-            if (status != QSFI_STATUS_OK)
-                return status;
+            if (fork) {
+                err = cudaStreamWaitEvent(st, plan->ev_shared, 0);
+                if (err != cudaSuccess)
+                    return set_cuda_error(ctx, err, "NVFP4 MoE layer join");
+            } else {
+                status = run_shared_nvfp4(st);
+                if (status != QSFI_STATUS_OK)
+                    return status;
+            }
         }
     } else {
         stage_mark(st, STAGE_GATHER);
