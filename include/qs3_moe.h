@@ -299,6 +299,30 @@ qsfi_status qscb_context_get_last_error(const qscb_context* ctx, qsfi_error_info
 void qscb_context_clear_last_error(qscb_context* ctx);
 qsfi_status qscb_gemm_bf16(qscb_context* ctx, const qscb_bf16_gemm_desc* desc);
 
+/* ---- RMSNorm neighbours of the MoE block (upstream qsfi.h:160-176, 330-331; there a
+ * FlashInfer call, qsfi_norm_rope.cu:139-206, 395-465). Same descriptors, validation
+ * order and messages (qsfi_norm_rope.cu:72-146, 208-238). ---- */
+typedef struct {
+    qsfi_tensor2 x;      /* bf16/f32 [rows, hidden_size]. */
+    qsfi_tensor1 weight; /* same dtype [hidden_size]. */
+    qsfi_tensor2 out;    /* same dtype [rows, hidden_size]. */
+    uint32_t hidden_size;
+    float weight_bias;   /* 0 for standard RMSNorm, 1 for raw-weight+1 q/k norm. */
+    float eps;
+} qsfi_rmsnorm_desc;
+
+typedef struct {
+    qsfi_tensor2 x;              /* bf16/f32 [rows, hidden_size], overwritten with normalized output. */
+    qsfi_tensor2 residual_inout; /* same dtype [rows, hidden_size], updated to residual + x. */
+    qsfi_tensor1 weight;         /* same dtype [hidden_size]. */
+    qsfi_tensor2 out;            /* must alias x; documents the normalized output tensor. */
+    uint32_t hidden_size;
+    float eps;
+} qsfi_fused_add_rmsnorm_desc;
+
+qsfi_status qsfi_rmsnorm(qsfi_context* ctx, const qsfi_rmsnorm_desc* desc);
+qsfi_status qsfi_fused_add_rmsnorm(qsfi_context* ctx, const qsfi_fused_add_rmsnorm_desc* desc);
+
 /* ============================ additive entry points (no upstream symbol) == */
 
 /* Scale-factor tile layout used by the block-scaled tensor-core path
@@ -348,6 +372,18 @@ typedef struct {
     uint32_t gated_rows;
 } qs3_nvfp4_tile_scales_desc;
 qsfi_status qs3_nvfp4_tile_scales(qsfi_context* ctx, const qs3_nvfp4_tile_scales_desc* desc);
+
+/* Fused add + RMSNorm (bf16) that also writes the NVFP4 quantisation of the normalised rows
+ * in token order (codes + tiled scales): the pre-MoE norm then hands the MoE layer its
+ * tokens already quantised, in the same pass over [rows, hidden]. No upstream counterpart.
+ * The codes equal qs3_nvfp4_quantize_act applied to the bf16 rows this call stores. */
+typedef struct {
+    qsfi_fused_add_rmsnorm_desc norm; /* bf16, hidden_size divisible by 64 and <= 8192 */
+    qsfi_tensor2 packed;              /* u8 [rows, hidden_size / 2] out */
+    qsfi_tensor1 scale_tiled;         /* u8 [>= qs3_nvfp4_tiled_scale_bytes(rows, hidden_size)] out */
+    float global_scale;               /* 0 means 1 */
+} qs3_fused_add_rmsnorm_nvfp4_desc;
+qsfi_status qs3_fused_add_rmsnorm_nvfp4(qsfi_context* ctx, const qs3_fused_add_rmsnorm_nvfp4_desc* desc);
 
 /* ---- FP8 block-scaled experts (no upstream counterpart: upstream declares only the
  * dtype values QSFI_DTYPE_FP8_E4M3 / _E5M2, qs_tensor.h:20-24, and no FP8 MoE entry) ----

@@ -329,3 +329,36 @@ def moe_fp8(hidden_codes, hidden_scale, ids, weights, gu, d, *, local_offset=0, 
                        C.c_int64(t), C.c_int64(h), C.c_int64(two_i // 2), C.c_int64(k),
                        C.c_int64(local_offset), C.c_int64(e), _p(tl), C.c_int64(n), _p(out))
     return out
+
+
+# ------------------------------------------------------------------ norms ---
+
+def _norm_input(a):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.uint16:
+        return a, 1
+    return a.astype(np.float32, copy=False), 0
+
+
+def rmsnorm(x, weight, eps=1e-6, weight_bias=0.0):
+    """f32 [rows, hidden] of the upstream RMSNorm checker; x / weight bf16 bits or f32."""
+    x, is_bf16 = _norm_input(x)
+    weight, _ = _norm_input(weight)
+    rows, hidden = x.shape
+    out = np.empty((rows, hidden), np.float32)
+    lib().qs3o_rmsnorm(_p(x), _p(weight), C.c_int(is_bf16), C.c_int64(rows), C.c_int64(hidden),
+                       C.c_float(eps), C.c_float(weight_bias), _p(out))
+    return out
+
+
+def fused_add_rmsnorm(x, residual, weight, eps=1e-6):
+    """(norm f32, residual f32) of the upstream fused add + RMSNorm checker."""
+    x, is_bf16 = _norm_input(x)
+    residual, _ = _norm_input(residual)
+    weight, _ = _norm_input(weight)
+    rows, hidden = x.shape
+    norm = np.empty((rows, hidden), np.float32)
+    res = np.empty((rows, hidden), np.float32)
+    lib().qs3o_fused_add_rmsnorm(_p(x), _p(residual), _p(weight), C.c_int(is_bf16), C.c_int64(rows),
+                                 C.c_int64(hidden), C.c_float(eps), _p(norm), _p(res))
+    return norm, res

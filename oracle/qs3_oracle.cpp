@@ -797,3 +797,53 @@ QS3O_API void qs3o_moe_fp8(
         }
     }
 }
+
+// ---- RMSNorm neighbours of the MoE block ---------------------------------------------------
+// Restates the upstream CPU checkers of the FlashInfer-backed norms
+// (tests_cuda_flashinfer_norm_rope.inc:139-188 and :190-246): everything in f32, the sum of
+// squares in column order, inv_rms = 1 / sqrt(sum / hidden + eps), plain weight (+ bias).
+// Inputs are bf16 bit patterns (is_bf16 != 0) or f32; outputs are f32 (the device result is
+// compared within the tolerances of the upstream tests: f32 2e-5 / 1e-5, bf16 0.018 / 0.012).
+
+namespace {
+inline float load_elem(const void* p, int is_bf16, int64_t i)
+{
+    return is_bf16 ? bf16_to_f32(static_cast<const uint16_t*>(p)[i]) : static_cast<const float*>(p)[i];
+}
+} // namespace
+
+QS3O_API void qs3o_rmsnorm(
+    const void* x, const void* weight, int is_bf16, int64_t rows, int64_t hidden, float eps,
+    float weight_bias, float* out
+)
+{
+    for (int64_t r = 0; r < rows; ++r) {
+        float sum_sq = 0.0f;
+        for (int64_t c = 0; c < hidden; ++c) {
+            const float v = load_elem(x, is_bf16, r * hidden + c);
+            sum_sq += v * v;
+        }
+        const float inv_rms = 1.0f / std::sqrt(sum_sq / static_cast<float>(hidden) + eps);
+        for (int64_t c = 0; c < hidden; ++c)
+            out[r * hidden + c]
+                = load_elem(x, is_bf16, r * hidden + c) * inv_rms * (weight_bias + load_elem(weight, is_bf16, c));
+    }
+}
+
+QS3O_API void qs3o_fused_add_rmsnorm(
+    const void* x, const void* residual, const void* weight, int is_bf16, int64_t rows,
+    int64_t hidden, float eps, float* norm_out, float* residual_out
+)
+{
+    for (int64_t r = 0; r < rows; ++r) {
+        float sum_sq = 0.0f;
+        for (int64_t c = 0; c < hidden; ++c) {
+            const float v = load_elem(x, is_bf16, r * hidden + c) + load_elem(residual, is_bf16, r * hidden + c);
+            residual_out[r * hidden + c] = v;
+            sum_sq += v * v;
+        }
+        const float inv_rms = 1.0f / std::sqrt(sum_sq / static_cast<float>(hidden) + eps);
+        for (int64_t c = 0; c < hidden; ++c)
+            norm_out[r * hidden + c] = residual_out[r * hidden + c] * inv_rms * load_elem(weight, is_bf16, c);
+    }
+}

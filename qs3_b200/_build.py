@@ -19,7 +19,7 @@ OBJ_DIR = os.path.join(SRC_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libqs3moe.so")
 
 SOURCES = ["context.cu", "router.cu", "routing.cu", "gemm.cu", "gemm_api.cu", "nvfp4.cu", "moe.cu",
-           "peak_probe.cu", "fp8.cu"]
+           "peak_probe.cu", "fp8.cu", "norm.cu"]
 HEADERS = ["common.cuh", "nvfp4.cuh", "tcgen05.cuh", os.path.join("..", "..", "include", "qs3_moe.h")]
 
 NVCC_FLAGS = [

@@ -227,6 +227,21 @@ class MoeEpPullTokensDesc(C.Structure):
                 ("num_segments", C.c_uint32)]
 
 
+class RmsnormDesc(C.Structure):
+    _fields_ = [("x", Tensor2), ("weight", Tensor1), ("out", Tensor2), ("hidden_size", C.c_uint32),
+                ("weight_bias", C.c_float), ("eps", C.c_float)]
+
+
+class FusedAddRmsnormDesc(C.Structure):
+    _fields_ = [("x", Tensor2), ("residual_inout", Tensor2), ("weight", Tensor1), ("out", Tensor2),
+                ("hidden_size", C.c_uint32), ("eps", C.c_float)]
+
+
+class FusedAddRmsnormNvfp4Desc(C.Structure):
+    _fields_ = [("norm", FusedAddRmsnormDesc), ("packed", Tensor2), ("scale_tiled", Tensor1),
+                ("global_scale", C.c_float)]
+
+
 _SIGNATURES = {
     "qsfi_status_string": (C.c_char_p, [C.c_int]),
     "qsfi_context_create": (C.c_int, [_P(ContextDesc), _P(C.c_void_p)]),
@@ -266,6 +281,9 @@ _SIGNATURES = {
                                                    _P(C.c_size_t)]),
     "qs3_moe_ep_finish": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeEpFinishDesc)]),
     "qs3_moe_ep_pull_tokens": (C.c_int, [C.c_void_p, _P(MoeEpPullTokensDesc)]),
+    "qsfi_rmsnorm": (C.c_int, [C.c_void_p, _P(RmsnormDesc)]),
+    "qsfi_fused_add_rmsnorm": (C.c_int, [C.c_void_p, _P(FusedAddRmsnormDesc)]),
+    "qs3_fused_add_rmsnorm_nvfp4": (C.c_int, [C.c_void_p, _P(FusedAddRmsnormNvfp4Desc)]),
     "qs3_moe_read_device_error": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
     "qs3_moe_launch_count": (C.c_uint64, []),
     "qs3_moe_profile_begin": (C.c_int, [C.c_void_p]),

@@ -556,3 +556,37 @@ def tensor_peak_probe(ctx: Context, kind: str = "nvfp4", n: int = 256, iters: in
     ctx.check(ctx._lib.qs3_tensor_peak_probe(ctx.handle, PEAK_KINDS[kind] + (16 if pair else 0), n, iters,
                                              C.byref(out)))
     return float(out.value)
+
+
+def rmsnorm(ctx: Context, x, weight, out, eps: float = 1e-6, weight_bias: float = 0.0):
+    """``qsfi_rmsnorm`` (upstream qsfi.h:160-167, 330)."""
+    d = capi.RmsnormDesc()
+    d.x, d.weight, d.out = _desc(x, 2), _desc(weight, 1), _desc(out, 2)
+    d.hidden_size, d.weight_bias, d.eps = x.shape[1], weight_bias, eps
+    ctx.check(ctx._lib.qsfi_rmsnorm(ctx.handle, C.byref(d)))
+
+
+def _fused_desc(x, residual, weight, eps):
+    d = capi.FusedAddRmsnormDesc()
+    d.x, d.residual_inout, d.weight, d.out = _desc(x, 2), _desc(residual, 2), _desc(weight, 1), _desc(x, 2)
+    d.hidden_size, d.eps = x.shape[1], eps
+    return d
+
+
+def fused_add_rmsnorm(ctx: Context, x, residual, weight, eps: float = 1e-6):
+    """``qsfi_fused_add_rmsnorm`` (upstream qsfi.h:169-176, 331): residual += x; x = norm(residual)."""
+    d = _fused_desc(x, residual, weight, eps)
+    ctx.check(ctx._lib.qsfi_fused_add_rmsnorm(ctx.handle, C.byref(d)))
+
+
+def fused_add_rmsnorm_nvfp4(ctx: Context, x, residual, weight, eps: float = 1e-6, global_scale: float = 1.0):
+    """``qs3_fused_add_rmsnorm_nvfp4``: as above, and returns the NVFP4 codes and tiled scales
+    of the normalised rows (token order)."""
+    rows, hidden = x.shape
+    packed = torch.empty((rows, hidden // 2), dtype=torch.uint8, device=x.device)
+    tiled = torch.zeros(nvfp4_tiled_scale_bytes(rows, hidden), dtype=torch.uint8, device=x.device)
+    d = capi.FusedAddRmsnormNvfp4Desc()
+    d.norm = _fused_desc(x, residual, weight, eps)
+    d.packed, d.scale_tiled, d.global_scale = _desc(packed, 2), _desc(tiled, 1), global_scale
+    ctx.check(ctx._lib.qs3_fused_add_rmsnorm_nvfp4(ctx.handle, C.byref(d)))
+    return packed, tiled

@@ -1,0 +1,129 @@
+"""GPU parity of the RMSNorm neighbours of the MoE block (qsfi_rmsnorm,
+qsfi_fused_add_rmsnorm and the variant that also emits NVFP4 codes) against the restated
+upstream CPU checkers, on the upstream test vectors and on seeded rows, with the upstream
+tolerances (f32: 2e-5 / 1e-5, bf16: 0.018 norm / 0.012 residual)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import bf16, f32, to_dev, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from qs3_b200 import ops as m
+    return m
+
+
+@pytest.fixture(scope="module")
+def ctx(ops):
+    return ops.Context()
+
+
+def _as_f32(a):
+    return f32(a) if a.dtype == np.uint16 else a
+
+
+@pytest.mark.parametrize("name", ["fused_add_rmsnorm_f32", "fused_add_rmsnorm_bf16"])
+def test_upstream_fused_add_vectors(ops, ctx, oracle, golden, name):
+    c = golden[name]
+    conv = bf16 if name.endswith("bf16") else (lambda a: a)
+    shape = (c["rows"], c["hidden"])
+    x = conv(np.array(c["x"], np.float32).reshape(shape))
+    r = conv(np.array(c["residual"], np.float32).reshape(shape))
+    w = conv(np.array(c["weight"], np.float32))
+    want_norm, want_res = oracle.fused_add_rmsnorm(x, r, w, c["eps"])
+    dx, dr = to_dev(x), to_dev(r)
+    ops.fused_add_rmsnorm(ctx, dx, dr, to_dev(w), c["eps"])
+    torch.cuda.synchronize()
+    assert np.max(np.abs(_as_f32(to_np(dx)) - want_norm)) <= c["abs_tol_norm"]
+    assert np.max(np.abs(_as_f32(to_np(dr)) - want_res)) <= c["abs_tol_residual"]
+
+
+def test_upstream_rmsnorm_vector(ops, ctx, oracle, golden):
+    c = golden["rmsnorm_f32"]
+    x = np.array(c["x"], np.float32).reshape(c["rows"], c["hidden"])
+    w = np.array(c["weight"], np.float32)
+    for bias in (0.0, 1.0):
+        out = torch.empty((c["rows"], c["hidden"]), dtype=torch.float32, device="cuda")
+        ops.rmsnorm(ctx, to_dev(x), to_dev(w), out, c["eps"], bias)
+        torch.cuda.synchronize()
+        assert np.max(np.abs(to_np(out) - oracle.rmsnorm(x, w, c["eps"], bias))) <= c["abs_tol"]
+
+
+@pytest.mark.parametrize("rows,hidden,dtype", [(5, 2048, "bf16"), (3, 2048, "f32"), (7, 200, "bf16"),
+                                               (2, 12, "f32"), (3, 13, "bf16"), (4, 9000, "bf16"),
+                                               (33, 4096, "bf16")])
+def test_seeded_rows_match_checker(ops, ctx, oracle, rows, hidden, dtype):
+    rng = np.random.default_rng(rows * 31 + hidden)
+    conv = bf16 if dtype == "bf16" else (lambda a: a.astype(np.float32))
+    x = conv(rng.standard_normal((rows, hidden), dtype=np.float32))
+    r = conv(rng.standard_normal((rows, hidden), dtype=np.float32) * 2.0)
+    w = conv(1.0 + 0.1 * rng.standard_normal(hidden, dtype=np.float32))
+    tol_n, tol_r = (0.06, 0.04) if dtype == "bf16" else (5e-5, 1e-5)  # bf16: half an ulp at |v| < 8
+    want_norm, want_res = oracle.fused_add_rmsnorm(x, r, w, 1e-6)
+    dx, dr = to_dev(x), to_dev(r)
+    ops.fused_add_rmsnorm(ctx, dx, dr, to_dev(w), 1e-6)
+    torch.cuda.synchronize()
+    assert np.max(np.abs(_as_f32(to_np(dx)) - want_norm)) <= tol_n
+    assert np.max(np.abs(_as_f32(to_np(dr)) - want_res)) <= tol_r
+    out = torch.empty_like(to_dev(x))
+    ops.rmsnorm(ctx, to_dev(x), to_dev(w), out, 1e-6, 1.0)
+    torch.cuda.synchronize()
+    assert np.max(np.abs(_as_f32(to_np(out)) - oracle.rmsnorm(x, w, 1e-6, 1.0))) <= tol_n
+
+
+def test_strided_rows(ops, ctx, oracle):
+    """Rows with a pitch larger than hidden_size (stride[0] >= shape[1] is legal upstream)."""
+    rng = np.random.default_rng(9)
+    rows, hidden, pitch = 6, 256, 320
+    x = bf16(rng.standard_normal((rows, hidden), dtype=np.float32))
+    r = bf16(rng.standard_normal((rows, hidden), dtype=np.float32))
+    w = bf16(rng.standard_normal(hidden, dtype=np.float32))
+    bx = torch.zeros((rows, pitch), dtype=torch.bfloat16, device="cuda")
+    br = torch.zeros((rows, pitch), dtype=torch.bfloat16, device="cuda")
+    bx[:, :hidden] = to_dev(x)
+    br[:, :hidden] = to_dev(r)
+    ops.fused_add_rmsnorm(ctx, bx[:, :hidden], br[:, :hidden], to_dev(w), 1e-6)
+    torch.cuda.synchronize()
+    want_norm, want_res = oracle.fused_add_rmsnorm(x, r, w, 1e-6)
+    assert np.max(np.abs(f32(to_np(bx[:, :hidden].contiguous())) - want_norm)) <= 0.06
+    assert np.max(np.abs(f32(to_np(br[:, :hidden].contiguous())) - want_res)) <= 0.04
+    assert not to_np(bx[:, hidden:].contiguous()).any()       # the padding columns stay untouched
+
+
+@pytest.mark.parametrize("rows,hidden", [(16, 2048), (130, 512), (3, 64)])
+def test_nvfp4_variant_equals_norm_then_quantise(ops, ctx, oracle, rows, hidden):
+    rng = np.random.default_rng(rows + hidden)
+    x = bf16(rng.standard_normal((rows, hidden), dtype=np.float32))
+    r = bf16(rng.standard_normal((rows, hidden), dtype=np.float32))
+    w = bf16(1.0 + 0.1 * rng.standard_normal(hidden, dtype=np.float32))
+    # unfused: norm, then the stand-alone activation quantiser on the stored bf16 rows
+    ax, ar = to_dev(x), to_dev(r)
+    ops.fused_add_rmsnorm(ctx, ax, ar, to_dev(w), 1e-6)
+    p_ref, s_ref = oracle.nvfp4_quantize_act(to_np(ax), 0.5)
+    # fused
+    bx, br = to_dev(x), to_dev(r)
+    packed, tiled = ops.fused_add_rmsnorm_nvfp4(ctx, bx, br, to_dev(w), 1e-6, 0.5)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_np(bx), to_np(ax)) and np.array_equal(to_np(br), to_np(ar))
+    assert np.array_equal(to_np(packed), p_ref)
+    idx = oracle.tiled_scale_index(rows, hidden)
+    assert np.array_equal(to_np(tiled)[idx], s_ref)
+
+
+def test_validation_messages(ops, ctx):
+    x = torch.zeros((2, 8), dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(8, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.Qs3Error, match="eps must be finite"):
+        ops.fused_add_rmsnorm(ctx, x, x.clone(), w, 0.0)
+    with pytest.raises(ops.Qs3Error, match="residual_inout shape must match x"):
+        ops.fused_add_rmsnorm(ctx, x, torch.zeros((3, 8), dtype=torch.bfloat16, device="cuda"), w, 1e-6)
+    with pytest.raises(ops.Qs3Error, match="dtype does not match"):
+        ops.fused_add_rmsnorm(ctx, x, x.clone(), w.float(), 1e-6)
+    with pytest.raises(ops.Qs3Error, match="supports only bf16/f32"):
+        ops.rmsnorm(ctx, x.to(torch.float16), w.to(torch.float16), x.to(torch.float16), 1e-6)
+    with pytest.raises(ops.Qs3Error, match="weight_bias must be 0.0 or 1.0"):
+        ops.rmsnorm(ctx, x, w, x.clone(), 1e-6, 0.5)

@@ -223,3 +223,27 @@ def test_seeded_golden_vectors_are_reproduced(oracle, seeded):
         case = mg.build_case(oracle, helpers, *args)
         for key, val in case.items():
             assert np.array_equal(np.asarray(val), seeded[f"{name}/{key}"]), (name, key)
+
+
+def _norm_f64(v, weight, eps, bias=0.0):
+    v = v.astype(np.float64)
+    inv = 1.0 / np.sqrt((v * v).mean(axis=1, keepdims=True) + eps)
+    return v * inv * (bias + weight.astype(np.float64))
+
+
+def test_rmsnorm_checkers_match_closed_form(oracle, golden):
+    """The norm restatements on the upstream test inputs against float64 algebra."""
+    c = golden["rmsnorm_f32"]
+    x = np.array(c["x"], np.float32).reshape(c["rows"], c["hidden"])
+    w = np.array(c["weight"], np.float32)
+    assert np.allclose(oracle.rmsnorm(x, w, c["eps"]), _norm_f64(x, w, c["eps"]), atol=1e-6)
+    assert np.allclose(oracle.rmsnorm(x, w, c["eps"], 1.0), _norm_f64(x, w, c["eps"], 1.0), atol=1e-6)
+    for name, conv in (("fused_add_rmsnorm_f32", lambda a: a), ("fused_add_rmsnorm_bf16", bf16)):
+        c = golden[name]
+        shape = (c["rows"], c["hidden"])
+        x = np.array(c["x"], np.float32).reshape(shape)
+        r = np.array(c["residual"], np.float32).reshape(shape)
+        w = np.array(c["weight"], np.float32)
+        norm, res = oracle.fused_add_rmsnorm(conv(x), conv(r), conv(w), c["eps"])
+        assert np.array_equal(res, x + r)            # the inputs are exactly representable
+        assert np.allclose(norm, _norm_f64(x + r, w, c["eps"]), atol=1e-6)
