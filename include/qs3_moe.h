@@ -473,6 +473,12 @@ typedef struct {
     qsfi_tensor2 router_logits; /* optional f32 [num_tokens, num_experts] out */
     qsfi_tensor1 workspace;    /* u8 [>= qs3_moe_layer_workspace_size] */
     uint32_t num_tokens;
+    /* optional, NVFP4 plans: the tokens already quantised in token order (codes u8
+       [num_tokens, hidden / 2] and tiled scales covering ceil(num_tokens / 128) * 128 rows),
+       as qs3_fused_add_rmsnorm_nvfp4 writes them with the same act_global_scale; the layer
+       then skips its own quantisation pass. `hidden` is still needed (router, shared gate). */
+    qsfi_tensor2 hidden_packed;
+    qsfi_tensor1 hidden_scale_tiled;
 } qs3_moe_layer_desc;
 
 qsfi_status qs3_moe_layer_workspace_size(

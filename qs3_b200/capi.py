@@ -157,7 +157,8 @@ class MoeLayerDesc(C.Structure):
                 ("score", C.c_int), ("renormalize", C.c_uint32), ("routed_scaling_factor", C.c_float),
                 ("act_global_scale", C.c_float), ("act2_global_scale", C.c_float), ("out", Tensor2),
                 ("topk_ids", Tensor2), ("topk_weights", Tensor2), ("router_logits", Tensor2),
-                ("workspace", Tensor1), ("num_tokens", C.c_uint32)]
+                ("workspace", Tensor1), ("num_tokens", C.c_uint32), ("hidden_packed", Tensor2),
+                ("hidden_scale_tiled", Tensor1)]
 
 
 class MoeEpRouteDesc(C.Structure):

@@ -986,6 +986,17 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
                        || !aligned16(d->shared_gate_weight.data))))
         return set_invalid_arg(ctx, "MoE tensors must be 16-byte aligned");
 
+    const bool prequant = nvfp4 && d->hidden_packed.data != nullptr;
+    if (prequant) {
+        if (d->hidden_packed.dtype != QSFI_DTYPE_U8 || !contiguous2(d->hidden_packed)
+            || d->hidden_packed.shape[0] < t || d->hidden_packed.shape[1] != h / 2
+            || !aligned16(d->hidden_packed.data) || d->hidden_scale_tiled.data == nullptr
+            || static_cast<uint64_t>(d->hidden_scale_tiled.shape[0])
+                < qs3_nvfp4_tiled_scale_bytes(static_cast<uint64_t>(t), static_cast<uint64_t>(h))
+            || !aligned16(d->hidden_scale_tiled.data))
+            return set_invalid_arg(ctx, "pre-quantised tokens need u8 [num_tokens, hidden/2] codes and tiled scales");
+    }
+
     char* base = static_cast<char*>(d->workspace.data);
     cudaStream_t st = ctx->stream;
     const uint32_t routes = d->num_tokens * p.top_k;
@@ -1006,6 +1017,10 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
     const RouteTables& rt = fp8 ? wf.rt : nvfp4 ? wn.rt : wb.rt;
     LayerExtra x = carve_layer(base, routed_bytes, p, d->num_tokens, shared ? is : 0, nvfp4);
     const __nv_bfloat16* hidden = static_cast<const __nv_bfloat16*>(d->hidden.data);
+    if (prequant) { // the caller's codes replace the layer's own token-order copy
+        x.sh_xq = static_cast<uint8_t*>(d->hidden_packed.data);
+        x.sh_xq_sf = static_cast<uint8_t*>(d->hidden_scale_tiled.data);
+    }
 
     // NVFP4 shared expert as a dense problem over the tokens in natural order (A operand:
     // the tokens quantised once in x.sh_xq)
@@ -1064,7 +1079,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         cudaError_t ferr = cudaEventRecord(plan->ev_fork, st);
         if (ferr == cudaSuccess)
             ferr = cudaStreamWaitEvent(side, plan->ev_fork, 0);
-        if (ferr == cudaSuccess)
+        if (ferr == cudaSuccess && !prequant)
             ferr = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
                                                 d->act_global_scale, x.sh_xq, x.sh_xq_sf, side);
         if (ferr == cudaSuccess)
@@ -1134,7 +1149,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         stage_mark(st, STAGE_GATHER);
         if (fork)
             err = cudaStreamWaitEvent(st, plan->ev_quant, 0);
-        else
+        else if (!prequant)
             err = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
                                                d->act_global_scale, x.sh_xq, x.sh_xq_sf, st);
         if (err == cudaSuccess)

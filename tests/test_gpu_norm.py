@@ -127,3 +127,36 @@ def test_validation_messages(ops, ctx):
         ops.rmsnorm(ctx, x.to(torch.float16), w.to(torch.float16), x.to(torch.float16), 1e-6)
     with pytest.raises(ops.Qs3Error, match="weight_bias must be 0.0 or 1.0"):
         ops.rmsnorm(ctx, x, w, x.clone(), 1e-6, 0.5)
+
+
+def test_layer_takes_the_tokens_the_norm_quantised(ops, ctx, oracle):
+    """Pre-MoE norm that hands its NVFP4 codes to the layer call == norm, then the layer
+    quantising for itself (bit for bit), with and without a shared expert."""
+    from helpers import make_moe_inputs
+    t, h, e, k, i, s = 200, 512, 16, 4, 256, 256
+    d = make_moe_inputs(77, t, h, e, i, s)
+    rng = d["rng"]
+    resid = bf16(rng.standard_normal((t, h), dtype=np.float32))
+    nw = bf16(1.0 + 0.1 * rng.standard_normal(h, dtype=np.float32))
+    gu = ops.nvfp4_quantize_weight(ctx, to_dev(d["gate_up"]), True)
+    dn = ops.nvfp4_quantize_weight(ctx, to_dev(d["down"]), False)
+    shared = ops.SharedExpert(ops.nvfp4_quantize_weight(ctx, to_dev(d["sh_gate_up"]), True),
+                              ops.nvfp4_quantize_weight(ctx, to_dev(d["sh_down"]), False), to_dev(d["sh_gate"]), s)
+    plan = ops.MoePlan(ctx, ops.MoePlanConfig(max_num_tokens=t, hidden_size=h, intermediate_size=i,
+                                              num_experts=e, top_k=k, backend=ops.capi.MOE_BACKEND_NVFP4))
+    ws = torch.zeros(plan.layer_workspace_size(t, s), dtype=torch.uint8, device="cuda")
+    outs = []
+    for fused in (False, True):
+        x, r = to_dev(d["hidden"]), to_dev(resid)
+        out = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+        if fused:
+            packed, tiled = ops.fused_add_rmsnorm_nvfp4(ctx, x, r, to_dev(nw), 1e-6, 1.0)
+            ops.moe_layer_execute(plan, x, to_dev(d["router"]), gu, dn, out, ws, shared=shared,
+                                  hidden_packed=packed, hidden_scale_tiled=tiled)
+        else:
+            ops.fused_add_rmsnorm(ctx, x, r, to_dev(nw), 1e-6)
+            ops.moe_layer_execute(plan, x, to_dev(d["router"]), gu, dn, out, ws, shared=shared)
+        torch.cuda.synchronize()
+        assert ctx.read_device_error() == 0
+        outs.append(to_np(out))
+    assert np.array_equal(outs[0], outs[1])
