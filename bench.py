@@ -181,6 +181,7 @@ def _config(cfg, world, placement="balanced"):
             "l2_policy": f"inputs_exceed_l2 (expert weights ~{weights_gb:.1f} GB per pass)"}
 
 
+
 def run_reference(args, rank, world):
     """Reference arm: the CPU restatement on the host cores, rank 0 only."""
     if rank != 0:
@@ -234,6 +235,14 @@ def run_ours(args, rank, world, local_rank):
                                       experts=args.experts or cfg.experts)
         data = workload.LayerData(cfg, ctx, seed=0)
         layer = SingleGpuLayer(ctx, data)
+        if not args.no_graph and not args.kernels_only:  # profiler captures see plain launches
+            try:
+                layer.capture()
+            except Exception as exc:  # capture is an optimisation of the launch path only
+                print(f"CUDA graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+                torch.cuda.synchronize()
+                ctx.use_current_stream()
+                layer.graph = None
     else:
         from qs3_b200 import ep
         cfg = workload.EP_NVFP4
@@ -298,6 +307,7 @@ def run_ours(args, rank, world, local_rank):
 
     if rank != 0:
         return
+    graphed = getattr(layer, "graph", None) is not None
     hbm_gbs, peak_kind = _peaks()
     line = {
         "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -307,7 +317,8 @@ def run_ours(args, rank, world, local_rank):
         "config": _config(cfg, world, args.placement),
         "e2e": {"value": e2e_value, "unit": "tokens/s",
                 "h2d_bytes_per_step": h_in.numel() * 2 * world, "d2h_bytes_per_step": h_out.numel() * 2 * world},
-        "gpu_launches": launches,
+        "gpu_launches": launches if graphed is False else args.steps * layer.launches_per_step,
+        "cuda_graph": graphed,
         "clocks": clocks.summary(),
         "stage_ms": stage_ms,
     }
@@ -376,20 +387,46 @@ class SingleGpuLayer:
         self.out = torch.empty((cfg.tokens, cfg.hidden), dtype=torch.bfloat16, device=dev)
         self.x_dev = torch.empty_like(data.hidden)
         self.ids = torch.empty((cfg.tokens, cfg.top_k), dtype=torch.int32, device=dev)
+        self.graph = None
 
     def step(self, hidden=None, out=None):
+        if self.graph is not None and hidden is None and out is None:
+            self.graph.replay()
+            return
         d = self.data
         self.ops.moe_layer_execute(self.plan, d.hidden if hidden is None else hidden, d.router, d.gate_up,
                                    d.down, self.out if out is None else out, self.ws, router_bias=d.bias,
                                    shared=d.shared, topk_ids=self.ids)
 
+    def capture(self):
+        """Capture one resident-input step in a CUDA graph (decode-sized steps are otherwise
+        bound by the host's launch rate, not by the GPU)."""
+        import torch
+        for _ in range(3):
+            self.step()
+        torch.cuda.synchronize()
+        before = self.ops.launch_count()
+        self.step()
+        self.launches_per_step = self.ops.launch_count() - before
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.ctx.use_current_stream()
+            self.step()
+        self.ctx.use_current_stream()
+        self.graph = graph
+
     def profile(self, iters):
         acc = {}
-        for _ in range(iters):
-            self.ops.profile_begin(self.ctx)
-            self.step()
-            for name, ms in self.ops.profile_end(self.ctx):
-                acc.setdefault(name, []).append(ms)
+        graph, self.graph = self.graph, None  # stage events are recorded by eager launches only
+        try:
+            for _ in range(iters):
+                self.ops.profile_begin(self.ctx)
+                self.step()
+                for name, ms in self.ops.profile_end(self.ctx):
+                    acc.setdefault(name, []).append(ms)
+        finally:
+            self.graph = graph
         return {k: statistics.mean(v) for k, v in acc.items()}
 
     def roofline(self, stage_ms, hbm_gbs, peak_kind):
@@ -447,6 +484,9 @@ def main():
                     help="N = 1 only: the FP8 decode batch (64 tokens, 128 experts, top-8) instead of the headline layer")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="N > 1: how the experts are assigned to ranks")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="N = 1: launch the resident-input steps eagerly instead of replaying one CUDA graph "
+                         "(the e2e leg is always eager)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernels-only", action="store_true",
                     help="only the device-timed loop (for profiler captures; prints no valid bench line)")

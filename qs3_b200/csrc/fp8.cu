@@ -43,36 +43,35 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(const float* f, float inv)
     return r;
 }
 
-// codes[prow, :] / scales[prow, :] = quantise(x[route / top_k, :]); one warp per route,
-// one 128-element group per step (4 elements per lane). route_prows == NULL: prow = route.
+// codes[prow, :] / scales[prow, :] = quantise(x[route / top_k, :]); one warp per (route,
+// 128-element group), 4 elements per lane. route_prows == NULL: prow = route.
 __global__ void __launch_bounds__(256)
 fp8_gather_quantize_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ route_prows,
                            uint32_t routes, uint32_t top_k, uint32_t k, uint8_t* __restrict__ codes,
                            float* __restrict__ scales)
 {
-    const uint32_t route = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const uint32_t groups = k / 128;
+    const uint64_t unit = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const uint32_t lane = threadIdx.x & 31;
-    if (route >= routes)
+    if (unit >= static_cast<uint64_t>(routes) * groups)
         return;
+    const uint32_t route = static_cast<uint32_t>(unit / groups), g = static_cast<uint32_t>(unit % groups);
     const int prow = route_prows != nullptr ? route_prows[route] : static_cast<int>(route);
     if (prow < 0)
         return;
     const uint2* src = reinterpret_cast<const uint2*>(x + static_cast<size_t>(route / top_k) * k);
     uint32_t* dst = reinterpret_cast<uint32_t*>(codes + static_cast<size_t>(prow) * k);
-    const uint32_t groups = k / 128;
-    for (uint32_t g = 0; g < groups; ++g) {
-        const uint2 v = src[g * 32 + lane];
-        const float f[4] = { bf16_bits_to_f32(v.x & 0xffffu), bf16_bits_to_f32(v.x >> 16),
-                             bf16_bits_to_f32(v.y & 0xffffu), bf16_bits_to_f32(v.y >> 16) };
-        float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+    const uint2 v = src[g * 32 + lane];
+    const float f[4] = { bf16_bits_to_f32(v.x & 0xffffu), bf16_bits_to_f32(v.x >> 16),
+                         bf16_bits_to_f32(v.y & 0xffffu), bf16_bits_to_f32(v.y >> 16) };
+    float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float s = fp8_scale_of(amax);
-        dst[g * 32 + lane] = pack_e4m3x4(f, __fdiv_rn(1.0f, s));
-        if (lane == 0)
-            scales[static_cast<size_t>(prow) * groups + g] = s;
-    }
+    for (int o = 16; o > 0; o >>= 1)
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = fp8_scale_of(amax);
+    dst[g * 32 + lane] = pack_e4m3x4(f, __fdiv_rn(1.0f, s));
+    if (lane == 0)
+        scales[static_cast<size_t>(prow) * groups + g] = s;
 }
 
 // One block per (k block, row block, expert): 128 x 128 weights -> codes + one scale.
@@ -439,8 +438,9 @@ cudaError_t launch_fp8_gather_quantize(const __nv_bfloat16* x, const int32_t* ro
 {
     if (routes == 0)
         return cudaSuccess;
-    fp8_gather_quantize_kernel<<<(routes + 7) / 8, 256, 0, stream>>>(x, route_prows, routes, top_k, k, codes,
-                                                                    scales);
+    const uint64_t units = static_cast<uint64_t>(routes) * (k / 128);
+    fp8_gather_quantize_kernel<<<static_cast<uint32_t>((units + 7) / 8), 256, 0, stream>>>(
+        x, route_prows, routes, top_k, k, codes, scales);
     note_launch();
     return cudaGetLastError();
 }
@@ -496,13 +496,7 @@ cudaError_t launch_fp8_gemm(const Fp8Gemm& g, cudaStream_t stream, const char** 
 
     // feature splits: enough CTAs to fill the resident slots of the device once
     const uint32_t slots = device_sm_count() * (two_per_sm ? 2u : 1u);
-    uint32_t want = std::max(1u, (slots + g.est_tiles - 1) / std::max(1u, g.est_tiles));
-    static const int forced = [] {
-        const char* v = getenv("QS3_FP8_SPLITS");
-        return v != nullptr ? atoi(v) : 0;
-    }();
-    if (forced > 0)
-        want = static_cast<uint32_t>(forced);
+    const uint32_t want = std::max(1u, (slots + g.est_tiles - 1) / std::max(1u, g.est_tiles));
     fp.fb_per_cta = std::max(1u, (fp.num_fb + want - 1) / want);
     const uint32_t splits = (fp.num_fb + fp.fb_per_cta - 1) / fp.fb_per_cta;
     if (g.max_tiles == 0 || g.max_tiles > 65535)

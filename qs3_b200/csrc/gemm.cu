@@ -311,24 +311,20 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                         break;
                     }
                     uint8_t* sb = ring + s * stage_bytes;
-                    if (p.debug & 1u) {
-                        mbar_arrive(&full_bar[s]);
-                    } else {
-                        mbar_expect_tx(&full_bar[s], stage_bytes);
-                        for (uint32_t q = 0; q < kbs; ++q) {
-                            const int c0 = static_cast<int>(st * kbs + q) * 128;
-                            uint8_t* dst = sb + q * kTileBytes;
-                            if (GATED) {
-                                tma_load_2d(dst, &map_b, &full_bar[s], c0, b_row);
-                                tma_load_2d(dst + kTileBytes / 2, &map_b, &full_bar[s], c0,
-                                            b_row + static_cast<int>(p.n));
-                            } else {
-                                tma_load_2d(dst, &map_b, &full_bar[s], c0, b_row);
-                            }
+                    mbar_expect_tx(&full_bar[s], stage_bytes);
+                    for (uint32_t q = 0; q < kbs; ++q) {
+                        const int c0 = static_cast<int>(st * kbs + q) * 128;
+                        uint8_t* dst = sb + q * kTileBytes;
+                        if (GATED) {
+                            tma_load_2d(dst, &map_b, &full_bar[s], c0, b_row);
+                            tma_load_2d(dst + kTileBytes / 2, &map_b, &full_bar[s], c0,
+                                        b_row + static_cast<int>(p.n));
+                        } else {
+                            tma_load_2d(dst, &map_b, &full_bar[s], c0, b_row);
                         }
-                        bulk_load(sb + kbs * kTileBytes, sfb_src + static_cast<uint64_t>(st * kbs) * kSfBytes,
-                                  kbs * kSfBytes, &full_bar[s]);
                     }
+                    bulk_load(sb + kbs * kTileBytes, sfb_src + static_cast<uint64_t>(st * kbs) * kSfBytes,
+                              kbs * kSfBytes, &full_bar[s]);
                     if (++s == stages) {
                         s = 0;
                         ph ^= 1;
@@ -366,26 +362,22 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     }
                     tc_fence_after();
                     const uint32_t sb = smem_u32(ring + s * stage_bytes);
-                    if (!(p.debug & 2u)) {
-                        for (uint32_t q = 0; q < kbs; ++q) {
-                            const uint32_t kb = st * kbs + q;
-                            // B scales alternate between two TMEM buffers so that this copy does
-                            // not have to wait for the previous k-block's MMAs to finish reading
-                            const uint32_t sfb_cols = tmem_sfb + 16 * sf_flip;
-                            sf_flip ^= 1;
-                            const uint32_t sf_smem = sb + kbs * kTileBytes + q * kSfBytes;
-                            if (!(p.debug & 8u)) {
+                    for (uint32_t q = 0; q < kbs; ++q) {
+                        const uint32_t kb = st * kbs + q;
+                        // B scales alternate between two TMEM buffers so that this copy does
+                        // not have to wait for the previous k-block's MMAs to finish reading
+                        const uint32_t sfb_cols = tmem_sfb + 16 * sf_flip;
+                        sf_flip ^= 1;
+                        const uint32_t sf_smem = sb + kbs * kTileBytes + q * kSfBytes;
 #pragma unroll
-                                for (uint32_t j = 0; j < 4; ++j)
-                                    tc_cp_scales(sfb_cols + 4 * j, scale_desc(sf_smem + j * 512));
-                            }
-                            const uint64_t da = operand_desc(a_addr + kb * kTileBytes);
-                            const uint64_t db = operand_desc(sb + q * kTileBytes);
+                        for (uint32_t j = 0; j < 4; ++j)
+                            tc_cp_scales(sfb_cols + 4 * j, scale_desc(sf_smem + j * 512));
+                        const uint64_t da = operand_desc(a_addr + kb * kTileBytes);
+                        const uint64_t db = operand_desc(sb + q * kTileBytes);
 #pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j)
-                                tc_mma_nvfp4(tmem_acc, da + 2 * j, db + 2 * j, kIdesc, (kb > 0 || j > 0) ? 1u : 0u,
-                                             tmem_sfa + 16 * kb + 4 * j, sfb_cols + 4 * j);
-                        }
+                        for (uint32_t j = 0; j < 4; ++j)
+                            tc_mma_nvfp4(tmem_acc, da + 2 * j, db + 2 * j, kIdesc, (kb > 0 || j > 0) ? 1u : 0u,
+                                         tmem_sfa + 16 * kb + 4 * j, sfb_cols + 4 * j);
                     }
                     tc_commit(&empty_bar[s]);
                     if (++s == stages) {
@@ -458,8 +450,7 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 }
                 continue;
             }
-            if (!(p.debug & 4u))
-                epilogue_tile<GATED, EPI, 2>(p, tmem_base + buf * kBN, warp & 3, lane, expert, row0, nrows, nt,
+            epilogue_tile<GATED, EPI, 2>(p, tmem_base + buf * kBN, warp & 3, lane, expert, row0, nrows, nt,
                                              warp >> 2);
             // hand the accumulator back once every lane of the warp has read it
             tc_fence_before();
@@ -637,15 +628,6 @@ cudaError_t launch_astat(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
     return cudaGetLastError();
 }
 
-bool astat_enabled()
-{
-    static const bool on = [] {
-        const char* v = getenv("QS3_GEMM_RESIDENT_A");
-        return v == nullptr || v[0] != '0';
-    }();
-    return on;
-}
-
 uint32_t sm_count()
 {
     static int count[64] = {};
@@ -662,6 +644,81 @@ uint32_t sm_count()
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- skinny bf16 GEMM for decode-sized batches ------------------------------------------------
+//
+// out[t, n] = sum_k A[t, k] * B[n, k] for a handful of rows (router logits of a decode batch):
+// one 128 x 128 tensor-core tile would stream all of k through a single SM, so instead every
+// output feature gets a block; a warp keeps its slice of the weight row in registers and
+// walks two rows of A (L2-resident), lanes split k, one shuffle reduction per output.
+constexpr uint32_t kSkinnyWarps = 8;
+constexpr uint32_t kSkinnyRowsPerWarp = 2;
+constexpr uint32_t kSkinnyMaxChunks = 16; // k <= 4096, in 256-element chunks (8 per lane)
+
+__global__ void __launch_bounds__(kSkinnyWarps * 32)
+gemm_skinny_kernel(const __nv_bfloat16* __restrict__ a, uint64_t a_pitch, const __nv_bfloat16* __restrict__ b,
+                   uint64_t b_pitch, uint32_t rows, uint32_t k, float* __restrict__ out, uint64_t out_pitch,
+                   float alpha, float beta, const float* __restrict__ bias)
+{
+    const uint32_t n = blockIdx.x;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t chunks = k / 256;
+    const uint4* wrow = reinterpret_cast<const uint4*>(b + static_cast<uint64_t>(n) * b_pitch);
+    uint4 wv[kSkinnyMaxChunks];
+#pragma unroll
+    for (uint32_t c = 0; c < kSkinnyMaxChunks; ++c)
+        wv[c] = c < chunks ? wrow[c * 32 + lane] : make_uint4(0, 0, 0, 0);
+    const uint32_t row0 = (blockIdx.y * kSkinnyWarps + warp) * kSkinnyRowsPerWarp;
+    for (uint32_t r = row0; r < min(rows, row0 + kSkinnyRowsPerWarp); ++r) {
+        const uint4* xrow = reinterpret_cast<const uint4*>(a + static_cast<uint64_t>(r) * a_pitch);
+        float acc = 0.0f;
+#pragma unroll
+        for (uint32_t c = 0; c < kSkinnyMaxChunks; ++c) {
+            if (c < chunks) {
+                const uint4 xv = xrow[c * 32 + lane];
+                const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
+                const uint32_t ws[4] = { wv[c].x, wv[c].y, wv[c].z, wv[c].w };
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc = fmaf(bf16_bits_to_f32(xs[j] & 0xffffu), bf16_bits_to_f32(ws[j] & 0xffffu), acc);
+                    acc = fmaf(bf16_bits_to_f32(xs[j] >> 16), bf16_bits_to_f32(ws[j] >> 16), acc);
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            float* o = out + static_cast<uint64_t>(r) * out_pitch + n;
+            float v = acc * (alpha == 0.0f ? 1.0f : alpha);
+            if (beta != 0.0f)
+                v += beta * *o;
+            if (bias != nullptr)
+                v += bias[n];
+            *o = v;
+        }
+    }
+}
+
+// Dense bf16 problem with f32 output whose rows would not fill one tensor-core tile.
+bool skinny_supported(const GemmProblem& g)
+{
+    return !g.nvfp4 && !g.gated && g.epilogue == EPI_STORE_F32 && g.tile_expert == nullptr && g.groups == 1
+        && g.group_scale == nullptr && g.a_rows <= 64 && g.k % 256 == 0 && g.k / 256 <= kSkinnyMaxChunks
+        && aligned16(g.a) && aligned16(g.b) && g.a_pitch_bytes % 16 == 0 && g.b_pitch_bytes % 16 == 0
+        && g.n <= 65535;
+}
+
+cudaError_t launch_skinny(const GemmProblem& g, cudaStream_t stream)
+{
+    const uint32_t rows = static_cast<uint32_t>(g.a_rows);
+    const dim3 grid(g.n, (rows + kSkinnyWarps * kSkinnyRowsPerWarp - 1) / (kSkinnyWarps * kSkinnyRowsPerWarp));
+    gemm_skinny_kernel<<<grid, kSkinnyWarps * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(g.a), g.a_pitch_bytes / 2, static_cast<const __nv_bfloat16*>(g.b),
+        g.b_pitch_bytes / 2, rows, g.k, static_cast<float*>(g.out), g.out_pitch_elems, g.alpha, g.beta, g.bias);
+    note_launch();
+    return cudaGetLastError();
+}
 
 TcParams make_params(const GemmProblem& g)
 {
@@ -688,11 +745,6 @@ TcParams make_params(const GemmProblem& g)
     tp.bias = g.bias;
     tp.out_global = g.out_global_scale == 0.0f ? 1.0f : g.out_global_scale;
     tp.err = device_error_word();
-    static const uint32_t debug = [] {
-        const char* v = getenv("QS3_GEMM_DEBUG");
-        return v != nullptr ? static_cast<uint32_t>(atoi(v)) : 0u;
-    }();
-    tp.debug = debug;
     return tp;
 }
 
@@ -732,12 +784,9 @@ cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** 
             *why = "more than 65535 row tiles";
         return cudaErrorNotSupported;
     }
-    const bool force_simt = [] {
-        const char* v = getenv("QS3_FORCE_SIMT");
-        return v != nullptr && v[0] == '1';
-    }();
-
-    if (gemm_tc_supported(g) && !(force_simt && !g.nvfp4)) {
+    if (skinny_supported(g))
+        return launch_skinny(g, stream);
+    if (gemm_tc_supported(g)) {
         const uint32_t feat = g.gated ? kBN / 2 : kBN;
         dim3 grid((g.n + feat - 1) / feat, m_tiles, 1);
         CUtensorMap ma, mb;
@@ -749,7 +798,7 @@ cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** 
                 *why = "cuTensorMapEncodeTiled failed";
             return cudaErrorInvalidValue;
         }
-        if (g.nvfp4 && tp.k_blocks <= kAsMaxKBlocks && astat_enabled()) {
+        if (g.nvfp4 && tp.k_blocks <= kAsMaxKBlocks) {
             // resident-A kernel: row tiles (estimated on the host) decide how far the
             // column tiles of one row tile are split over CTAs
             const uint32_t n_tiles = grid.x;

@@ -48,11 +48,10 @@ warp_histogram(const int32_t* ids, uint32_t routes, uint32_t local_offset, uint3
     __syncthreads();
 }
 
-__global__ void __launch_bounds__(kSortWarps * 32)
-route_hist_kernel(const int32_t* __restrict__ ids, uint32_t routes, uint32_t local_offset,
-                  uint32_t experts, int32_t* __restrict__ block_hist)
+__device__ __forceinline__ void route_hist_body(const int32_t* __restrict__ ids, uint32_t routes,
+                                                uint32_t local_offset, uint32_t experts,
+                                                int32_t* __restrict__ block_hist, uint16_t* s_hist)
 {
-    extern __shared__ uint16_t s_hist[];
     warp_histogram(ids, routes, local_offset, experts, s_hist);
     for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
         int total = 0;
@@ -63,12 +62,19 @@ route_hist_kernel(const int32_t* __restrict__ ids, uint32_t routes, uint32_t loc
     }
 }
 
+__global__ void __launch_bounds__(kSortWarps * 32)
+route_hist_kernel(const int32_t* __restrict__ ids, uint32_t routes, uint32_t local_offset,
+                  uint32_t experts, int32_t* __restrict__ block_hist)
+{
+    extern __shared__ uint16_t s_hist[];
+    route_hist_body(ids, routes, local_offset, experts, block_hist, s_hist);
+}
+
 // Single block: per expert, exclusive scan of the block histograms (column scan),
 // then exclusive scans over experts of the counts, of the counts padded to the
 // tile height, and of the tile counts; finally the tile table.
-__global__ void __launch_bounds__(1024)
-route_scan_kernel(int32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_t experts,
-                  RouteTables rt)
+__device__ __forceinline__ void route_scan_body(int32_t* __restrict__ block_hist, uint32_t num_blocks,
+                                                uint32_t experts, const RouteTables& rt)
 {
     __shared__ int s_warp[3][32];
     __shared__ int s_carry[3];
@@ -114,6 +120,8 @@ route_scan_kernel(int32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_
             incl[j] = x;
             if (lane == 31)
                 s_warp[j][warp] = x;
+            if (threadIdx.x < 32 && threadIdx.x >= blockDim.x / 32)
+                s_warp[j][threadIdx.x] = 0; // slots of warps this block does not have
         }
         __syncthreads();
         if (warp == 0) {
@@ -158,16 +166,22 @@ route_scan_kernel(int32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_
     }
 }
 
+__global__ void __launch_bounds__(1024)
+route_scan_kernel(int32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_t experts,
+                  RouteTables rt)
+{
+    route_scan_body(block_hist, num_blocks, experts, rt);
+}
+
 // Placement: row of a route = segment start + routes of the same expert in earlier
 // blocks + in earlier warps of this block + earlier in this warp. Stable in route
 // index, so the permutation is reproducible (upstream's is atomics-ordered).
-__global__ void __launch_bounds__(kSortWarps * 32)
-route_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weights,
-                   uint32_t routes, uint32_t top_k, uint32_t local_offset, uint32_t experts,
-                   RouteTables rt)
+// `s_hist` holds the per-warp histograms of this block (warp_histogram).
+__device__ __forceinline__ void route_place_body(const int32_t* __restrict__ ids,
+                                                 const float* __restrict__ weights, uint32_t routes,
+                                                 uint32_t top_k, uint32_t local_offset, uint32_t experts,
+                                                 const RouteTables& rt, uint16_t* s_hist)
 {
-    extern __shared__ uint16_t s_hist[];
-    warp_histogram(ids, routes, local_offset, experts, s_hist);
     // exclusive prefix over the warps of the block, per expert
     for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
         int run = 0;
@@ -210,6 +224,31 @@ route_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ we
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(kSortWarps * 32)
+route_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weights,
+                   uint32_t routes, uint32_t top_k, uint32_t local_offset, uint32_t experts,
+                   RouteTables rt)
+{
+    extern __shared__ uint16_t s_hist[];
+    warp_histogram(ids, routes, local_offset, experts, s_hist);
+    route_place_body(ids, weights, routes, top_k, local_offset, experts, rt, s_hist);
+}
+
+// All three steps in one block when the routes fit one block's chunk (decode batches):
+// the same arithmetic as the three kernels, without two launch boundaries.
+__global__ void __launch_bounds__(kSortWarps * 32)
+route_sort_small_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weights,
+                        uint32_t routes, uint32_t top_k, uint32_t local_offset, uint32_t experts,
+                        RouteTables rt)
+{
+    extern __shared__ uint16_t s_hist[];
+    route_hist_body(ids, routes, local_offset, experts, rt.block_hist, s_hist);
+    __syncthreads(); // block_hist (global) is read back by this block
+    route_scan_body(rt.block_hist, 1, experts, rt);
+    __syncthreads(); // indptr / pad_indptr (global) are read back by this block
+    route_place_body(ids, weights, routes, top_k, local_offset, experts, rt, s_hist);
 }
 
 // expanded[prow, :] = hidden[route / top_k, :]; one warp per route, 16-byte copies.
@@ -623,6 +662,19 @@ cudaError_t launch_route_sort(const int32_t* topk_ids, const float* topk_weights
                                        static_cast<int>(smem));
         if (err != cudaSuccess)
             return err;
+    }
+    if (rt.route_blocks == 1) {
+        if (smem > 48 * 1024) {
+            cudaError_t aerr = cudaFuncSetAttribute(route_sort_small_kernel,
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    static_cast<int>(smem));
+            if (aerr != cudaSuccess)
+                return aerr;
+        }
+        route_sort_small_kernel<<<1, kSortWarps * 32, smem, stream>>>(topk_ids, topk_weights, routes, top_k,
+                                                                     local_offset, experts, rt);
+        note_launch();
+        return cudaGetLastError();
     }
     route_hist_kernel<<<rt.route_blocks, kSortWarps * 32, smem, stream>>>(
         topk_ids, routes, local_offset, experts, rt.block_hist);

@@ -46,7 +46,6 @@ struct TcParams {
     float out_global;
     uint32_t* err;
     uint32_t tma_store; // resident-A kernel, bf16 output: stage the tile in smem and store it with TMA
-    uint32_t debug;     // timing experiments only (QS3_GEMM_DEBUG): 1 no loads, 2 no MMAs, 4 no epilogue
 };
 
 // Host helpers defined beside the GEMM launchers. make_operand_map: 2-D tensor map over a
