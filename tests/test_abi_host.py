@@ -285,3 +285,21 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(capi, "LIB_PATH", "/nonexistent/libqs3moe.so")
     with pytest.raises(RuntimeError, match="no CPU or library fallback"):
         capi.load()
+
+
+def test_header_compiles_as_c_and_cpp(tmp_path):
+    """include/qs3_moe.h is the drop-in boundary: it must be plain C (the upstream bindgen input
+    is C) and also valid C++, with no warnings under -Wall -Wextra -pedantic."""
+    import shutil
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "hdr_check.c"
+    src.write_text('#include "qs3_moe.h"\nint main(void) { qsfi_moe_plan_desc d; (void)d; '
+                   "return (int)sizeof(qs3_moe_layer_desc) == 0; }\n")
+    for compiler, flags in (("gcc", ["-std=c11", "-pedantic"]), ("g++", ["-std=c++17", "-x", "c++"])):
+        exe = shutil.which(compiler)
+        if exe is None:
+            pytest.skip(f"{compiler} not installed")
+        r = subprocess.run([exe, *flags, "-Wall", "-Wextra", "-Werror", "-fsyntax-only",
+                            "-I", os.path.join(root, "include"), str(src)], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
