@@ -479,6 +479,13 @@ typedef struct {
        then skips its own quantisation pass. `hidden` is still needed (router, shared gate). */
     qsfi_tensor2 hidden_packed;
     qsfi_tensor1 hidden_scale_tiled;
+    /* optional: the block's post-MoE neighbours fused into the combine (hidden <= 2048):
+       residual_inout (bf16 [num_tokens, hidden], contiguous) += the layer's output, in place,
+       and `out` receives rmsnorm(residual_inout) * next_norm_weight instead of the raw MoE
+       output, i.e. qsfi_fused_add_rmsnorm applied to the layer's output in the same pass. */
+    qsfi_tensor2 residual_inout;
+    qsfi_tensor1 next_norm_weight; /* bf16 [hidden] */
+    float next_norm_eps;
 } qs3_moe_layer_desc;
 
 qsfi_status qs3_moe_layer_workspace_size(

@@ -158,7 +158,8 @@ class MoeLayerDesc(C.Structure):
                 ("act_global_scale", C.c_float), ("act2_global_scale", C.c_float), ("out", Tensor2),
                 ("topk_ids", Tensor2), ("topk_weights", Tensor2), ("router_logits", Tensor2),
                 ("workspace", Tensor1), ("num_tokens", C.c_uint32), ("hidden_packed", Tensor2),
-                ("hidden_scale_tiled", Tensor1)]
+                ("hidden_scale_tiled", Tensor1), ("residual_inout", Tensor2), ("next_norm_weight", Tensor1),
+                ("next_norm_eps", C.c_float)]
 
 
 class MoeEpRouteDesc(C.Structure):

@@ -134,6 +134,11 @@ struct CombineParams {
     const __nv_bfloat16* gate_w;     // [H]
     int round_before_shared;         // 1: round the routed sum to bf16 first (upstream chain)
     int skip_empty;                  // 1: leave rows of tokens without any local route unwritten
+    // optional post-MoE neighbours fused in (hidden_size <= 2048): residual += out (bf16, in
+    // place) and out = rmsnorm(residual) * norm_weight, as qsfi_fused_add_rmsnorm would do
+    __nv_bfloat16* residual;         // [T, H] or NULL
+    const __nv_bfloat16* norm_weight; // [H]
+    float norm_eps;
 };
 
 struct EpPullParams {

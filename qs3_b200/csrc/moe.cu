@@ -997,6 +997,21 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
             return set_invalid_arg(ctx, "pre-quantised tokens need u8 [num_tokens, hidden/2] codes and tiled scales");
     }
 
+    const bool post_norm = d->residual_inout.data != nullptr;
+    if (post_norm) {
+        if (d->residual_inout.dtype != QSFI_DTYPE_BF16 || !contiguous2(d->residual_inout)
+            || d->residual_inout.shape[0] != t || d->residual_inout.shape[1] != h
+            || d->next_norm_weight.data == nullptr || d->next_norm_weight.dtype != QSFI_DTYPE_BF16
+            || d->next_norm_weight.shape[0] != h || !contiguous1(d->next_norm_weight)
+            || !aligned16(d->residual_inout.data) || !aligned16(d->next_norm_weight.data))
+            return set_invalid_arg(ctx, "fused post-MoE norm needs bf16 residual_inout [num_tokens, hidden] and "
+                                        "next_norm_weight [hidden], 16-byte aligned");
+        if (!std::isfinite(d->next_norm_eps) || d->next_norm_eps <= 0.0f)
+            return set_invalid_arg(ctx, "rmsnorm eps must be finite and > 0");
+        if (h > 2048)
+            return set_unsupported(ctx, "fused post-MoE norm supports hidden_size up to 2048");
+    }
+
     char* base = static_cast<char*>(d->workspace.data);
     cudaStream_t st = ctx->stream;
     const uint32_t routes = d->num_tokens * p.top_k;
@@ -1241,6 +1256,11 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         cp.hidden = hidden;
         cp.gate_w = static_cast<const __nv_bfloat16*>(d->shared_gate_weight.data);
         cp.round_before_shared = nvfp4 ? 0 : 1;
+    }
+    if (post_norm) {
+        cp.residual = static_cast<__nv_bfloat16*>(d->residual_inout.data);
+        cp.norm_weight = static_cast<const __nv_bfloat16*>(d->next_norm_weight.data);
+        cp.norm_eps = d->next_norm_eps;
     }
     status = set_cuda_error(ctx, launch_combine(cp, st), "qs3_moe_layer_execute");
     stage_mark(st, STAGE_END);

@@ -432,6 +432,180 @@ __global__ void __launch_bounds__(kCombineTokens* kCombineGroup, 4) combine_kern
     }
 }
 
+// The combine above followed by the block's post-MoE neighbours in the same pass:
+//   x        = bf16(sum_k w_k * Y2[row_k] (+ shared term))        (what combine_kernel stores)
+//   residual = bf16(f32(x) + f32(residual))                       (in place)
+//   out      = bf16((f32(x) + f32(residual)) * rsqrt(mean(.^2) + eps) * norm_weight)
+// i.e. qsfi_fused_add_rmsnorm applied to the MoE output without the round trip of [T, H]
+// through HBM. A thread keeps its four chunks of the row in registers across the row-wide
+// reduction, so rows are limited to 4 * 64 * 8 = 2048 elements.
+__global__ void __launch_bounds__(kCombineTokens* kCombineGroup, 2) combine_norm_kernel(CombineParams p)
+{
+    __shared__ int s_row[kCombineTokens][32];
+    __shared__ float s_w[kCombineTokens][32];
+    __shared__ float s_dot[kCombineTokens][kCombineGroup / 32];
+    __shared__ float s_sq[kCombineTokens][kCombineGroup / 32];
+    __shared__ int s_any[kCombineTokens];
+    const uint32_t group = threadIdx.x / kCombineGroup, gl = threadIdx.x % kCombineGroup;
+    const uint32_t token = blockIdx.x * kCombineTokens + group;
+    const bool live = token < p.num_tokens;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t vec_per_row = p.hidden_size / 8;
+
+    if (gl < 32) {
+        int row = -1;
+        float wgt = 0.0f;
+        if (live && gl < p.top_k) {
+            row = p.route_prows[static_cast<size_t>(token) * p.top_k + gl];
+            wgt = p.topk_weights[static_cast<size_t>(token) * p.top_k + gl];
+        }
+        const uint32_t valid = __ballot_sync(0xffffffffu, row >= 0);
+        if (row >= 0) {
+            const uint32_t slot = __popc(valid & ((1u << gl) - 1u));
+            s_row[group][slot] = row;
+            s_w[group][slot] = wgt;
+        }
+        if (gl == 0)
+            s_any[group] = __popc(valid);
+    }
+    float dot = 0.0f;
+    if (p.shared_out != nullptr) {
+        if (live) {
+            const uint4* x = reinterpret_cast<const uint4*>(p.hidden) + static_cast<size_t>(token) * vec_per_row;
+            const uint4* w = reinterpret_cast<const uint4*>(p.gate_w);
+            for (uint32_t i = gl; i < vec_per_row; i += kCombineGroup) {
+                const uint4 xv = x[i], wv = w[i];
+                const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
+                const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    dot += bf16_bits_to_f32(xs[j] & 0xffffu) * bf16_bits_to_f32(ws[j] & 0xffffu);
+                    dot += bf16_bits_to_f32(xs[j] >> 16) * bf16_bits_to_f32(ws[j] >> 16);
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0)
+            s_dot[group][gl / 32] = dot;
+    }
+    __syncthreads();
+    float gate = 0.0f;
+    if (p.shared_out != nullptr) {
+        dot = 0.0f;
+#pragma unroll
+        for (uint32_t w = 0; w < kCombineGroup / 32; ++w)
+            dot += s_dot[group][w];
+        gate = sigmoid_fast(dot);
+    }
+
+    const uint4* y2 = reinterpret_cast<const uint4*>(p.expert_out);
+    const uint32_t n_valid = live ? static_cast<uint32_t>(s_any[group]) : 0u;
+    uint4* res = reinterpret_cast<uint4*>(p.residual) + static_cast<size_t>(live ? token : 0) * vec_per_row;
+    float vals[4][8]; // chunks gl, gl + 64, gl + 128, gl + 192 of the row
+    float sum_sq = 0.0f;
+#pragma unroll
+    for (uint32_t step = 0; step < 2; ++step) {
+        const uint32_t i0 = gl + step * 2 * kCombineGroup, i1 = i0 + kCombineGroup;
+        const bool one = live && i0 < vec_per_row, two = live && i1 < vec_per_row;
+        float* acc0 = vals[2 * step];
+        float* acc1 = vals[2 * step + 1];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            acc0[j] = acc1[j] = 0.0f;
+        for (uint32_t k0 = 0; k0 < n_valid; k0 += 4) {
+            uint4 v0[4], v1[4];
+            float w[4];
+            int row[4];
+#pragma unroll
+            for (uint32_t q = 0; q < 4; ++q) {
+                row[q] = k0 + q < n_valid ? s_row[group][k0 + q] : -1;
+                w[q] = row[q] >= 0 ? s_w[group][k0 + q] : 0.0f;
+                const uint4* src = y2 + static_cast<size_t>(row[q] >= 0 ? row[q] : 0) * vec_per_row;
+                v0[q] = (row[q] >= 0 && one) ? src[i0] : make_uint4(0, 0, 0, 0);
+                v1[q] = (row[q] >= 0 && two) ? src[i1] : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (uint32_t q = 0; q < 4; ++q) {
+                if (row[q] < 0)
+                    continue;
+                accumulate_row(acc0, v0[q], w[q]);
+                accumulate_row(acc1, v1[q], w[q]);
+            }
+        }
+#pragma unroll
+        for (int hsel = 0; hsel < 2; ++hsel) {
+            float* acc = hsel == 0 ? acc0 : acc1;
+            const uint32_t i = hsel == 0 ? i0 : i1;
+            if (!(hsel == 0 ? one : two))
+                continue;
+            if (p.shared_out != nullptr) {
+                const uint4 sv
+                    = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
+                const uint32_t ss[4] = { sv.x, sv.y, sv.z, sv.w };
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float a0 = acc[2 * j], a1 = acc[2 * j + 1];
+                    if (p.round_before_shared) {
+                        a0 = __bfloat162float(__float2bfloat16(a0));
+                        a1 = __bfloat162float(__float2bfloat16(a1));
+                    }
+                    acc[2 * j] = a0 + gate * bf16_bits_to_f32(ss[j] & 0xffffu);
+                    acc[2 * j + 1] = a1 + gate * bf16_bits_to_f32(ss[j] >> 16);
+                }
+            }
+            const uint4 rv = res[i];
+            const uint32_t rs[4] = { rv.x, rv.y, rv.z, rv.w };
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // the MoE output as the unfused path would have stored it, plus the residual
+                const float x0 = __bfloat162float(__float2bfloat16(acc[2 * j]));
+                const float x1 = __bfloat162float(__float2bfloat16(acc[2 * j + 1]));
+                acc[2 * j] = x0 + bf16_bits_to_f32(rs[j] & 0xffffu);
+                acc[2 * j + 1] = x1 + bf16_bits_to_f32(rs[j] >> 16);
+                sum_sq += acc[2 * j] * acc[2 * j] + acc[2 * j + 1] * acc[2 * j + 1];
+                const __nv_bfloat162 r2 = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                o[j] = *reinterpret_cast<const uint32_t*>(&r2);
+            }
+            res[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, o);
+    if (lane == 0)
+        s_sq[group][gl / 32] = sum_sq;
+    __syncthreads();
+    if (!live)
+        return;
+    float total = 0.0f;
+#pragma unroll
+    for (uint32_t w = 0; w < kCombineGroup / 32; ++w)
+        total += s_sq[group][w];
+    const float inv_rms = 1.0f / sqrtf(total / static_cast<float>(p.hidden_size) + p.norm_eps);
+    uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
+    const uint4* nw = reinterpret_cast<const uint4*>(p.norm_weight);
+#pragma unroll
+    for (uint32_t c = 0; c < 4; ++c) {
+        const uint32_t i = gl + c * kCombineGroup;
+        if (i >= vec_per_row)
+            continue;
+        const uint4 wv = nw[i];
+        const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 r2
+                = __floats2bfloat162_rn(vals[c][2 * j] * inv_rms * bf16_bits_to_f32(ws[j] & 0xffffu),
+                                        vals[c][2 * j + 1] * inv_rms * bf16_bits_to_f32(ws[j] >> 16));
+            o[j] = *reinterpret_cast<const uint32_t*>(&r2);
+        }
+        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 // rows[t * ranks + r] = r * tokens + t, weights = 1: lets the combine kernel sum the
 // per-rank partial rows of one token in ascending rank order.
 __global__ void ep_rank_routes_kernel(int32_t* rows, float* weights, uint32_t tokens, uint32_t ranks)
@@ -723,8 +897,14 @@ cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream)
 {
     if (p.num_tokens == 0)
         return cudaSuccess;
-    combine_kernel<<<(p.num_tokens + kCombineTokens - 1) / kCombineTokens, kCombineTokens * kCombineGroup, 0,
-                     stream>>>(p);
+    const uint32_t blocks = (p.num_tokens + kCombineTokens - 1) / kCombineTokens;
+    if (p.residual != nullptr) {
+        if (p.hidden_size > 4 * kCombineGroup * 8 || p.skip_empty)
+            return cudaErrorNotSupported;
+        combine_norm_kernel<<<blocks, kCombineTokens * kCombineGroup, 0, stream>>>(p);
+    } else {
+        combine_kernel<<<blocks, kCombineTokens * kCombineGroup, 0, stream>>>(p);
+    }
     note_launch();
     return cudaGetLastError();
 }

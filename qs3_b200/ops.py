@@ -444,7 +444,8 @@ def moe_layer_execute(plan: MoePlan, hidden, router_weight, gate_up, down, out, 
                       router_bias=None, shared: SharedExpert | None = None,
                       score=capi.ROUTER_SCORE_SOFTMAX, renormalize=True, routed_scaling_factor=1.0,
                       act_global_scale=1.0, act2_global_scale=1.0, topk_ids=None, topk_weights=None,
-                      router_logits=None, num_tokens=None, hidden_packed=None, hidden_scale_tiled=None):
+                      router_logits=None, num_tokens=None, hidden_packed=None, hidden_scale_tiled=None,
+                      residual_inout=None, next_norm_weight=None, next_norm_eps=1e-6):
     """``qs3_moe_layer_execute``: the whole layer of upstream ``execute_moe_mlp``
     (src/model.rs:2072-2228) in one call. ``gate_up`` / ``down`` are bf16 tensors for
     a bf16 plan, :class:`Nvfp4Weight` for an NVFP4 plan and :class:`Fp8Weight` for an FP8
@@ -486,6 +487,9 @@ def moe_layer_execute(plan: MoePlan, hidden, router_weight, gate_up, down, out, 
     d.num_tokens = hidden.shape[0] if num_tokens is None else num_tokens
     d.hidden_packed = _desc(hidden_packed, 2)
     d.hidden_scale_tiled = _desc(hidden_scale_tiled, 1)
+    d.residual_inout = _desc(residual_inout, 2)
+    d.next_norm_weight = _desc(next_norm_weight, 1)
+    d.next_norm_eps = next_norm_eps
     ctx.check(ctx._lib.qs3_moe_layer_execute(ctx.handle, plan.handle, C.byref(d)))
 
 

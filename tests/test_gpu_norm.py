@@ -160,3 +160,53 @@ def test_layer_takes_the_tokens_the_norm_quantised(ops, ctx, oracle):
         assert ctx.read_device_error() == 0
         outs.append(to_np(out))
     assert np.array_equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("kind", ["nvfp4_shared", "bf16", "fp8"])
+def test_layer_with_fused_post_norm(ops, ctx, oracle, kind):
+    """Post-MoE residual add + next-layer RMSNorm folded into the combine == the layer call
+    followed by qsfi_fused_add_rmsnorm: residual bit-exact, norm within one bf16 step (the
+    row sum of squares is reduced in a different order)."""
+    from helpers import make_moe_inputs
+    t, h, e, k, i = 150, 512, 16, 4, 256
+    s = 256 if kind == "nvfp4_shared" else 0
+    d = make_moe_inputs(91, t, h, e, i, s)
+    rng = d["rng"]
+    resid = bf16(rng.standard_normal((t, h), dtype=np.float32))
+    nw = bf16(1.0 + 0.1 * rng.standard_normal(h, dtype=np.float32))
+    shared = None
+    if kind == "nvfp4_shared":
+        backend = ops.capi.MOE_BACKEND_NVFP4
+        gu = ops.nvfp4_quantize_weight(ctx, to_dev(d["gate_up"]), True)
+        dn = ops.nvfp4_quantize_weight(ctx, to_dev(d["down"]), False)
+        shared = ops.SharedExpert(ops.nvfp4_quantize_weight(ctx, to_dev(d["sh_gate_up"]), True),
+                                  ops.nvfp4_quantize_weight(ctx, to_dev(d["sh_down"]), False),
+                                  to_dev(d["sh_gate"]), s)
+    elif kind == "fp8":
+        backend = ops.capi.MOE_BACKEND_FP8_BLOCKSCALE
+        gu, dn = ops.fp8_quantize_weight(ctx, to_dev(d["gate_up"])), ops.fp8_quantize_weight(ctx, to_dev(d["down"]))
+    else:
+        backend = ops.capi.MOE_BACKEND_STAGED_BF16
+        gu, dn = to_dev(d["gate_up"]), to_dev(d["down"])
+    plan = ops.MoePlan(ctx, ops.MoePlanConfig(max_num_tokens=t, hidden_size=h, intermediate_size=i,
+                                              num_experts=e, top_k=k, backend=backend))
+    ws = torch.zeros(plan.layer_workspace_size(t, s), dtype=torch.uint8, device="cuda")
+    x = to_dev(d["hidden"])
+    # unfused: layer, then the stand-alone fused add + norm
+    out_a = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+    res_a = to_dev(resid)
+    ops.moe_layer_execute(plan, x, to_dev(d["router"]), gu, dn, out_a, ws, shared=shared)
+    moe_out = to_np(out_a)
+    ops.fused_add_rmsnorm(ctx, out_a, res_a, to_dev(nw), 1e-6)
+    # fused
+    out_b = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+    res_b = to_dev(resid)
+    ops.moe_layer_execute(plan, x, to_dev(d["router"]), gu, dn, out_b, ws, shared=shared,
+                          residual_inout=res_b, next_norm_weight=to_dev(nw), next_norm_eps=1e-6)
+    torch.cuda.synchronize()
+    assert ctx.read_device_error() == 0
+    assert np.array_equal(to_np(res_b), to_np(res_a))
+    want_norm, want_res = oracle.fused_add_rmsnorm(moe_out, resid, nw, 1e-6)
+    assert np.max(np.abs(f32(to_np(res_b)) - want_res)) <= 0.04
+    assert np.max(np.abs(f32(to_np(out_b)) - want_norm)) <= 0.06
+    assert np.max(np.abs(f32(to_np(out_b)) - f32(to_np(out_a)))) <= 0.04   # at most one bf16 step apart
