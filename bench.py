@@ -463,6 +463,10 @@ class SingleGpuLayer:
         # kernels (FP8: on this very workload; NVFP4: on a reduced case of the same layer, scaled here by
         # the algorithmic bytes of the full launch); see the ncu summaries under profiles/
         traffic = 1.02 * algo
+        # tensor-pipe ceiling of the operand format, measured now on this device (issue loop of
+        # 128 x 256 tcgen05.mma from resident shared-memory tiles)
+        fmt = "fp8" if cfg.fp8 else "nvfp4"
+        ceiling = self.ops.tensor_peak_probe(self.ctx, fmt, 256, 20000)
         out = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
                "frac": achieved / hbm_gbs, "traffic": traffic,
                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, ratio to algorithmic bytes "
@@ -470,7 +474,9 @@ class SingleGpuLayer:
                "peak_source": f"{peak_kind} copy bandwidth",
                "kernel": kernel, "kernel_ms": ms, "algorithmic_bytes": algo, "experts_hit": hit,
                "max_rows_per_expert": int(counts.max().item()),
-               "tensor_tflops": flops / (ms * 1e-3) / 1e12, key: flops / (ms * 1e-3) / nominal}
+               "tensor_tflops": flops / (ms * 1e-3) / 1e12, key: flops / (ms * 1e-3) / nominal,
+               "tensor_ceiling_tflops_measured": ceiling,
+               "tensor_frac_of_measured_ceiling": flops / (ms * 1e-3) / 1e12 / ceiling}
         ms2 = stage_ms.get("down_gemm")
         if ms2:
             algo2 = hit * d_bytes + act_out + routes * cfg.hidden * 2
