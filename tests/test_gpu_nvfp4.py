@@ -146,3 +146,39 @@ def test_whole_layer_matches_oracle(ops, ctx, oracle, cfg):
     if s:
         full = oracle.shared_expert_bf16(d["hidden"], d["sh_gate_up"], d["sh_down"], d["sh_gate"], full)
     assert rel_l2(to_np(out), full) <= 0.25
+
+
+def test_layer_call_replays_from_a_cuda_graph(ops, oracle):
+    """The whole-layer call (with its internal side-stream fork for the shared expert) captured
+    once in a CUDA graph and replayed on fresh inputs gives the eager result bit for bit."""
+    t, h, e, k, i, s = 256, 512, 32, 4, 256, 256
+    d = make_moe_inputs(35, t, h, e, i, s)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ctx = ops.Context()          # bound to this (non-default) stream
+        gu, dn, sh = _quantise_all(ops, ctx, d, True)
+        shared = ops.SharedExpert(sh[0], sh[1], to_dev(d["sh_gate"]), s)
+        plan = ops.MoePlan(ctx, ops.MoePlanConfig(max_num_tokens=t, hidden_size=h, intermediate_size=i,
+                                                  num_experts=e, top_k=k, backend=ops.capi.MOE_BACKEND_NVFP4))
+        ws = torch.zeros(plan.layer_workspace_size(t, s), dtype=torch.uint8, device="cuda")
+        x = to_dev(d["hidden"])
+        router = to_dev(d["router"])
+        out = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+        run = lambda: ops.moe_layer_execute(plan, x, router, gu, dn, out, ws, shared=shared)
+        for _ in range(2):
+            run()
+        stream.synchronize()
+        eager_first = to_np(out)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            run()
+        # new tokens in the same buffer: the graph must recompute everything from them
+        x.copy_(to_dev(bf16(f32(d["hidden"])[::-1].copy())))
+        graph.replay()
+        stream.synchronize()
+        replayed = to_np(out)
+        run()
+        stream.synchronize()
+        assert ctx.read_device_error() == 0
+        assert np.array_equal(replayed, to_np(out))
+        assert not np.array_equal(replayed, eager_first)
