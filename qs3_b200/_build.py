@@ -17,6 +17,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 SRC_DIR = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(SRC_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libqs3moe.so")
+CHECKED_LIB_PATH = os.path.join(PKG_DIR, "libqs3moe_checked.so")
 
 SOURCES = ["context.cu", "router.cu", "routing.cu", "gemm.cu", "gemm_api.cu", "nvfp4.cu", "moe.cu",
            "peak_probe.cu", "fp8.cu", "norm.cu"]
@@ -43,20 +44,26 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, checked: bool = False) -> str:
+    """Compile the library in-tree. ``checked`` builds the variant with device-side input
+    validation (``-DQSFI_ENABLE_CHECKED_VALIDATION=1``, as upstream's checked test binary):
+    ``libqs3moe_checked.so`` next to the release ``libqs3moe.so``."""
     nvcc = _nvcc()
-    os.makedirs(OBJ_DIR, exist_ok=True)
+    obj_dir = OBJ_DIR + ("_checked" if checked else "")
+    lib_path = CHECKED_LIB_PATH if checked else LIB_PATH
+    flags = NVCC_FLAGS + (["-DQSFI_ENABLE_CHECKED_VALIDATION=1"] if checked else [])
+    os.makedirs(obj_dir, exist_ok=True)
     headers = [os.path.join(SRC_DIR, h) for h in HEADERS]
     jobs = []
     for src in SOURCES:
         s = os.path.join(SRC_DIR, src)
-        o = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
+        o = os.path.join(obj_dir, src.replace(".cu", ".o"))
         if force or _stale(o, [s] + headers):
             jobs.append((s, o))
 
     def compile_one(job):
         s, o = job
-        cmd = [nvcc, *NVCC_FLAGS, "-c", s, "-o", o]
+        cmd = [nvcc, *flags, "-c", s, "-o", o]
         if verbose:
             cmd[1:1] = ["-Xptxas", "-v"]
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -68,14 +75,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 sys.stderr.write(r.stderr)
             if r.returncode != 0:
                 raise RuntimeError(f"nvcc failed on {s}:\n{r.stdout}\n{r.stderr}")
-    objs = [os.path.join(OBJ_DIR, s.replace(".cu", ".o")) for s in SOURCES]
-    if force or jobs or _stale(LIB_PATH, objs):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-Xcompiler", "-fPIC"]
+    objs = [os.path.join(obj_dir, s.replace(".cu", ".o")) for s in SOURCES]
+    if force or jobs or _stale(lib_path, objs):
+        cmd = [nvcc, "-shared", "-o", lib_path, *objs, "-Xcompiler", "-fPIC"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, checked=True))

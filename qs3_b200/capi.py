@@ -12,6 +12,7 @@ import os
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libqs3moe.so")
+CHECKED_LIB_PATH = os.path.join(PKG_DIR, "libqs3moe_checked.so")
 
 ERROR_MESSAGE_BYTES = 512
 
@@ -300,6 +301,16 @@ _SIGNATURES = {
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
 _lib = None
+_checked_lib = None
+
+
+def _bind(path: str) -> C.CDLL:
+    lib = C.CDLL(path)
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
 
 
 def load() -> C.CDLL:
@@ -310,10 +321,16 @@ def load() -> C.CDLL:
             raise RuntimeError(
                 f"{LIB_PATH} is missing: build it with `python -m qs3_b200._build` "
                 "(nvcc, sm_100a). There is no CPU or library fallback for this path.")
-        lib = C.CDLL(LIB_PATH)
-        for name, (res, args) in _SIGNATURES.items():
-            fn = getattr(lib, name)
-            fn.restype = res
-            fn.argtypes = args
-        _lib = lib
+        _lib = _bind(LIB_PATH)
     return _lib
+
+
+def load_checked() -> C.CDLL:
+    """Load ``libqs3moe_checked.so``, the build with device-side input validation
+    (``QSFI_ENABLE_CHECKED_VALIDATION=1``: one stream sync per validated call)."""
+    global _checked_lib
+    if _checked_lib is None:
+        if not os.path.exists(CHECKED_LIB_PATH):
+            raise RuntimeError(f"{CHECKED_LIB_PATH} is missing: build it with `python -m qs3_b200._build`.")
+        _checked_lib = _bind(CHECKED_LIB_PATH)
+    return _checked_lib

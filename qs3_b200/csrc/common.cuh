@@ -52,6 +52,14 @@ qsfi_status status_from_cuda(cudaError_t err);
 // Device-side error word shared by the tensor-core kernels (one per device).
 uint32_t* device_error_word();
 
+#if QSFI_ENABLE_CHECKED_VALIDATION
+// Checked builds only (upstream qsfi_native_common.h checked-validation flag): a device flag
+// that validator kernels raise; `checked_flag_finish` copies it back (one stream sync) and
+// returns true when it was raised. The flag lives in the library, nothing is allocated.
+int* checked_flag_reset(cudaStream_t stream, cudaError_t* err);
+bool checked_flag_finish(cudaStream_t stream, cudaError_t* err);
+#endif
+
 // Kernel-launch counter (all kernels of this library) and the optional per-stage
 // event recorder behind qs3_moe_profile_begin / qs3_moe_profile_end.
 void note_launch(uint32_t n = 1);

@@ -120,6 +120,31 @@ static StageRecorder g_rec;
 
 bool stage_recording() { return g_rec.on; }
 
+#if QSFI_ENABLE_CHECKED_VALIDATION
+__device__ int g_checked_flag;
+
+int* checked_flag_reset(cudaStream_t stream, cudaError_t* err)
+{
+    int* flag = nullptr;
+    *err = cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_checked_flag);
+    if (*err == cudaSuccess)
+        *err = cudaMemsetAsync(flag, 0, sizeof(int), stream);
+    return flag;
+}
+
+bool checked_flag_finish(cudaStream_t stream, cudaError_t* err)
+{
+    int* flag = nullptr;
+    int host = 0;
+    *err = cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_checked_flag);
+    if (*err == cudaSuccess)
+        *err = cudaMemcpyAsync(&host, flag, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (*err == cudaSuccess)
+        *err = cudaStreamSynchronize(stream);
+    return host != 0;
+}
+#endif
+
 void stage_mark(cudaStream_t stream, int stage)
 {
     if (!g_rec.on || g_rec.count >= 64)

@@ -516,6 +516,57 @@ qsfi_status validate_routing_tensors(qsfi_context* ctx, const qsfi_moe_plan_desc
     return QSFI_STATUS_OK;
 }
 
+#if QSFI_ENABLE_CHECKED_VALIDATION
+// upstream validate_routes_kernel, qsfi_moe.cu:307-325, with one difference: a plan that
+// owns only part of the experts (expert parallelism, rejected upstream) accepts every id of
+// the global range, since routes to other ranks' experts are legal there
+__global__ void validate_routes_kernel(const int32_t* topk_ids, const float* topk_weights, uint32_t total_routes,
+                                       int32_t first_valid, int32_t num_valid, int* error)
+{
+    const uint32_t route = blockIdx.x * blockDim.x + threadIdx.x;
+    if (route >= total_routes)
+        return;
+    const int32_t rel = topk_ids[route] - first_valid;
+    if (rel < 0 || rel >= num_valid || !isfinite(topk_weights[route]))
+        atomicExch(error, 1);
+}
+#endif
+
+// Checked builds: every route must name a valid expert and carry a finite weight (upstream
+// validate_moe_routes, qsfi_moe.cu:494-537; costs one stream sync). Release builds: no-op.
+qsfi_status validate_routes_checked(qsfi_context* ctx, const qsfi_moe_plan_desc& p, const void* ids,
+                                    const void* weights, uint32_t total_routes)
+{
+#if !QSFI_ENABLE_CHECKED_VALIDATION
+    (void)ctx;
+    (void)p;
+    (void)ids;
+    (void)weights;
+    (void)total_routes;
+    return QSFI_STATUS_OK;
+#else
+    cudaError_t err = cudaSuccess;
+    int* flag = checked_flag_reset(ctx->stream, &err);
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "cudaMemsetAsync MoE route validation flag");
+    const bool whole = p.local_num_experts == p.num_experts;
+    validate_routes_kernel<<<(total_routes + 255) / 256, 256, 0, ctx->stream>>>(
+        static_cast<const int32_t*>(ids), static_cast<const float*>(weights), total_routes,
+        whole ? static_cast<int32_t>(p.local_expert_offset) : 0,
+        static_cast<int32_t>(whole ? p.local_num_experts : p.num_experts), flag);
+    note_launch();
+    err = cudaGetLastError();
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "launch MoE route validation");
+    const bool bad = checked_flag_finish(ctx->stream, &err);
+    if (err != cudaSuccess)
+        return set_cuda_error(ctx, err, "copy MoE route validation flag");
+    if (bad)
+        return set_invalid_arg(ctx, "MoE routes must target local experts and weights must be finite");
+    return QSFI_STATUS_OK;
+#endif
+}
+
 qsfi_status validate_workspace(qsfi_context* ctx, const qsfi_tensor1& ws, size_t need)
 {
     qsfi_status status = validate_tensor(ctx, ws, "workspace", ws.dtype);
@@ -684,6 +735,10 @@ qsfi_status qsfi_moe_execute_bf16(qsfi_context* ctx, const qsfi_moe_plan* plan,
         || !aligned16(desc->down_weight.data) || (reinterpret_cast<uintptr_t>(desc->workspace.data) & 255u) != 0)
         return set_invalid_arg(ctx, "MoE tensors must be 16-byte aligned and the workspace 256-byte aligned");
 
+    status = validate_routes_checked(ctx, p, desc->topk_ids.data, desc->topk_weights.data,
+                                     desc->num_tokens * p.top_k);
+    if (status != QSFI_STATUS_OK)
+        return status;
     Bf16Workspace w = carve_bf16(static_cast<char*>(desc->workspace.data), p, desc->num_tokens);
     const uint32_t routes = desc->num_tokens * p.top_k;
     cudaError_t err = launch_route_sort(static_cast<const int32_t*>(desc->topk_ids.data),
@@ -784,6 +839,10 @@ qsfi_status qsfi_moe_execute_nvfp4(qsfi_context* ctx, const qsfi_moe_plan* plan,
         || (reinterpret_cast<uintptr_t>(desc->down_weight_scale.data) & 3u) != 0)
         return set_invalid_arg(ctx, "NVFP4 MoE tensors must be 16-byte aligned (scales 4-byte aligned)");
 
+    status = validate_routes_checked(ctx, p, desc->topk_ids.data, desc->topk_weights.data,
+                                     desc->num_tokens * p.top_k);
+    if (status != QSFI_STATUS_OK)
+        return status;
     Nvfp4Workspace w = carve_nvfp4(static_cast<char*>(desc->workspace.data), p, desc->num_tokens, true);
     const uint32_t routes = desc->num_tokens * p.top_k;
     cudaStream_t st = ctx->stream;
@@ -1833,6 +1892,10 @@ qsfi_status qsfi_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, c
         || !aligned16(desc->down_weight.data))
         return set_invalid_arg(ctx, "FP8 MoE tensors must be 16-byte aligned");
 
+    status = validate_routes_checked(ctx, p, desc->topk_ids.data, desc->topk_weights.data,
+                                     desc->num_tokens * p.top_k);
+    if (status != QSFI_STATUS_OK)
+        return status;
     Fp8Workspace w = carve_fp8(static_cast<char*>(desc->workspace.data), p, desc->num_tokens);
     const uint32_t routes = desc->num_tokens * p.top_k;
     cudaStream_t st = ctx->stream;

@@ -418,6 +418,25 @@ qsfi_status validate_router_desc(const qscu_router_topk_desc* d)
 
 } // namespace qs3
 
+#if QSFI_ENABLE_CHECKED_VALIDATION
+namespace qs3 {
+namespace {
+// upstream validate_finite_tensor2_contents (qscu.cu:158-246): any non-finite logit raises the flag
+template <typename T>
+__global__ void validate_finite_kernel(const T* v, uint64_t rows, uint64_t cols, int64_t stride0, int64_t stride1,
+                                       int* error)
+{
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * cols)
+        return;
+    const int64_t off = static_cast<int64_t>(i / cols) * stride0 + static_cast<int64_t>(i % cols) * stride1;
+    if (!isfinite(static_cast<float>(v[off])))
+        atomicExch(error, 1);
+}
+} // namespace
+} // namespace qs3
+#endif
+
 using namespace qs3;
 
 extern "C" {
@@ -427,6 +446,35 @@ qsfi_status qscu_router_topk(const qscu_router_topk_desc* desc, qsfi_cuda_stream
     qsfi_status status = validate_router_desc(desc);
     if (status != QSFI_STATUS_OK)
         return status;
+#if QSFI_ENABLE_CHECKED_VALIDATION
+    {
+        // "qscu router logits contain non-finite values" (upstream qscu.cu:1824-1834)
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        cudaError_t verr = cudaSuccess;
+        int* flag = checked_flag_reset(st, &verr);
+        if (verr != cudaSuccess)
+            return status_from_cuda(verr);
+        const uint64_t total = static_cast<uint64_t>(desc->num_tokens) * desc->num_experts;
+        const uint32_t blocks = static_cast<uint32_t>((total + 255) / 256);
+        if (desc->logits.dtype == QSFI_DTYPE_BF16)
+            validate_finite_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(desc->logits.data),
+                                                          desc->num_tokens, desc->num_experts,
+                                                          desc->logits.stride[0], desc->logits.stride[1], flag);
+        else
+            validate_finite_kernel<<<blocks, 256, 0, st>>>(static_cast<const float*>(desc->logits.data),
+                                                          desc->num_tokens, desc->num_experts,
+                                                          desc->logits.stride[0], desc->logits.stride[1], flag);
+        note_launch();
+        verr = cudaGetLastError();
+        if (verr != cudaSuccess)
+            return status_from_cuda(verr);
+        const bool bad = checked_flag_finish(st, &verr);
+        if (verr != cudaSuccess)
+            return status_from_cuda(verr);
+        if (bad)
+            return QSFI_STATUS_INVALID_ARGUMENT;
+    }
+#endif
     cudaError_t err = launch_router_topk(
         desc->logits.data, desc->logits.dtype == QSFI_DTYPE_BF16, nullptr,
         static_cast<int32_t*>(desc->topk_ids.data), static_cast<float*>(desc->topk_weights.data),

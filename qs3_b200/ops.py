@@ -58,8 +58,8 @@ def _stream_ptr(device=None) -> int:
 class Context:
     """``qsfi_context``: device ordinal + stream + last-error record."""
 
-    def __init__(self, device: int | None = None, stream: int | None = None):
-        self._lib = capi.load()
+    def __init__(self, device: int | None = None, stream: int | None = None, lib=None):
+        self._lib = capi.load() if lib is None else lib   # lib: e.g. capi.load_checked()
         if device is None:
             device = torch.cuda.current_device()
         self.device = device
@@ -192,9 +192,10 @@ class MoePlan:
 # ------------------------------------------------------------------ qscu ops ---
 
 def router_topk(logits, topk_ids, topk_weights, *, score=capi.ROUTER_SCORE_SOFTMAX, renormalize=True,
-                routed_scaling_factor=1.0, num_tokens=None, num_experts=None, top_k=None, stream=None):
+                routed_scaling_factor=1.0, num_tokens=None, num_experts=None, top_k=None, stream=None,
+                lib=None):
     """``qscu_router_topk`` (upstream qscu.h:278; builder src/runtime/kernels.rs:692-741)."""
-    lib = capi.load()
+    lib = capi.load() if lib is None else lib
     d = capi.RouterTopkDesc()
     d.logits = _desc(logits, 2)
     d.topk_ids = _desc(topk_ids, 2)

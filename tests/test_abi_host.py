@@ -72,6 +72,9 @@ def test_header_symbols_are_exported(lib):
     assert declared == set(capi.EXPORTED_SYMBOLS)
     for name in declared:
         assert hasattr(lib, name), name
+    checked = capi.load_checked()     # the checked-validation build exports the same interface
+    for name in declared:
+        assert hasattr(checked, name), name
 
 
 def test_struct_sizes_match_the_c_side():
