@@ -267,7 +267,8 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 8); // one arrival per epilogue warp
+            // one arrival per epilogue warp that reads the buffer (a group of four with TMA stores)
+            mbar_init(&acc_empty[b], (EPI == EPI_STORE_BF16 && p.tma_store) ? 4 : 8);
         }
         mbar_init(panel_bar, 1);
         *abort_flag = 0;
@@ -389,6 +390,70 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     tc_commit(&acc_full[buf]);
             }
         }
+    } else if (EPI == EPI_STORE_BF16 && p.tma_store) {
+        // ------------------------------------- epilogue, bf16 tiles through TMA stores --
+        // Two groups of four warps; group g owns accumulator g and staging tile g and takes
+        // every second column tile, so two tiles are in flight in the epilogue: the chain
+        // wait -> tcgen05.ld -> convert -> shared memory -> TMA store of one tile is longer
+        // than the MMAs of a tile with a short k. Every row of the tile is written: rows past
+        // the segment end are padding rows of the same expert, rows past the tensor are clipped.
+        const uint32_t group = warp >> 2, quad = warp & 3;
+        const uint32_t r = quad * 32 + lane;
+        const bool issuer = quad == 0 && lane == 0;
+        uint8_t* stage_buf = staging + group * 2 * kTileBytes;
+        float scale = p.alpha == 0.0f ? 1.0f : p.alpha;
+        if (p.group_scale != nullptr)
+            scale *= p.group_scale[expert];
+        for (uint32_t nt = nt_begin + group; nt < nt_end; nt += 2) {
+            const uint32_t use = (nt - nt_begin) >> 1;
+            const bool ready = __all_sync(
+                0xffffffffu, mbar_wait(&acc_full[group], use & 1, abort_flag, p.err, ERR_AS_ACC_FULL_WAIT));
+            if (!ready)
+                break;
+            tc_fence_after();
+            if (issuer) // this group's previous store must have left the staging tile
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
+#pragma unroll
+            for (uint32_t h2 = 0; h2 < 2; ++h2) {
+                uint32_t v[4][16];
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c)
+                    tc_ld16(tmem_base + group * kBN + ((quad * 32) << 16) + h2 * 64 + c * 16, v[c]);
+                tc_ld_wait();
+                uint8_t* row_smem = stage_buf + h2 * kTileBytes + r * 128;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        w[i] = pack_bf16x2(__uint_as_float(v[c][2 * i]) * scale,
+                                           __uint_as_float(v[c][2 * i + 1]) * scale);
+                    *reinterpret_cast<uint4*>(row_smem + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(row_smem + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+            // the accumulator is free again; publish the staged tile to the async proxy
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&acc_empty[group]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
+            if (issuer) {
+                const int n0 = static_cast<int>(nt * kBN);
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    if (n0 + h2 * 64 < static_cast<int>(p.n))
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                         reinterpret_cast<uint64_t>(&map_o)),
+                                     "r"(smem_u32(stage_buf + h2 * kTileBytes)), "r"(n0 + h2 * 64), "r"(row0)
+                                     : "memory");
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        }
+        if (issuer)
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // stores done before smem goes away
     } else {
         // ------------------------------------------------------------ epilogue --
         for (uint32_t nt = nt_begin; nt < nt_end; ++nt) {
@@ -400,56 +465,6 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             if (!ready)
                 break;
             tc_fence_after();
-            if (EPI == EPI_STORE_BF16 && p.tma_store) {
-                // bf16 tile -> shared memory (128-byte swizzled rows) -> one TMA store per
-                // 64-column half. Every row of the tile is written: rows past the segment
-                // end are padding rows of the same expert, rows past the tensor are clipped.
-                const uint32_t quad = warp & 3, half = warp >> 2;
-                const uint32_t r = quad * 32 + lane;
-                uint8_t* stage_buf = staging + (local & 1) * 2 * kTileBytes; // two staging tiles alternate
-                if (warp == 0 && lane == 0) // the store issued two tiles ago must have left this buffer
-                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                float scale = p.alpha == 0.0f ? 1.0f : p.alpha;
-                if (p.group_scale != nullptr)
-                    scale *= p.group_scale[expert];
-                // this warp's 64 columns in one go, then the accumulator is free again
-                uint32_t v[4][16];
-#pragma unroll
-                for (uint32_t c = 0; c < 4; ++c)
-                    tc_ld16(tmem_base + buf * kBN + ((quad * 32) << 16) + half * 64 + c * 16, v[c]);
-                tc_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0)
-                    mbar_arrive(&acc_empty[buf]);
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                uint8_t* row_smem = stage_buf + half * kTileBytes + r * 128;
-#pragma unroll
-                for (uint32_t c = 0; c < 4; ++c) {
-                    uint32_t w[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        w[i] = pack_bf16x2(__uint_as_float(v[c][2 * i]) * scale,
-                                           __uint_as_float(v[c][2 * i + 1]) * scale);
-                    *reinterpret_cast<uint4*>(row_smem + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-                    *reinterpret_cast<uint4*>(row_smem + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-                }
-                // publish the staged tile to the async proxy
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                if (warp == 0 && lane == 0) {
-                    const int n0 = static_cast<int>(nt * kBN);
-                    for (int h2 = 0; h2 < 2; ++h2) {
-                        if (n0 + h2 * 64 < static_cast<int>(p.n))
-                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                                             reinterpret_cast<uint64_t>(&map_o)),
-                                         "r"(smem_u32(stage_buf + h2 * kTileBytes)), "r"(n0 + h2 * 64), "r"(row0)
-                                         : "memory");
-                    }
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                }
-                continue;
-            }
             epilogue_tile<GATED, EPI, 2>(p, tmem_base + buf * kBN, warp & 3, lane, expert, row0, nrows, nt,
                                              warp >> 2);
             // hand the accumulator back once every lane of the warp has read it
@@ -458,8 +473,6 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             if (lane == 0)
                 mbar_arrive(&acc_empty[buf]);
         }
-        if (EPI == EPI_STORE_BF16 && p.tma_store && warp == 0 && lane == 0)
-            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // stores done before smem goes away
     }
 
     tc_fence_before();
