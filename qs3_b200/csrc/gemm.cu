@@ -1,5 +1,11 @@
-// Grouped / dense GEMM  D[m, n] = sum_k A[m, k] * B[g][n, k]  on the 5th-generation
-// tensor cores (tcgen05), one 128 x 128 output tile per CTA:
+// Grouped / dense GEMM  D[m, n] = sum_k A[m, k] * B[g][n, k]. Kernels in this file:
+//   gemm_tc_kernel        tcgen05, one 128 x 128 tile per CTA: every bf16 problem, NVFP4 with k > 2048
+//   gemm_tc_astat_kernel  tcgen05, NVFP4 with the A panel resident in shared memory (k <= 2048)
+//   gemm_skinny_kernel    CUDA cores, bf16 with at most 64 rows (router logits of a decode batch)
+//   gemm_simt_kernel      CUDA cores, shapes the tensor-core tiles cannot address
+// launch_gemm() at the end picks one.
+//
+// gemm_tc_kernel: one 128 x 128 output tile per CTA on the 5th-generation tensor cores:
 //
 //   warp 4      TMA producer: A and B tiles (128 rows x 128 bytes, 128-byte swizzle)
 //               and, for NVFP4, their scale tiles, into a ring of kStages stages
@@ -198,8 +204,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // doubles the FLOP per streamed byte. Two 128-column accumulators in tensor memory
 // alternate, so the epilogue of column tile i overlaps the MMAs of tile i + 1.
 //
-//   TMEM: [0,128) acc 0 | [128,256) acc 1 | [256,384) A scales (k/64 * 4 columns) | [384,400) B scales
-//   smem: A panel k_blocks x 16 KB | A-scale staging k_blocks x 2 KB | ring of (16 KB B + 2 KB scales)
+//   TMEM: [0,128) acc 0 | [128,256) acc 1 | [256,384) A scales (k/64 * 4 columns) | [384,416) B scales
+//         (two 16-column buffers, alternating per k block)
+//   smem: A panel k_blocks x 16 KB | A-scale staging k_blocks x 2 KB | ring of stages, each one or
+//         two k blocks of (16 KB B + 2 KB scales) | bf16 output: two 32 KB staging tiles
+//
+// Epilogue, eight warps: with the SwiGLU / f32 / plain-store epilogues two warps share a
+// TMEM lane quadrant and split the columns of one tile; with bf16 tiles written through TMA
+// stores the warps form two groups that take alternate column tiles.
 //
 // Grid: (n_splits, row tiles). A CTA handles column tiles [split * per, ...); n_splits > 1
 // only when there are too few row tiles to fill the GPU.
