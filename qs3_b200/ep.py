@@ -401,3 +401,4 @@ class ExpertParallelLayer:
                 "kernel_ms": ms, "algorithmic_bytes": algo, "experts_hit": hit, "local_routes": routes,
                 "tensor_tflops": flops / (ms * 1e-3) / 1e12,
                 "combine_exchange_gbs_per_direction": (exch_bytes / (exch * 1e-3) / 1e9) if exch else None}
+
