@@ -447,14 +447,16 @@ typedef struct {
        FP8 plans take no shared expert */
     qsfi_tensor3 gate_up_weight;       /* bf16 [E_local, 2I, H] or u8 [E_local, 2I, H/2] */
     qsfi_tensor1 gate_up_scale_tiled;  /* NVFP4 / FP8 only */
-    qsfi_tensor1 gate_up_global_scale; /* NVFP4 only, f32 [E_local] */
+    qsfi_tensor1 gate_up_global_scale; /* NVFP4 only, f32 [E_local], or f32 [2 * E_local]: the global
+                                          scales of the gate rows followed by those of the up rows
+                                          (checkpoints that quantise gate_proj and up_proj apart) */
     qsfi_tensor3 down_weight;          /* bf16 [E_local, H, I] or u8 [E_local, H, I/2] */
     qsfi_tensor1 down_scale_tiled;     /* NVFP4 / FP8 only */
     qsfi_tensor1 down_global_scale;    /* NVFP4 only, f32 [E_local] */
     /* optional shared expert (data == NULL on shared_gate_up_weight: none); same dtype family */
     qsfi_tensor3 shared_gate_up_weight;       /* [1, 2*Is, H] (or packed) */
     qsfi_tensor1 shared_gate_up_scale_tiled;
-    qsfi_tensor1 shared_gate_up_global_scale; /* f32 [1] */
+    qsfi_tensor1 shared_gate_up_global_scale; /* f32 [1], or f32 [2]: gate rows, up rows */
     qsfi_tensor3 shared_down_weight;          /* [1, H, Is] (or packed) */
     qsfi_tensor1 shared_down_scale_tiled;
     qsfi_tensor1 shared_down_global_scale;    /* f32 [1] */
@@ -530,7 +532,7 @@ typedef struct {
     qsfi_tensor2 topk_weights;         /* f32  [num_tokens, top_k] */
     qsfi_tensor3 gate_up_weight;       /* u8   [local_experts, 2*inter, hidden/2] */
     qsfi_tensor1 gate_up_scale_tiled;
-    qsfi_tensor1 gate_up_global_scale; /* optional f32 [local_experts] */
+    qsfi_tensor1 gate_up_global_scale; /* optional f32 [local_experts] or [2 * local_experts] (gate, up) */
     qsfi_tensor3 down_weight;          /* u8   [local_experts, hidden, inter/2] */
     qsfi_tensor1 down_scale_tiled;
     qsfi_tensor1 down_global_scale;    /* optional f32 [local_experts] */
@@ -678,6 +680,157 @@ qsfi_status qs3_moe_profile_end(
  * of 32). Returns dense TFLOP/s. Used as the denominator of the reported tensor-pipe
  * fractions. */
 qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, uint32_t n, uint32_t iters, double* tflops);
+
+/* ================================================= checkpoint loader ======
+ * Upstream has the loader only as a trait (src/weight_loader.rs:33-38: alloc_tensor,
+ * read_exact, zero_fill, seal) with its contract in prose (src/weight_loader.rs:9-32,
+ * AGENTS.md:55-67): parse config.json, the safetensors index and every shard header
+ * first; reject duplicate, missing, unexpected, wrong-dtype, wrong-shape, overlapping
+ * or out-of-range tensors before any CUDA-visible memory is touched; then fill the
+ * final device storage from byte ranges of the files through a pinned staging ring
+ * (cudaHostAlloc ring, pread, cudaMemcpyAsync, events), with one synchronisation
+ * point at the end ("seal"). This section is that loader for the tensors of one MoE
+ * layer, producing the layouts qs3_moe_layer_execute consumes.
+ *
+ * File formats: safetensors (8-byte little-endian header length, JSON header
+ * {name: {dtype, shape, data_offsets}}, raw little-endian data) and the
+ * model.safetensors.index.json / config.json files that accompany it. */
+
+typedef struct qs3_checkpoint qs3_checkpoint;
+
+/* Opens `directory`: with model.safetensors.index.json present its weight_map names the
+ * shards, otherwise every *.safetensors file of the directory is a shard. Every shard
+ * header is parsed and checked (header length inside the file, well-formed JSON, no
+ * tensor name twice in a shard or across shards, known dtype, product(shape) * element
+ * size == length of the byte range, ranges inside the file and pairwise disjoint; with
+ * an index: every indexed tensor present in the shard it names and no tensor of a shard
+ * missing from the index). Makes no CUDA call. */
+qsfi_status qs3_checkpoint_open(qsfi_context* ctx, const char* directory, qs3_checkpoint** out);
+void qs3_checkpoint_close(qs3_checkpoint* checkpoint); /* NULL is legal */
+uint64_t qs3_checkpoint_num_tensors(const qs3_checkpoint* checkpoint);
+
+#define QS3_CHECKPOINT_MAX_RANK 8u
+typedef struct {
+    const char* name;       /* owned by the checkpoint object */
+    const char* file;       /* path of the shard, owned by the checkpoint object */
+    const char* dtype_name; /* safetensors spelling: "BF16", "F8_E4M3", "U8", "F32", ... */
+    qsfi_dtype dtype;       /* QSFI_DTYPE_INVALID for types qsfi_dtype cannot name (I64, F64, BOOL, ...) */
+    uint32_t element_bytes;
+    uint32_t rank;
+    int64_t shape[QS3_CHECKPOINT_MAX_RANK];
+    uint64_t file_offset; /* absolute offset of the first byte inside the shard */
+    uint64_t bytes;
+} qs3_checkpoint_tensor_info;
+/* Tensors are numbered in name order. */
+qsfi_status qs3_checkpoint_tensor_at(
+    qsfi_context* ctx, const qs3_checkpoint* checkpoint, uint64_t index, qs3_checkpoint_tensor_info* out
+);
+qsfi_status qs3_checkpoint_find(
+    qsfi_context* ctx, const qs3_checkpoint* checkpoint, const char* name, qs3_checkpoint_tensor_info* out
+);
+/* Copies the bytes of one tensor into host memory (dst_bytes must equal its size). */
+qsfi_status qs3_checkpoint_read_host(
+    qsfi_context* ctx, const qs3_checkpoint* checkpoint, const char* name, void* dst, uint64_t dst_bytes
+);
+
+/* MoE hyper-parameters of config.json (keys as Hugging Face's Qwen MoE configurations spell
+ * them, read from the top level or from "text_config"): hidden_size, moe_intermediate_size,
+ * num_experts, num_experts_per_tok, shared_expert_intermediate_size (0 when absent),
+ * num_hidden_layers, norm_topk_prob (1 when absent), rms_norm_eps (1e-6 when absent). */
+typedef struct {
+    uint32_t hidden_size;
+    uint32_t intermediate_size;
+    uint32_t num_experts;
+    uint32_t top_k;
+    uint32_t shared_intermediate_size;
+    uint32_t num_layers;
+    uint32_t renormalize;
+    float rms_norm_eps;
+} qs3_checkpoint_moe_config;
+qsfi_status qs3_checkpoint_read_moe_config(
+    qsfi_context* ctx, const qs3_checkpoint* checkpoint, qs3_checkpoint_moe_config* out
+);
+
+/* How the routed experts are stored (AGENTS.md:45-47): BF16 checkpoints hold the fused
+ * tensors <prefix>experts.gate_up_proj and <prefix>experts.down_proj; NVFP4 checkpoints
+ * hold per expert e and per projection p in {gate_proj, up_proj, down_proj}
+ *   <prefix>experts.<e>.<p>.weight          U8      [rows, k / 2]  two e2m1 codes per byte, low nibble = even k
+ *   <prefix>experts.<e>.<p>.weight_scale    F8_E4M3 [rows, k / 16] one scale per 16 elements along k
+ *   <prefix>experts.<e>.<p>.weight_scale_2  F32     [] or [1]      global scale of the matrix
+ *   <prefix>experts.<e>.<p>.input_scale     F32     [] or [1]      global scale of the activations it multiplies
+ * with value = e2m1 * weight_scale * weight_scale_2. The other tensors of the layer:
+ *   <prefix>gate.weight                      BF16 [num_experts, hidden]   router
+ *   <prefix>shared_expert.{gate,up,down}_proj.weight  (BF16, or NVFP4 with the four tensors above)
+ *   <prefix>shared_expert_gate.weight        BF16 [1, hidden]
+ * The fused BF16 expert tensors are accepted as [E, 2I, H] / [E, H, I] (the layout the
+ * kernels read) or transposed, [E, H, 2I] / [E, I, H]; when hidden == 2 * intermediate the
+ * two readings of gate_up_proj coincide and `fused_transposed` decides. */
+typedef enum {
+    QS3_CHECKPOINT_EXPERTS_BF16_FUSED = 0,
+    QS3_CHECKPOINT_EXPERTS_NVFP4_SPLIT = 1
+} qs3_checkpoint_expert_format;
+
+typedef struct {
+    const char* layer_prefix; /* e.g. "model.language_model.layers.3.mlp." */
+    uint32_t hidden_size;
+    uint32_t intermediate_size;
+    uint32_t num_experts;
+    uint32_t shared_intermediate_size; /* 0: the layer has no shared expert */
+    uint32_t local_expert_offset;      /* first PHYSICAL expert position this rank holds */
+    uint32_t local_num_experts;
+    const uint32_t* expert_order;      /* optional [num_experts]: checkpoint expert id at each physical
+                                          position (a placement that spreads hot experts over ranks);
+                                          router rows are permuted the same way. NULL: identity */
+    qs3_checkpoint_expert_format format;
+    qsfi_moe_backend backend;          /* layout to produce: one of the two BF16 backends, or
+                                          QSFI_MOE_BACKEND_FLASHINFER_NVFP4 (a BF16 checkpoint is
+                                          then quantised on the device) */
+    uint32_t fused_transposed;         /* BF16_FUSED, ambiguous shapes only: 1 = [E, H, 2I] / [E, I, H] */
+} qs3_moe_layer_load_desc;
+
+/* Device tensors of one loaded layer, ready to be copied into qs3_moe_layer_desc. They
+ * all live inside the caller's device block. */
+typedef struct {
+    qsfi_tensor2 router_weight;               /* bf16 [num_experts, hidden], rows in physical order */
+    qsfi_tensor3 gate_up_weight;              /* bf16 [E_local, 2I, H] or u8 [E_local, 2I, H/2] */
+    qsfi_tensor1 gate_up_scale_tiled;         /* NVFP4 */
+    qsfi_tensor1 gate_up_global_scale;        /* NVFP4 checkpoint: f32 [2 * E_local] (gate rows, up rows);
+                                                 quantised here from BF16: f32 [E_local] */
+    qsfi_tensor3 down_weight;
+    qsfi_tensor1 down_scale_tiled;
+    qsfi_tensor1 down_global_scale;           /* NVFP4: f32 [E_local] */
+    qsfi_tensor3 shared_gate_up_weight;       /* data == NULL without a shared expert */
+    qsfi_tensor1 shared_gate_up_scale_tiled;
+    qsfi_tensor1 shared_gate_up_global_scale; /* f32 [2] from an NVFP4 checkpoint, f32 [1] otherwise */
+    qsfi_tensor3 shared_down_weight;
+    qsfi_tensor1 shared_down_scale_tiled;
+    qsfi_tensor1 shared_down_global_scale;
+    qsfi_tensor2 shared_gate_weight;          /* bf16 [1, hidden] */
+    float act_global_scale;  /* NVFP4 checkpoints: max input_scale of all gate_proj / up_proj (every
+                                expert of the layer, so that all ranks quantise tokens alike); else 1 */
+    float act2_global_scale; /* max input_scale of all down_proj; else 1 */
+} qs3_moe_layer_weights;
+
+/* Validates the layer against the checkpoint (every expected tensor present with the
+ * expected dtype and shape; no other tensor under layer_prefix) and returns the sizes of
+ * the two device buffers qs3_checkpoint_load_moe_layer needs: `weight_bytes` for the
+ * loaded tensors (kept) and `scratch_bytes` for load-time staging (may be freed after the
+ * load). Makes no CUDA call. */
+qsfi_status qs3_checkpoint_moe_layer_bytes(
+    qsfi_context* ctx, const qs3_checkpoint* checkpoint, const qs3_moe_layer_load_desc* desc,
+    size_t* weight_bytes, size_t* scratch_bytes
+);
+
+/* Loads the layer into `weights` (256-byte aligned device block of >= weight_bytes): file
+ * byte ranges go through a ring of pinned host buffers and cudaMemcpyAsync on a copy stream
+ * of the loader; scale re-tiling, transposes and quantisation then run on the context's
+ * stream. Returns after the copy stream has drained and the device work is enqueued (work
+ * on the context's stream is ordered after the copies); `scratch` may be released once the
+ * context's stream has passed this point. */
+qsfi_status qs3_checkpoint_load_moe_layer(
+    qsfi_context* ctx, const qs3_checkpoint* checkpoint, const qs3_moe_layer_load_desc* desc,
+    void* weights, size_t weight_bytes, void* scratch, size_t scratch_bytes, qs3_moe_layer_weights* out
+);
 
 #ifdef __cplusplus
 }

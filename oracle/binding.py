@@ -254,6 +254,8 @@ def moe_nvfp4(hidden_packed, hidden_scale, ids, weights, gu, d, *, act_global=1.
     t = hp.shape[0]
     h = hp.shape[1] * 2
     e, two_i, _ = gup.shape
+    # globals of shape [2, experts] (routed) and [2] (shared): gate rows and up rows scaled apart
+    split = int(gug.size == 2 * e)
     k = ids.shape[1]
     tl = _c(token_list, np.int32)
     n = t if tl is None else tl.size
@@ -264,6 +266,7 @@ def moe_nvfp4(hidden_packed, hidden_scale, ids, weights, gu, d, *, act_global=1.
         gate_w = _c(shared["gate_w"], np.uint16).reshape(-1)
         hb = _c(hidden_bf16, np.uint16)
         s_inter = sgu[0].reshape(-1, h // 2).shape[0] // 2
+        split |= 2 * (sgu[2].size == 2)
     else:
         sgu = [None] * 3
         sd = [None] * 3
@@ -275,7 +278,7 @@ def moe_nvfp4(hidden_packed, hidden_scale, ids, weights, gu, d, *, act_global=1.
                          C.c_int64(h), C.c_int64(two_i // 2), C.c_int64(k), C.c_int64(local_offset),
                          C.c_int64(e), _p(sgu[0]), _p(sgu[1]), _p(sgu[2]), _p(sd[0]), _p(sd[1]),
                          _p(sd[2]), C.c_int64(s_inter), _p(hb), _p(gate_w), _p(tl), C.c_int64(n),
-                         _p(out))
+                         C.c_int32(split), _p(out))
     return out
 
 

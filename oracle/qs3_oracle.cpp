@@ -576,7 +576,9 @@ QS3O_API void qs3o_nvfp4_quantize_weight(
 
 // Routed + optional shared experts on NVFP4 operands, this repository's chain:
 //   xq = quantise(x, act_global)                       (or given pre-quantised)
-//   Y1 = (xq . Wgu_q) * act_global * gu_global[e]      f32, no bf16 rounding
+//   Y1 = (xq . Wgu_q) * act_global * gu_global[e]      f32, no bf16 rounding; with bit 0 of gu_split
+//        set gu_global holds [2, experts]: row 0 scales the gate rows, row 1 the up rows
+//        (bit 1: the same for the shared expert, sh_gu_global = [gate, up])
 //   act = g * sigmoid(g) * u                           f32
 //   aq = quantise(act, act2_global)
 //   Y2 = bf16((aq . Wd_q) * act2_global * d_global[e])
@@ -593,7 +595,7 @@ QS3O_API void qs3o_moe_nvfp4(
     int64_t local_experts, const uint8_t* sh_gu_packed, const uint8_t* sh_gu_scale,
     const float* sh_gu_global, const uint8_t* sh_d_packed, const uint8_t* sh_d_scale,
     const float* sh_d_global, int64_t shared_inter, const uint16_t* hidden_bf16,
-    const uint16_t* gate_w, const int32_t* token_list, int64_t n_list, uint16_t* out
+    const uint16_t* gate_w, const int32_t* token_list, int64_t n_list, int32_t gu_split, uint16_t* out
 )
 {
     const float ga = act_global == 0.0f ? 1.0f : act_global;
@@ -606,12 +608,12 @@ QS3O_API void qs3o_moe_nvfp4(
             wrow(std::max(hidden_size, max_inter)), acc(hidden_size), xb(hidden_size);
         std::vector<uint8_t> ap(max_inter / 2), as(max_inter / 16);
 
-        auto run_expert = [&](const uint8_t* gup, const uint8_t* gus, float gug, const uint8_t* dp,
-                              const uint8_t* ds, float dg, int64_t I, float wgt) {
+        auto run_expert = [&](const uint8_t* gup, const uint8_t* gus, float gug, float gug_up,
+                              const uint8_t* dp, const uint8_t* ds, float dg, int64_t I, float wgt) {
             for (int64_t j = 0; j < 2 * I; ++j) {
                 nvfp4_dequantize_row(gup + j * (hidden_size / 2), gus + j * (hidden_size / 16),
                                      hidden_size, wrow.data());
-                y1[j] = dotf(x.data(), wrow.data(), hidden_size) * (ga * gug);
+                y1[j] = dotf(x.data(), wrow.data(), hidden_size) * (ga * (j < I ? gug : gug_up));
             }
             for (int64_t i = 0; i < I; ++i) {
                 const float g = y1[i];
@@ -638,6 +640,7 @@ QS3O_API void qs3o_moe_nvfp4(
                     continue;
                 run_expert(gu_packed + local * 2 * inter * (hidden_size / 2),
                            gu_scale + local * 2 * inter * (hidden_size / 16), gu_global[local],
+                           gu_global[(gu_split & 1) ? local_experts + local : local],
                            d_packed + local * hidden_size * (inter / 2),
                            d_scale + local * hidden_size * (inter / 16), d_global[local], inter,
                            weights[t * top_k + k]);
@@ -648,7 +651,8 @@ QS3O_API void qs3o_moe_nvfp4(
                     wrow[h] = bf16_to_f32(gate_w[h]);
                 }
                 const float gamma = sigmoidf(dotf(xb.data(), wrow.data(), hidden_size));
-                run_expert(sh_gu_packed, sh_gu_scale, sh_gu_global[0], sh_d_packed, sh_d_scale,
+                run_expert(sh_gu_packed, sh_gu_scale, sh_gu_global[0], sh_gu_global[(gu_split & 2) ? 1 : 0],
+                           sh_d_packed, sh_d_scale,
                            sh_d_global[0], shared_inter, gamma);
             }
             for (int64_t h = 0; h < hidden_size; ++h)

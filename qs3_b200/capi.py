@@ -245,6 +245,43 @@ class FusedAddRmsnormNvfp4Desc(C.Structure):
                 ("global_scale", C.c_float)]
 
 
+CHECKPOINT_MAX_RANK = 8
+CHECKPOINT_EXPERTS_BF16_FUSED = 0
+CHECKPOINT_EXPERTS_NVFP4_SPLIT = 1
+
+
+class CheckpointTensorInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("file", C.c_char_p), ("dtype_name", C.c_char_p), ("dtype", C.c_int),
+                ("element_bytes", C.c_uint32), ("rank", C.c_uint32), ("shape", C.c_int64 * CHECKPOINT_MAX_RANK),
+                ("file_offset", C.c_uint64), ("bytes", C.c_uint64)]
+
+
+class CheckpointMoeConfig(C.Structure):
+    _fields_ = [("hidden_size", C.c_uint32), ("intermediate_size", C.c_uint32), ("num_experts", C.c_uint32),
+                ("top_k", C.c_uint32), ("shared_intermediate_size", C.c_uint32), ("num_layers", C.c_uint32),
+                ("renormalize", C.c_uint32), ("rms_norm_eps", C.c_float)]
+
+
+class MoeLayerLoadDesc(C.Structure):
+    _fields_ = [("layer_prefix", C.c_char_p), ("hidden_size", C.c_uint32), ("intermediate_size", C.c_uint32),
+                ("num_experts", C.c_uint32), ("shared_intermediate_size", C.c_uint32),
+                ("local_expert_offset", C.c_uint32), ("local_num_experts", C.c_uint32),
+                ("expert_order", _P(C.c_uint32)), ("format", C.c_int), ("backend", C.c_int),
+                ("fused_transposed", C.c_uint32)]
+
+
+class MoeLayerWeights(C.Structure):
+    _fields_ = [("router_weight", Tensor2),
+                ("gate_up_weight", Tensor3), ("gate_up_scale_tiled", Tensor1), ("gate_up_global_scale", Tensor1),
+                ("down_weight", Tensor3), ("down_scale_tiled", Tensor1), ("down_global_scale", Tensor1),
+                ("shared_gate_up_weight", Tensor3), ("shared_gate_up_scale_tiled", Tensor1),
+                ("shared_gate_up_global_scale", Tensor1),
+                ("shared_down_weight", Tensor3), ("shared_down_scale_tiled", Tensor1),
+                ("shared_down_global_scale", Tensor1),
+                ("shared_gate_weight", Tensor2),
+                ("act_global_scale", C.c_float), ("act2_global_scale", C.c_float)]
+
+
 _SIGNATURES = {
     "qsfi_status_string": (C.c_char_p, [C.c_int]),
     "qsfi_context_create": (C.c_int, [_P(ContextDesc), _P(C.c_void_p)]),
@@ -296,6 +333,17 @@ _SIGNATURES = {
     "qs3_fp8_quantize_act": (C.c_int, [C.c_void_p, _P(Fp8QuantizeActDesc)]),
     "qsfi_moe_execute_fp8": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeFp8ExecuteDesc)]),
     "qs3_tensor_peak_probe": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, _P(C.c_double)]),
+    "qs3_checkpoint_open": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_void_p)]),
+    "qs3_checkpoint_close": (None, [C.c_void_p]),
+    "qs3_checkpoint_num_tensors": (C.c_uint64, [C.c_void_p]),
+    "qs3_checkpoint_tensor_at": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, _P(CheckpointTensorInfo)]),
+    "qs3_checkpoint_find": (C.c_int, [C.c_void_p, C.c_void_p, C.c_char_p, _P(CheckpointTensorInfo)]),
+    "qs3_checkpoint_read_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_char_p, C.c_void_p, C.c_uint64]),
+    "qs3_checkpoint_read_moe_config": (C.c_int, [C.c_void_p, C.c_void_p, _P(CheckpointMoeConfig)]),
+    "qs3_checkpoint_moe_layer_bytes": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeLayerLoadDesc), _P(C.c_size_t),
+                                                 _P(C.c_size_t)]),
+    "qs3_checkpoint_load_moe_layer": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeLayerLoadDesc), C.c_void_p, C.c_size_t,
+                                                C.c_void_p, C.c_size_t, _P(MoeLayerWeights)]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

@@ -208,6 +208,7 @@ struct GemmProblem {
     float alpha;                // 0 means 1
     float beta;
     const float* group_scale;   // optional per-group multiplier on acc
+    const float* group_scale_up; // gated: optional multiplier of the up rows (NULL: group_scale)
     const float* bias;          // optional f32 [n] (EPI_STORE_F32)
     float out_global_scale;     // EPI_SWIGLU_NVFP4: global scale of the quantised output
 };

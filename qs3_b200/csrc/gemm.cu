@@ -517,8 +517,11 @@ __global__ void gemm_simt_kernel(const __nv_bfloat16* __restrict__ a, uint64_t a
         nrows = min(kBM, static_cast<int>(p.dense_rows) - row0);
     }
     float scale = p.alpha == 0.0f ? 1.0f : p.alpha;
+    float scale_up = scale;
     if (p.group_scale != nullptr)
         scale *= p.group_scale[expert];
+    scale_up *= p.group_scale_up != nullptr ? p.group_scale_up[expert]
+                                            : (p.group_scale != nullptr ? p.group_scale[expert] : 1.0f);
     const uint32_t cols = blockDim.x; // output features handled per block-row pass
     const uint32_t n = blockIdx.x * cols + threadIdx.x;
     if (n >= p.n)
@@ -537,7 +540,7 @@ __global__ void gemm_simt_kernel(const __nv_bfloat16* __restrict__ a, uint64_t a
         }
         if constexpr (EPI == EPI_SWIGLU_BF16) {
             const float g = round_bf16(acc * scale);
-            const float u = round_bf16(acc2 * scale);
+            const float u = round_bf16(acc2 * scale_up);
             static_cast<__nv_bfloat16*>(p.out)[grow * p.out_pitch + n]
                 = __float2bfloat16(g * sigmoid_fast(g) * u);
         } else if constexpr (EPI == EPI_STORE_F32) {
@@ -767,6 +770,7 @@ TcParams make_params(const GemmProblem& g)
     tp.alpha = g.alpha;
     tp.beta = g.beta;
     tp.group_scale = g.group_scale;
+    tp.group_scale_up = g.group_scale_up;
     tp.bias = g.bias;
     tp.out_global = g.out_global_scale == 0.0f ? 1.0f : g.out_global_scale;
     tp.err = device_error_word();

@@ -383,10 +383,24 @@ qsfi_status run_routed_bf16(qsfi_context* ctx, const qsfi_moe_plan_desc& p, cons
     return gemm_or_error(ctx, g2, "MoE down GEMM");
 }
 
+// Global scales of a gate_up weight: f32 [groups] (one per expert, gate and up rows alike) or
+// f32 [2 * groups] (the gate-row scales followed by the up-row scales, as checkpoints that
+// quantise gate_proj and up_proj separately have them).
+bool gate_up_global_ok(const qsfi_tensor1& g, int64_t groups)
+{
+    return g.data == nullptr
+        || (g.dtype == QSFI_DTYPE_F32 && (g.shape[0] == groups || g.shape[0] == 2 * groups) && g.stride[0] == 1);
+}
+const float* gate_up_global_up(const qsfi_tensor1& g, int64_t groups)
+{
+    return g.data != nullptr && g.shape[0] == 2 * groups ? static_cast<const float*>(g.data) + groups : nullptr;
+}
+
 struct Nvfp4Weights {
     const uint8_t* gu_packed;
     const uint8_t* gu_sf_tiled;
     const float* gu_global; // optional
+    const float* gu_global_up; // optional: separate global scale of the up rows
     const uint8_t* d_packed;
     const uint8_t* d_sf_tiled;
     const float* d_global;  // optional
@@ -416,6 +430,7 @@ qsfi_status run_routed_nvfp4(qsfi_context* ctx, const qsfi_moe_plan_desc& p, con
     g1.out_scale_tiled = w.act_sf;
     g1.alpha = ga;
     g1.group_scale = wt.gu_global;
+    g1.group_scale_up = wt.gu_global_up;
     g1.out_global_scale = ga2;
     qsfi_status status = gemm_or_error(ctx, g1, "NVFP4 MoE gate_up GEMM");
     if (status != QSFI_STATUS_OK)
@@ -1012,6 +1027,9 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
             || static_cast<uint64_t>(d->gate_up_scale_tiled.shape[0]) < e * qs3_nvfp4_tiled_scale_bytes(2 * i, h)
             || static_cast<uint64_t>(d->down_scale_tiled.shape[0]) < e * qs3_nvfp4_tiled_scale_bytes(h, i))
             return set_invalid_arg(ctx, "NVFP4 MoE layer needs tiled weight scales of the right size");
+        if (!gate_up_global_ok(d->gate_up_global_scale, e)
+            || (shared && !gate_up_global_ok(d->shared_gate_up_global_scale, 1)))
+            return set_invalid_arg(ctx, "gate_up global scales must be contiguous f32 [groups] or [2 * groups] tensors");
         if (shared
             && (d->shared_gate_up_scale_tiled.data == nullptr || d->shared_down_scale_tiled.data == nullptr
                 || static_cast<uint64_t>(d->shared_gate_up_scale_tiled.shape[0])
@@ -1120,6 +1138,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         s1.out_scale_tiled = x.sh_actq_sf;
         s1.alpha = ga;
         s1.group_scale = static_cast<const float*>(d->shared_gate_up_global_scale.data);
+        s1.group_scale_up = gate_up_global_up(d->shared_gate_up_global_scale, 1);
         s1.out_global_scale = ga2;
         qsfi_status st1 = gemm_on_stream(ctx, s1, "NVFP4 shared gate_up GEMM", stream);
         if (st1 != QSFI_STATUS_OK)
@@ -1235,6 +1254,7 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
         wt.gu_packed = static_cast<const uint8_t*>(d->gate_up_weight.data);
         wt.gu_sf_tiled = static_cast<const uint8_t*>(d->gate_up_scale_tiled.data);
         wt.gu_global = static_cast<const float*>(d->gate_up_global_scale.data);
+        wt.gu_global_up = gate_up_global_up(d->gate_up_global_scale, p.local_num_experts);
         wt.d_packed = static_cast<const uint8_t*>(d->down_weight.data);
         wt.d_sf_tiled = static_cast<const uint8_t*>(d->down_scale_tiled.data);
         wt.d_global = static_cast<const float*>(d->down_global_scale.data);
@@ -1465,9 +1485,12 @@ qsfi_status qs3_moe_execute_nvfp4_prepared(qsfi_context* ctx, const qsfi_moe_pla
         || static_cast<uint64_t>(d->gate_up_scale_tiled.shape[0]) < e * qs3_nvfp4_tiled_scale_bytes(2 * i, h)
         || static_cast<uint64_t>(d->down_scale_tiled.shape[0]) < e * qs3_nvfp4_tiled_scale_bytes(h, i))
         return set_invalid_arg(ctx, "NVFP4 MoE needs tiled weight scales of the right size");
-    for (const qsfi_tensor1* g : { &d->gate_up_global_scale, &d->down_global_scale })
-        if (g->data != nullptr && (g->dtype != QSFI_DTYPE_F32 || g->shape[0] != e || !contiguous1(*g)))
-            return set_invalid_arg(ctx, "global scales must be contiguous f32 [local_num_experts] tensors");
+    if (!gate_up_global_ok(d->gate_up_global_scale, e)
+        || (d->down_global_scale.data != nullptr
+            && (d->down_global_scale.dtype != QSFI_DTYPE_F32 || d->down_global_scale.shape[0] != e
+                || !contiguous1(d->down_global_scale))))
+        return set_invalid_arg(ctx, "global scales must be contiguous f32 [local_num_experts] tensors "
+                                    "(gate_up: or [2 * local_num_experts])");
     const size_t need = carve_nvfp4(nullptr, p, d->num_tokens, false).bytes;
     status = validate_workspace(ctx, d->workspace, need);
     if (status != QSFI_STATUS_OK)
@@ -1497,6 +1520,7 @@ qsfi_status qs3_moe_execute_nvfp4_prepared(qsfi_context* ctx, const qsfi_moe_pla
     wt.gu_packed = static_cast<const uint8_t*>(d->gate_up_weight.data);
     wt.gu_sf_tiled = static_cast<const uint8_t*>(d->gate_up_scale_tiled.data);
     wt.gu_global = static_cast<const float*>(d->gate_up_global_scale.data);
+    wt.gu_global_up = gate_up_global_up(d->gate_up_global_scale, p.local_num_experts);
     wt.d_packed = static_cast<const uint8_t*>(d->down_weight.data);
     wt.d_sf_tiled = static_cast<const uint8_t*>(d->down_scale_tiled.data);
     wt.d_global = static_cast<const float*>(d->down_global_scale.data);
@@ -1583,6 +1607,8 @@ qsfi_status qs3_moe_ep_finish(qsfi_context* ctx, const qsfi_moe_plan* plan, cons
             || static_cast<uint64_t>(d->shared_gate_up_scale_tiled.shape[0]) < qs3_nvfp4_tiled_scale_bytes(2 * is, h)
             || static_cast<uint64_t>(d->shared_down_scale_tiled.shape[0]) < qs3_nvfp4_tiled_scale_bytes(h, is))
             return set_invalid_arg(ctx, "NVFP4 MoE layer needs tiled shared-expert scales of the right size");
+        if (!gate_up_global_ok(d->shared_gate_up_global_scale, 1))
+            return set_invalid_arg(ctx, "gate_up global scales must be contiguous f32 [groups] or [2 * groups] tensors");
         status = validate_nvfp4_dims(ctx, p.hidden_size, is, "shared-expert");
         if (status != QSFI_STATUS_OK)
             return status;
@@ -1629,6 +1655,7 @@ qsfi_status qs3_moe_ep_finish(qsfi_context* ctx, const qsfi_moe_plan* plan, cons
         s1.out_scale_tiled = x.sh_actq_sf;
         s1.alpha = ga;
         s1.group_scale = static_cast<const float*>(d->shared_gate_up_global_scale.data);
+        s1.group_scale_up = gate_up_global_up(d->shared_gate_up_global_scale, 1);
         s1.out_global_scale = ga2;
         status = gemm_or_error(ctx, s1, "NVFP4 shared gate_up GEMM");
         if (status != QSFI_STATUS_OK)

@@ -42,6 +42,7 @@ struct TcParams {
     float alpha;
     float beta;
     const float* group_scale;
+    const float* group_scale_up; // gated tiles: multiplier of the up columns (NULL: group_scale)
     const float* bias;
     float out_global;
     uint32_t* err;
@@ -246,8 +247,11 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_a
     const uint64_t grow = static_cast<uint64_t>(row0) + r;
     const uint32_t lane_base = (warp * 32) << 16;
     float scale = p.alpha == 0.0f ? 1.0f : p.alpha;
+    float scale_up = scale; // gate and up rows of an expert may carry different global scales
     if (p.group_scale != nullptr)
         scale *= p.group_scale[expert];
+    scale_up *= p.group_scale_up != nullptr ? p.group_scale_up[expert]
+                                            : (p.group_scale != nullptr ? p.group_scale[expert] : 1.0f);
 
     if constexpr (!GATED) {
         constexpr uint32_t kChunks = kBN / 16 / HALVES;
@@ -330,7 +334,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_a
                     // upstream stores the gate_up product as bf16 before SwiGLU
                     // (qsfi_moe.cu:638-651,445-463)
                     const float g = round_bf16(__uint_as_float(vg[i]) * scale);
-                    const float u = round_bf16(__uint_as_float(vu[i]) * scale);
+                    const float u = round_bf16(__uint_as_float(vu[i]) * scale_up);
                     act[i] = g * sigmoid_fast(g) * u;
                 }
                 __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + grow * p.out_pitch + fb;
@@ -351,7 +355,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_a
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float g = __uint_as_float(vg[i]) * scale;
-                    const float u = __uint_as_float(vu[i]) * scale;
+                    const float u = __uint_as_float(vu[i]) * scale_up;
                     act[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
                 }
                 uint32_t lo, hi;

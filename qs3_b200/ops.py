@@ -63,7 +63,10 @@ class Context:
         if device is None:
             device = torch.cuda.current_device()
         self.device = device
-        desc = capi.ContextDesc(device, stream if stream is not None else _stream_ptr(device))
+        if device < 0:   # no device binding: host-side calls only (validation, checkpoint parsing)
+            desc = capi.ContextDesc(-1, None)
+        else:
+            desc = capi.ContextDesc(device, stream if stream is not None else _stream_ptr(device))
         handle = C.c_void_p()
         status = self._lib.qsfi_context_create(C.byref(desc), C.byref(handle))
         if status != capi.STATUS_OK:

@@ -182,3 +182,36 @@ def test_layer_call_replays_from_a_cuda_graph(ops, oracle):
         assert ctx.read_device_error() == 0
         assert np.array_equal(replayed, to_np(out))
         assert not np.array_equal(replayed, eager_first)
+
+
+def test_gate_and_up_rows_with_separate_global_scales(ops, ctx, oracle):
+    """Checkpoints that quantise gate_proj and up_proj apart carry one global scale for each;
+    the layer takes them as f32 [2 * experts] (routed) and f32 [2] (shared expert)."""
+    import dataclasses
+    t, h, e, k, i, s = 96, 512, 16, 4, 256, 256
+    d = make_moe_inputs(37, t, h, e, i, s)
+    gu, dn, sh = _quantise_all(ops, ctx, d, True)
+    factor = torch.linspace(0.6, 1.7, e, device="cuda")
+    gu2 = dataclasses.replace(gu, global_scale=torch.cat([gu.global_scale, gu.global_scale * factor]))
+    sgu2 = dataclasses.replace(sh[0], global_scale=torch.cat([sh[0].global_scale, sh[0].global_scale * 1.3]))
+    plan = ops.MoePlan(ctx, ops.MoePlanConfig(max_num_tokens=t, hidden_size=h, intermediate_size=i,
+                                              num_experts=e, top_k=k, backend=ops.capi.MOE_BACKEND_NVFP4))
+    ws = torch.zeros(plan.layer_workspace_size(t, s), dtype=torch.uint8, device="cuda")
+    out = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+    ids_t = torch.empty((t, k), dtype=torch.int32, device="cuda")
+    w_t = torch.empty((t, k), dtype=torch.float32, device="cuda")
+    shared = ops.SharedExpert(sgu2, sh[1], to_dev(d["sh_gate"]), s)
+    ops.moe_layer_execute(plan, to_dev(d["hidden"]), to_dev(d["router"]), gu2, dn, out, ws, shared=shared,
+                          topk_ids=ids_t, topk_weights=w_t)
+    torch.cuda.synchronize()
+    assert ctx.read_device_error() == 0
+    hp, hs = oracle.nvfp4_quantize_act(d["hidden"], 1.0)
+    ref = oracle.moe_nvfp4(hp, hs, to_np(ids_t), to_np(w_t), _triple(gu2), _triple(dn),
+                           shared=dict(gu=_triple(sgu2), d=_triple(sh[1]), gate_w=d["sh_gate"]),
+                           hidden_bf16=d["hidden"])
+    _check(to_np(out), ref)
+    # the second scale is really applied: the single-scale result differs
+    single = oracle.moe_nvfp4(hp, hs, to_np(ids_t), to_np(w_t), _triple(gu), _triple(dn),
+                              shared=dict(gu=_triple(sh[0]), d=_triple(sh[1]), gate_w=d["sh_gate"]),
+                              hidden_bf16=d["hidden"])
+    assert rel_l2(to_np(out), single) > 0.05
