@@ -11,9 +11,9 @@
  *
  *  2. Additive entry points (prefix qs3_) that upstream does not have: NVFP4
  *     weight preparation, a dense bf16 GEMM for the router / shared expert, a
- *     whole-layer call (router logits -> top-k -> experts -> combine), and the
- *     expert-parallel pack/unpack helpers. They never change an upstream
- *     signature.
+ *     whole-layer call (router logits -> top-k -> experts -> combine), the
+ *     expert-parallel pack/unpack helpers, and a checkpoint loader for the
+ *     tensors of one MoE layer. They never change an upstream signature.
  *
  * Conventions (upstream qs_tensor.h:6-13, qsfi.h:14-18): strides are element
  * strides; an optional tensor is absent when data == NULL; all work is

@@ -81,8 +81,9 @@ def test_bf16_checkpoint_quantised_at_load_time(tmp_path, ops, loader, ctx):
     h, e, i, s = 256, 11, 128, 128
     d = make_moe_inputs(62, 4, h, e, i, s)
     ck, _ = _checkpoint(tmp_path, loader, ctx, d, nvfp4=False, transposed=True)
+    # hidden == 2 * intermediate: the shape of gate_up_proj does not tell its layout, the caller does
     w = loader.load_moe_layer(ck, PREFIX, hidden=h, inter=i, experts=e, shared_inter=s,
-                              backend=ops.capi.MOE_BACKEND_NVFP4)
+                              backend=ops.capi.MOE_BACKEND_NVFP4, fused_transposed=True)
     for got, src, gated in [(w.gate_up, d["gate_up"], True), (w.down, d["down"], False),
                             (w.shared.gate_up, d["sh_gate_up"], True), (w.shared.down, d["sh_down"], False)]:
         want = ops.nvfp4_quantize_weight(ctx, to_dev(src), gated)
