@@ -589,12 +589,16 @@ def fused_add_rmsnorm(ctx: Context, x, residual, weight, eps: float = 1e-6):
     ctx.check(ctx._lib.qsfi_fused_add_rmsnorm(ctx.handle, C.byref(d)))
 
 
-def fused_add_rmsnorm_nvfp4(ctx: Context, x, residual, weight, eps: float = 1e-6, global_scale: float = 1.0):
+def fused_add_rmsnorm_nvfp4(ctx: Context, x, residual, weight, eps: float = 1e-6, global_scale: float = 1.0,
+                            packed=None, tiled=None):
     """``qs3_fused_add_rmsnorm_nvfp4``: as above, and returns the NVFP4 codes and tiled scales
-    of the normalised rows (token order)."""
+    of the normalised rows (token order). ``packed`` / ``tiled``: buffers to write into (a caller
+    that replays a CUDA graph owns them); allocated here when absent."""
     rows, hidden = x.shape
-    packed = torch.empty((rows, hidden // 2), dtype=torch.uint8, device=x.device)
-    tiled = torch.zeros(nvfp4_tiled_scale_bytes(rows, hidden), dtype=torch.uint8, device=x.device)
+    if packed is None:
+        packed = torch.empty((rows, hidden // 2), dtype=torch.uint8, device=x.device)
+    if tiled is None:
+        tiled = torch.zeros(nvfp4_tiled_scale_bytes(rows, hidden), dtype=torch.uint8, device=x.device)
     d = capi.FusedAddRmsnormNvfp4Desc()
     d.norm = _fused_desc(x, residual, weight, eps)
     d.packed, d.scale_tiled, d.global_scale = _desc(packed, 2), _desc(tiled, 1), global_scale
