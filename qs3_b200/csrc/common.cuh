@@ -201,6 +201,8 @@ struct GemmProblem {
     const int32_t* tile_nrows;
     const int32_t* total_tiles;
     uint32_t max_tiles;
+    uint32_t tile_rows;  // rows per tile of the tables: 128, or 32 (NVFP4 decode kernel, operands swapped)
+    uint32_t est_tiles;  // expected number of tiles (sizes the splits of the decode kernel), 0: unknown
     // output
     void* out;
     uint64_t out_pitch_elems;   // elements (bytes for packed NVFP4 output)
@@ -215,6 +217,10 @@ struct GemmProblem {
 // Chooses the tcgen05 kernel when the shape allows it and the plain CUDA-core
 // kernel otherwise (tiny or unaligned shapes; bf16 only).
 cudaError_t launch_gemm(const GemmProblem& p, cudaStream_t stream, const char** why_unsupported);
+// NVFP4 grouped GEMM for 32-row token tiles (decode batches): weights are the M side of the MMA.
+cudaError_t launch_nvfp4_swap_gemm(const GemmProblem& p, cudaStream_t stream, const char** why_unsupported);
+// Rows per token tile of an NVFP4 plan: 32 (decode kernel) when experts get few rows each, else 128.
+uint32_t nvfp4_tile_rows(uint32_t routes, uint32_t experts, uint32_t hidden, uint32_t inter);
 bool gemm_tc_supported(const GemmProblem& p);
 
 // ---- NVFP4 ----------------------------------------------------------------------

@@ -217,6 +217,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // only when there are too few row tiles to fill the GPU.
 constexpr int kAsMaxKBlocks = 8;   // k <= 2048
 constexpr int kAsMaxStages = 8;
+constexpr uint32_t kSmallTileRows = 32; // bf16-output tiles with at most this many rows store them directly
 constexpr int kAsThreads = 320;    // warps 0-7 epilogue (two per TMEM lane quadrant), 8 producer, 9 MMA
 constexpr uint32_t kAsStageBytes = kTileBytes + kSfBytes;
 
@@ -409,10 +410,12 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // wait -> tcgen05.ld -> convert -> shared memory -> TMA store of one tile is longer
         // than the MMAs of a tile with a short k. Every row of the tile is written: rows past
         // the segment end are padding rows of the same expert, rows past the tensor are clipped.
+        // Tiles of at most kSmallTileRows rows skip the staging and store their rows directly.
         const uint32_t group = warp >> 2, quad = warp & 3;
         const uint32_t r = quad * 32 + lane;
         const bool issuer = quad == 0 && lane == 0;
         uint8_t* stage_buf = staging + group * 2 * kTileBytes;
+        const bool small_tile = nrows <= static_cast<int>(kSmallTileRows);
         float scale = p.alpha == 0.0f ? 1.0f : p.alpha;
         if (p.group_scale != nullptr)
             scale *= p.group_scale[expert];
@@ -423,6 +426,18 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             if (!ready)
                 break;
             tc_fence_after();
+            if (small_tile) {
+                // a tile with few rows (an expert that got a handful of tokens): only the warps that
+                // own valid rows read the accumulator, and they store those rows directly
+                if (quad * 32 < static_cast<uint32_t>(nrows))
+                    epilogue_tile<false, EPI_STORE_BF16, 1>(p, tmem_base + group * kBN, quad, lane, expert, row0,
+                                                            nrows, nt);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&acc_empty[group]);
+                continue;
+            }
             if (issuer) // this group's previous store must have left the staging tile
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
@@ -802,6 +817,8 @@ cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** 
 {
     if (why != nullptr)
         *why = nullptr;
+    if (g.nvfp4 && g.tile_expert != nullptr && g.tile_rows != 0 && g.tile_rows != static_cast<uint32_t>(kBM))
+        return launch_nvfp4_swap_gemm(g, stream, why);
     TcParams tp = make_params(g);
     const uint32_t m_tiles = g.tile_expert != nullptr
         ? g.max_tiles

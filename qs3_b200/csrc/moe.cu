@@ -105,7 +105,8 @@ Nvfp4Workspace carve_nvfp4(char* base, const qsfi_moe_plan_desc& d, uint32_t num
 {
     Nvfp4Workspace w {};
     const uint32_t routes = num_tokens * d.top_k;
-    size_t off = route_tables_carve(base, routes, d.local_num_experts, &w.rt);
+    size_t off = route_tables_carve(base, routes, d.local_num_experts, &w.rt,
+                                    nvfp4_tile_rows(routes, d.local_num_experts, d.hidden_size, d.intermediate_size));
     const size_t rows = w.rt.max_pad_rows;
     const size_t h = d.hidden_size, i = d.intermediate_size, e = d.local_num_experts;
     w.xq = carve<uint8_t>(base, off, rows * h / 2);
@@ -306,6 +307,7 @@ GemmProblem grouped_problem(const RouteTables& rt, uint32_t groups)
     g.tile_nrows = rt.tile_nrows;
     g.total_tiles = rt.total_tiles;
     g.max_tiles = rt.max_tiles;
+    g.tile_rows = rt.tile_rows;
     return g;
 }
 
@@ -413,7 +415,11 @@ qsfi_status run_routed_nvfp4(qsfi_context* ctx, const qsfi_moe_plan_desc& p, con
     const float ga = act_global == 0.0f ? 1.0f : act_global;
     const float ga2 = act2_global == 0.0f ? 1.0f : act2_global;
     stage_mark(ctx->stream, STAGE_GATE_UP_GEMM);
+    const uint32_t routes_hint = static_cast<uint32_t>(w.rt.max_pad_rows); // upper bound of the padded rows
+    const uint32_t est_tiles = std::min<uint32_t>(w.rt.max_tiles,
+                                                  p.local_num_experts + routes_hint / w.rt.tile_rows);
     GemmProblem g1 = grouped_problem(w.rt, p.local_num_experts);
+    g1.est_tiles = est_tiles;
     g1.nvfp4 = 1;
     g1.a = w.xq;
     g1.a_pitch_bytes = p.hidden_size / 2;
@@ -437,6 +443,7 @@ qsfi_status run_routed_nvfp4(qsfi_context* ctx, const qsfi_moe_plan_desc& p, con
         return status;
     stage_mark(ctx->stream, STAGE_DOWN_GEMM);
     GemmProblem g2 = grouped_problem(w.rt, p.local_num_experts);
+    g2.est_tiles = est_tiles;
     g2.nvfp4 = 1;
     g2.a = w.act;
     g2.a_pitch_bytes = p.intermediate_size / 2;

@@ -215,3 +215,35 @@ def test_gate_and_up_rows_with_separate_global_scales(ops, ctx, oracle):
                               shared=dict(gu=_triple(sh[0]), d=_triple(sh[1]), gate_w=d["sh_gate"]),
                               hidden_bf16=d["hidden"])
     assert rel_l2(to_np(out), single) > 0.05
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(t=16, h=512, e=64, k=4, i=256, s=256),                 # a few rows per expert, most experts empty
+    dict(t=128, h=2048, e=128, k=10, i=512, s=512, bias=True),  # decode batch of the prefill layer's shape
+    dict(t=40, h=256, e=4, k=2, i=256, s=0),                    # 80 routes on 4 experts: several 32-row tiles each
+])
+def test_decode_batches_take_the_swapped_operand_kernel(ops, ctx, oracle, cfg):
+    """With at most 16 routes per expert on average the plan pads expert segments to 32 rows and
+    the grouped GEMMs run with the weights as the M side of the MMA; same results as the oracle."""
+    t, h, e, k, i, s = cfg["t"], cfg["h"], cfg["e"], cfg["k"], cfg["i"], cfg["s"]
+    assert t * k <= 16 * e or e == 4
+    d = make_moe_inputs(41, t, h, e, i, s)
+    bias = zipf_bias(e, d["rng"]) if cfg.get("bias") else None
+    gu, dn, sh = _quantise_all(ops, ctx, d, bool(s))
+    plan = ops.MoePlan(ctx, ops.MoePlanConfig(max_num_tokens=t, hidden_size=h, intermediate_size=i,
+                                              num_experts=e, top_k=k, backend=ops.capi.MOE_BACKEND_NVFP4))
+    ws = torch.zeros(plan.layer_workspace_size(t, s), dtype=torch.uint8, device="cuda")
+    out = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+    ids_t = torch.empty((t, k), dtype=torch.int32, device="cuda")
+    w_t = torch.empty((t, k), dtype=torch.float32, device="cuda")
+    shared = ops.SharedExpert(sh[0], sh[1], to_dev(d["sh_gate"]), s) if s else None
+    ops.moe_layer_execute(plan, to_dev(d["hidden"]), to_dev(d["router"]), gu, dn, out, ws,
+                          router_bias=None if bias is None else to_dev(bias), shared=shared,
+                          act_global_scale=0.5, act2_global_scale=0.25, topk_ids=ids_t, topk_weights=w_t)
+    torch.cuda.synchronize()
+    assert ctx.read_device_error() == 0
+    hp, hs = oracle.nvfp4_quantize_act(d["hidden"], 0.5)
+    shared_ref = dict(gu=_triple(sh[0]), d=_triple(sh[1]), gate_w=d["sh_gate"]) if s else None
+    ref = oracle.moe_nvfp4(hp, hs, to_np(ids_t), to_np(w_t), _triple(gu), _triple(dn), act_global=0.5,
+                           act2_global=0.25, shared=shared_ref, hidden_bf16=d["hidden"])
+    _check(to_np(out), ref)
