@@ -9,7 +9,8 @@
 //
 //   grid   (feature splits, token tiles); one CTA = one 32-row token tile of one expert and a
 //          range of 128-row feature blocks of that expert's weight
-//   smem   token panel (all of k: k/256 tiles of 32 x 128 B) and its scale tiles, resident;
+//   smem   token panel (all of k: k/256 tiles of 32 x 128 B) resident, its scale tiles (later the
+//          gate / up exchange buffer);
 //          weight ring: stages x (128 x 128 B codes + 4 scale tiles)
 //   TMEM   2 accumulators of 32 columns (lane = feature, column = token) | 2 x 16 columns of
 //          weight scales (alternating per k block) | token scales of all of k
@@ -76,7 +77,7 @@ struct SwapParams {
 };
 
 template <bool GATED>
-__global__ void __launch_bounds__(kSwThreads)
+__global__ void __launch_bounds__(kSwThreads, 2)
 gemm_nvfp4_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                        const SwapParams p)
 {
@@ -96,7 +97,7 @@ gemm_nvfp4_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* panel = smem;                                   // k_blocks x 4 KB
     uint8_t* panel_sf = panel + p.k_blocks * kSwPanelTile;   // kgroups x 512 B
-    uint8_t* ring = panel_sf + ((p.kgroups * 512u + 1023u) & ~1023u);
+    uint8_t* ring = panel_sf + max((p.kgroups * 512u + 1023u) & ~1023u, GATED ? kSwUpBytes : 0u);
     uint8_t* misc = ring + p.stages * kSwStageBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);
     uint64_t* empty_bar = full_bar + kSwMaxStages;
@@ -106,7 +107,9 @@ gemm_nvfp4_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     uint64_t* sf_bar = panel_bar + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 256);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* s_up = reinterpret_cast<float*>(misc + kSwMiscBytes); // [token][64 features], gated only
+    // [token][64 features], gated only; reuses the token scale tiles, which are dead once copied to
+    // tensor memory (the first accumulator is complete only after those copies)
+    float* s_up = reinterpret_cast<float*>(panel_sf);
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -399,15 +402,17 @@ cudaError_t launch_nvfp4_swap_gemm(const GemmProblem& g, cudaStream_t stream, co
     sp.err = device_error_word();
 
     const size_t fixed = 1024 + static_cast<size_t>(sp.k_blocks) * kSwPanelTile
-        + ((static_cast<size_t>(sp.kgroups) * 512 + 1023) & ~static_cast<size_t>(1023)) + kSwMiscBytes
-        + (gated ? kSwUpBytes : 0);
-    const size_t budget = 220 * 1024;
+        + std::max((static_cast<size_t>(sp.kgroups) * 512 + 1023) & ~static_cast<size_t>(1023),
+                   static_cast<size_t>(gated ? kSwUpBytes : 0))
+        + kSwMiscBytes;
+    // two CTAs per SM: one CTA's start-up (token panel, scale tiles) hides behind the other's weight stream
+    const size_t budget = 112 * 1024;
     sp.stages = static_cast<uint32_t>(std::min<size_t>(kSwMaxStages, (budget - fixed) / kSwStageBytes));
     const size_t smem = fixed + static_cast<size_t>(sp.stages) * kSwStageBytes;
 
-    // feature splits: about four CTAs per SM over the launch, so that the tail is short
+    // feature splits: about eight CTAs per SM over the launch, so that the tail is short
     const uint32_t tiles = std::max(1u, std::min(g.max_tiles, g.est_tiles != 0 ? g.est_tiles : g.max_tiles));
-    const uint32_t want = std::max(1u, (4u * device_sm_count() + tiles - 1) / tiles);
+    const uint32_t want = std::max(1u, (8u * device_sm_count() + tiles - 1) / tiles);
     sp.fb_per_cta = std::max(1u, (sp.num_fb + want - 1) / want);
     const uint32_t splits = (sp.num_fb + sp.fb_per_cta - 1) / sp.fb_per_cta;
 
