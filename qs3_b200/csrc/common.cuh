@@ -217,6 +217,9 @@ struct GemmProblem {
 // Chooses the tcgen05 kernel when the shape allows it and the plain CUDA-core
 // kernel otherwise (tiny or unaligned shapes; bf16 only).
 cudaError_t launch_gemm(const GemmProblem& p, cudaStream_t stream, const char** why_unsupported);
+// Persistent 128 x 256 kernel for dense bf16 problems with more than 64 rows (gemm_dense.cu).
+bool gemm_dense_bf16_supported(const GemmProblem& p);
+cudaError_t launch_gemm_dense_bf16(const GemmProblem& p, cudaStream_t stream, const char** why_unsupported);
 // NVFP4 grouped GEMM for 32-row token tiles (decode batches): weights are the M side of the MMA.
 cudaError_t launch_nvfp4_swap_gemm(const GemmProblem& p, cudaStream_t stream, const char** why_unsupported);
 // Rows per token tile of an NVFP4 plan: 32 (decode kernel) when experts get few rows each, else 128.

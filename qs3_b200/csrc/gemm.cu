@@ -1,9 +1,11 @@
 // Grouped / dense GEMM  D[m, n] = sum_k A[m, k] * B[g][n, k]. Kernels in this file:
-//   gemm_tc_kernel        tcgen05, one 128 x 128 tile per CTA: every bf16 problem, NVFP4 with k > 2048
+//   gemm_tc_kernel        tcgen05, one 128 x 128 tile per CTA: grouped bf16 problems, NVFP4 with k > 2048
+//                         (dense bf16 problems with more than 64 rows go to gemm_dense.cu)
 //   gemm_tc_astat_kernel  tcgen05, NVFP4 with the A panel resident in shared memory (k <= 2048)
 //   gemm_skinny_kernel    CUDA cores, bf16 with at most 64 rows (router logits of a decode batch)
 //   gemm_simt_kernel      CUDA cores, shapes the tensor-core tiles cannot address
-// launch_gemm() at the end picks one.
+// launch_gemm() at the end picks one of these, the dense kernel of gemm_dense.cu or the decode
+// kernel of nvfp4_decode.cu.
 //
 // gemm_tc_kernel: one 128 x 128 output tile per CTA on the 5th-generation tensor cores:
 //
@@ -832,6 +834,8 @@ cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** 
     }
     if (skinny_supported(g))
         return launch_skinny(g, stream);
+    if (gemm_dense_bf16_supported(g))
+        return launch_gemm_dense_bf16(g, stream, why);
     if (gemm_tc_supported(g)) {
         const uint32_t feat = g.gated ? kBN / 2 : kBN;
         dim3 grid((g.n + feat - 1) / feat, m_tiles, 1);

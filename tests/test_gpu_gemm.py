@@ -103,3 +103,31 @@ def test_tensor_peak_probe_runs(kind):
     tf = ops.tensor_peak_probe(ctx, kind, n=128, iters=2000)
     assert 10.0 < tf < 40000.0
     assert ctx.read_device_error() == 0
+
+
+@pytest.mark.parametrize("shape", [(65, 64, 128), (129, 64, 257), (257, 192, 300), (700, 1024, 2304), (128, 2048, 5000)])
+@pytest.mark.parametrize("out_dtype", ["f32", "bf16"])
+def test_dense_kernel_edges_and_epilogue(gemm, shape, out_dtype):
+    """More than 64 rows, k a multiple of 64, n >= 128: the persistent 128 x 256 kernel. Ragged
+    rows and columns, alpha / beta, padded row strides (sentinel padding must survive)."""
+    rows, k, n = shape
+    rng = np.random.default_rng(rows + 3 * k + 5 * n)
+    x = bf16(rng.standard_normal((rows, k), dtype=np.float32))
+    w = bf16(rng.standard_normal((n, k), dtype=np.float32) * 0.05)
+    c = bf16(rng.standard_normal((rows, n), dtype=np.float32))
+    dt = torch.float32 if out_dtype == "f32" else torch.bfloat16
+    x_full = torch.full((rows, k + 8), 3.0, dtype=torch.bfloat16, device="cuda")
+    w_full = torch.full((n, k + 24), -2.0, dtype=torch.bfloat16, device="cuda")
+    o_full = torch.full((rows, n + 8), 5.0, dtype=dt, device="cuda")
+    x_full[:, :k] = to_dev(x)
+    w_full[:, :k] = to_dev(w)
+    o_full[:, :n] = to_dev(c).to(dt)
+    gemm.gemm_bf16(x_full[:, :k], w_full[:, :k], o_full[:, :n], alpha=0.5, beta=-1.5)
+    torch.cuda.synchronize()
+    got = o_full.float().cpu().numpy().astype(np.float64)
+    want = 0.5 * _ref(x, w) - 1.5 * f32(c).astype(np.float64)
+    if out_dtype == "f32":
+        assert np.linalg.norm(got[:, :n] - want) <= 1e-5 * np.linalg.norm(want) + 1e-9
+    else:
+        assert np.all(np.abs(got[:, :n] - want) <= np.abs(want) * 2.0 ** -7 + 2e-3)
+    assert np.all(got[:, n:] == 5.0)
