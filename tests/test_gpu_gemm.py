@@ -105,11 +105,13 @@ def test_tensor_peak_probe_runs(kind):
     assert ctx.read_device_error() == 0
 
 
-@pytest.mark.parametrize("shape", [(65, 64, 128), (129, 64, 257), (257, 192, 300), (700, 1024, 2304), (128, 2048, 5000)])
+@pytest.mark.parametrize("shape", [(65, 64, 128), (129, 64, 257), (257, 192, 300), (700, 1024, 2304), (128, 2048, 5000),
+                                   (2100, 256, 2400), (2305, 128, 2048)])   # the last two: CTA-pair kernel
 @pytest.mark.parametrize("out_dtype", ["f32", "bf16"])
 def test_dense_kernel_edges_and_epilogue(gemm, shape, out_dtype):
-    """More than 64 rows, k a multiple of 64, n >= 128: the persistent 128 x 256 kernel. Ragged
-    rows and columns, alpha / beta, padded row strides (sentinel padding must survive)."""
+    """More than 64 rows, k a multiple of 64, n >= 128: the persistent 128 x 256 kernel, or with at
+    least 74 tiles of 256 x 256 its CTA-pair variant. Ragged rows and columns, alpha / beta, padded
+    row strides (sentinel padding must survive)."""
     rows, k, n = shape
     rng = np.random.default_rng(rows + 3 * k + 5 * n)
     x = bf16(rng.standard_normal((rows, k), dtype=np.float32))
