@@ -231,6 +231,12 @@ cudaError_t launch_nvfp4_gather_quantize(const __nv_bfloat16* hidden, const int3
                                          uint32_t routes, uint32_t top_k, uint32_t hidden_size,
                                          float global_scale, uint8_t* packed, uint8_t* scale_tiled,
                                          cudaStream_t stream);
+// Gather of already-quantised token rows into the padded permuted layout of sorted routing tables.
+// 128-row tiles: organised by destination tile (coalesced code rows, whole scale tiles; rows past a
+// tile's last row keep stale codes and get zero scales); smaller tiles: launch_nvfp4_gather_packed.
+cudaError_t launch_nvfp4_gather_tiles(const uint8_t* hidden_packed, const uint8_t* hidden_scale, const RouteTables& rt,
+                                      uint32_t routes, uint32_t top_k, uint32_t hidden_size, uint8_t* packed,
+                                      uint8_t* scale_tiled, cudaStream_t stream, int src_scale_tiled = 0);
 // `src_scale_tiled`: the source scales are tiled by token row instead of row-major.
 cudaError_t launch_nvfp4_gather_packed(const uint8_t* hidden_packed, const uint8_t* hidden_scale,
                                        const int32_t* route_prows, uint32_t routes, uint32_t top_k,

@@ -882,9 +882,9 @@ qsfi_status qsfi_moe_execute_nvfp4(qsfi_context* ctx, const qsfi_moe_plan* plan,
                                 static_cast<const float*>(desc->topk_weights.data), routes, p.top_k,
                                 p.local_expert_offset, p.local_num_experts, w.rt, st);
     if (err == cudaSuccess)
-        err = launch_nvfp4_gather_packed(static_cast<const uint8_t*>(desc->hidden_packed.data),
-                                         static_cast<const uint8_t*>(desc->hidden_scale.data),
-                                         w.rt.route_prows, routes, p.top_k, p.hidden_size, w.xq, w.xq_sf, st);
+        err = launch_nvfp4_gather_tiles(static_cast<const uint8_t*>(desc->hidden_packed.data),
+                                        static_cast<const uint8_t*>(desc->hidden_scale.data), w.rt, routes,
+                                        p.top_k, p.hidden_size, w.xq, w.xq_sf, st);
     if (err != cudaSuccess)
         return set_cuda_error(ctx, err, "NVFP4 MoE routing");
     Nvfp4Weights wt {};
@@ -1253,8 +1253,8 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
             err = launch_nvfp4_gather_quantize(hidden, nullptr, d->num_tokens, 1, p.hidden_size,
                                                d->act_global_scale, x.sh_xq, x.sh_xq_sf, st);
         if (err == cudaSuccess)
-            err = launch_nvfp4_gather_packed(x.sh_xq, x.sh_xq_sf, rt.route_prows, routes, p.top_k,
-                                             p.hidden_size, wn.xq, wn.xq_sf, st, 1);
+            err = launch_nvfp4_gather_tiles(x.sh_xq, x.sh_xq_sf, rt, routes, p.top_k, p.hidden_size, wn.xq, wn.xq_sf,
+                                            st, 1);
         if (err != cudaSuccess)
             return set_cuda_error(ctx, err, "NVFP4 MoE gather");
         Nvfp4Weights wt {};
@@ -1518,9 +1518,9 @@ qsfi_status qs3_moe_execute_nvfp4_prepared(qsfi_context* ctx, const qsfi_moe_pla
                                         p.local_expert_offset, p.local_num_experts, w.rt, st);
     stage_mark(st, STAGE_GATHER);
     if (err == cudaSuccess)
-        err = launch_nvfp4_gather_packed(static_cast<const uint8_t*>(d->hidden_packed.data),
-                                         static_cast<const uint8_t*>(d->hidden_scale.data), w.rt.route_prows,
-                                         routes, p.top_k, p.hidden_size, w.xq, w.xq_sf, st);
+        err = launch_nvfp4_gather_tiles(static_cast<const uint8_t*>(d->hidden_packed.data),
+                                        static_cast<const uint8_t*>(d->hidden_scale.data), w.rt, routes,
+                                        p.top_k, p.hidden_size, w.xq, w.xq_sf, st);
     if (err != cudaSuccess)
         return set_cuda_error(ctx, err, "NVFP4 MoE routing");
     Nvfp4Weights wt {};

@@ -160,6 +160,62 @@ gather_packed_kernel(const uint8_t* __restrict__ hidden_packed, const uint8_t* _
     *reinterpret_cast<uint32_t*>(scale_tiled + tiled_scale_offset(prow, 4ull * kg, kgroups)) = sf;
 }
 
+// The same gather organised by destination tile, for 128-row token tiles: block (k chunk, tile)
+// moves the rows of one token tile of one expert for 512 elements of k. The codes of a row chunk are 256 contiguous
+// bytes (16 threads x 16 bytes), and a scale tile of the destination (512 bytes: 32 lanes x
+// four 32-row groups) is written with one 16-byte store per lane instead of 128 scattered
+// 4-byte stores. Rows are found through the
+// routing tables: padded row -> dense row -> token.
+constexpr uint32_t kGatherChunk = 512; // elements of k per block
+
+__global__ void __launch_bounds__(256)
+gather_packed_tiles_kernel(const uint8_t* __restrict__ hidden_packed, const uint8_t* __restrict__ hidden_scale,
+                           const RouteTables rt, uint32_t hidden_size, uint8_t* __restrict__ packed,
+                           uint8_t* __restrict__ scale_tiled, int src_scale_tiled)
+{
+    const uint32_t tile = blockIdx.y;
+    if (static_cast<int>(tile) >= *rt.total_tiles)
+        return;
+    const int expert = rt.tile_expert[tile];
+    const uint32_t row0 = static_cast<uint32_t>(rt.tile_row0[tile]);
+    const uint32_t nrows = static_cast<uint32_t>(rt.tile_nrows[tile]);
+    // dense (unpadded) row of the tile's first row: same offset inside the expert's segment
+    const uint32_t dense0 = static_cast<uint32_t>(rt.indptr[expert])
+        + (row0 - static_cast<uint32_t>(rt.pad_indptr[expert]));
+    const uint32_t kgroups = hidden_size / 64;
+    const uint32_t row_bytes = hidden_size / 2;
+    const uint32_t chunk_bytes = kGatherChunk / 2;
+    const uint32_t c0 = blockIdx.x * chunk_bytes;
+
+    // codes: 16 threads per row, 16 rows per pass
+    const uint32_t sub = threadIdx.x & 15;
+    if (c0 + sub * 16 < row_bytes) {
+        for (uint32_t j = threadIdx.x >> 4; j < nrows; j += 16) {
+            const uint64_t token = static_cast<uint64_t>(rt.row_tokens[dense0 + j]);
+            const uint4 v = *reinterpret_cast<const uint4*>(hidden_packed + token * row_bytes + c0 + sub * 16);
+            *reinterpret_cast<uint4*>(packed + static_cast<uint64_t>(row0 + j) * row_bytes + c0 + sub * 16) = v;
+        }
+    }
+    // scales: this block's k groups
+    const uint32_t kg0 = blockIdx.x * (kGatherChunk / 64);
+    const auto src_word = [&](uint32_t j, uint32_t kg) -> uint32_t {
+        if (j >= nrows)
+            return 0u;
+        const uint64_t token = static_cast<uint64_t>(rt.row_tokens[dense0 + j]);
+        const uint64_t off = src_scale_tiled ? tiled_scale_offset(token, 4ull * kg, kgroups)
+                                             : token * (hidden_size / 16) + kg * 4;
+        return *reinterpret_cast<const uint32_t*>(hidden_scale + off);
+    };
+    // thread = (k group, lane of the scale tile): the words of rows lane, lane + 32, lane + 64, lane + 96
+    const uint32_t kg = kg0 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (kg < kgroups) {
+        const uint4 v = make_uint4(src_word(lane, kg), src_word(lane + 32, kg), src_word(lane + 64, kg),
+                                   src_word(lane + 96, kg));
+        *reinterpret_cast<uint4*>(scale_tiled + (static_cast<uint64_t>(row0 >> 7) * kgroups + kg) * 512 + lane * 16)
+            = v;
+    }
+}
+
 // linear [experts, rows, k/16] -> tiled; one thread per (row, k group).
 __global__ void tile_scales_kernel(const uint8_t* __restrict__ linear, uint32_t rows, uint32_t k,
                                    uint64_t total, uint8_t* __restrict__ tiled, uint64_t tiled_bytes,
@@ -211,6 +267,23 @@ cudaError_t launch_nvfp4_gather_packed(const uint8_t* hidden_packed, const uint8
     gather_packed_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
         hidden_packed, hidden_scale, route_prows, total, top_k, hidden_size, packed, scale_tiled,
         src_scale_tiled);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_nvfp4_gather_tiles(const uint8_t* hidden_packed, const uint8_t* hidden_scale, const RouteTables& rt,
+                                      uint32_t routes, uint32_t top_k, uint32_t hidden_size, uint8_t* packed,
+                                      uint8_t* scale_tiled, cudaStream_t stream, int src_scale_tiled)
+{
+    if (rt.max_tiles == 0)
+        return cudaSuccess;
+    // 32-row tiles (decode batches) hold a few rows each: a thread per (route, k group) does better there
+    if (rt.tile_rows != 128)
+        return launch_nvfp4_gather_packed(hidden_packed, hidden_scale, rt.route_prows, routes, top_k, hidden_size,
+                                          packed, scale_tiled, stream, src_scale_tiled);
+    const dim3 grid((hidden_size + kGatherChunk - 1) / kGatherChunk, rt.max_tiles, 1);
+    gather_packed_tiles_kernel<<<grid, 256, 0, stream>>>(hidden_packed, hidden_scale, rt, hidden_size, packed,
+                                                        scale_tiled, src_scale_tiled);
     note_launch();
     return cudaGetLastError();
 }
