@@ -182,10 +182,10 @@ gemm_dense_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 // (two SMs) compute one 256 x 256 tile with cta_group::2 instructions: each loads its own 128
 // rows of A and HALF of the 256 B rows, the tensor cores of both SMs read both halves, and each
 // CTA ends up with its 128 output rows in its own tensor memory. Operand traffic per product
-// drops by a third. No load is multicast: each CTA's TMA loads (cta_group::2 form) signal the
-// barrier of the pair's first CTA, which issues the MMAs for both.
+// drops by a third. Every load has one destination CTA: each CTA's own TMA loads (cta_group::2
+// form) signal the barrier of the pair's first CTA, which issues the MMAs for both.
 //
-//   barriers  full[s]      first CTA only: its expect_tx covers both CTAs' 32 KB of the stage
+//   barriers  full[s]      first CTA only: its expect_tx covers both CTAs' tiles of the stage
 //             empty[s]     one per CTA: the first CTA commits to its own and to its peer's
 //             acc_full[b]  one per CTA, same way;  acc_empty[b] first CTA only, 16 arrivals
 //                          (eight epilogue warps of each CTA, the peer's through cluster addresses)
