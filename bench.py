@@ -9,7 +9,8 @@ one batch of synthetic tokens. At N = 1 the workload is the NVFP4 prefill layer
 (8192 tokens, hidden 2048, 512 experts, top-10 + shared expert, Zipf-skewed router);
 at N > 1 it is the expert-parallel variant with 4096 tokens per rank (weak scaling),
 launched one process per GPU by torch.distributed.run. `--workload decode_fp8` (N = 1)
-times the FP8 block-scaled decode batch instead (64 tokens, 128 experts, top-8).
+times the FP8 block-scaled decode batch instead (64 tokens, 128 experts, top-8) and
+`--workload decode_nvfp4` a 128-token decode batch of the NVFP4 layer (unbiased router).
 
 Prints ONE JSON line on rank 0. `value` is device-timed (CUDA events, max over
 ranks) with inputs resident in HBM; `e2e` goes through the same C-ABI call with the
@@ -169,7 +170,8 @@ def _workload(args):
     --workload names the FP8 decode batch; at N > 1 the expert-parallel NVFP4 layer."""
     from qs3_b200 import workload
     if args.gpus == 1:
-        return workload.DECODE_FP8 if args.workload == "decode_fp8" else workload.PREFILL_NVFP4
+        return {"decode_fp8": workload.DECODE_FP8, "decode_nvfp4": workload.DECODE_NVFP4}.get(
+            args.workload, workload.PREFILL_NVFP4)
     if args.workload != "prefill_nvfp4":
         raise SystemExit("only the NVFP4 layer runs expert-parallel")
     return workload.EP_NVFP4
@@ -456,7 +458,9 @@ class SingleGpuLayer:
         else:
             act_in = routes * (cfg.hidden // 2 + cfg.hidden // 16)
             act_out = routes * (cfg.inter // 2 + cfg.inter // 16)
-            kernel, nominal, key = "gemm_tc_astat_kernel<gated, swiglu_nvfp4>", 9e15, "tensor_frac_of_nominal_fp4"
+            decode = routes <= 16 * cfg.experts   # the plan's own rule for the swapped-operand kernel
+            kernel = "gemm_nvfp4_swap_kernel<gated>" if decode else "gemm_tc_astat_kernel<gated, swiglu_nvfp4>"
+            nominal, key = 9e15, "tensor_frac_of_nominal_fp4"
         algo = hit * gu_bytes + act_in + act_out
         achieved = algo / (ms * 1e-3) / 1e9
         # DRAM bytes per launch: ncu measured dram read + write = 1.02 x the algorithmic bytes for both
@@ -492,8 +496,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="prefill_nvfp4", choices=["prefill_nvfp4", "decode_fp8"],
-                    help="N = 1 only: the FP8 decode batch (64 tokens, 128 experts, top-8) instead of the headline layer")
+    ap.add_argument("--workload", default="prefill_nvfp4", choices=["prefill_nvfp4", "decode_fp8", "decode_nvfp4"],
+                    help="N = 1 only: the FP8 decode batch (64 tokens, 128 experts, top-8) or a 128-token decode "
+                         "batch of the NVFP4 layer instead of the headline layer")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="N > 1: how the experts are assigned to ranks")
     ap.add_argument("--no-graph", action="store_true",

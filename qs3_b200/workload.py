@@ -37,6 +37,9 @@ PREFILL_NVFP4 = LayerConfig("qwen3next_moe_prefill_nvfp4", 8192, 2048, 512, 10, 
 # per-rank slice of the expert-parallel configuration (4096 tokens per rank)
 EP_NVFP4 = LayerConfig("qwen3next_moe_ep_nvfp4", 4096, 2048, 512, 10, 512, 512, True, 1.1)
 TINY_BF16 = LayerConfig("tiny_bf16", 16, 256, 8, 2, 128, 0, False, 0.0)
+# decode batch of the same layer as the prefill workload (what one layer of the 48-layer hybrid decode
+# sees: 128 sequences, unbiased router, so almost every expert is hit by a few rows)
+DECODE_NVFP4 = LayerConfig("qwen3next_moe_decode_nvfp4", 128, 2048, 512, 10, 512, 512, True, 0.0)
 # Qwen3-30B-A3B-shaped decode batch: 64 tokens, 128 experts, top-8, FP8 block-scaled, no shared expert
 DECODE_FP8 = LayerConfig("qwen3_30b_a3b_moe_decode_fp8", 64, 2048, 128, 8, 768, 0, False, 0.0, True)
 
