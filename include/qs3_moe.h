@@ -677,8 +677,11 @@ qsfi_status qs3_moe_profile_end(
  * kind 0 = bf16 (kind::f16), 1 = fp8 e4m3 (kind::f8f6f4), 2 = NVFP4 block-scaled
  * (kind::mxf4nvf4, scale_vec::4X). n is a multiple of 16 in [16, 256]. kind + 16: CTA
  * pairs (clusters of two) issue cta_group::2 instructions of 256 x n instead (n a multiple
- * of 32). Returns dense TFLOP/s. Used as the denominator of the reported tensor-pipe
- * fractions. */
+ * of 32). kind + 256 * a + 4096 * b (single-CTA NVFP4 probe only, a, b <= 8): every iteration
+ * also issues a scale-tile copies (tcgen05.cp, 512 bytes each) from the MMA thread ahead of its
+ * MMAs and b from a second thread, which measures what the scale copies of a block-scaled
+ * main loop cost. Returns dense TFLOP/s. Used as the denominator of the reported
+ * tensor-pipe fractions. */
 qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, uint32_t n, uint32_t iters, double* tflops);
 
 /* ================================================= checkpoint loader ======

@@ -65,6 +65,14 @@ def num_threads() -> int:
     return int(lib().qs3o_num_threads())
 
 
+def set_num_threads(n: int | None = None) -> int:
+    """Use ``n`` OpenMP threads from now on (default: every core this process may run on)."""
+    if n is None:
+        n = len(os.sched_getaffinity(0))
+    lib().qs3o_set_num_threads(C.c_int(int(n)))
+    return num_threads()
+
+
 # ----------------------------------------------------------------- codecs ---
 
 def f32_to_bf16(x: np.ndarray) -> np.ndarray:

@@ -232,6 +232,18 @@ QS3O_API int qs3o_num_threads(void)
 #endif
 }
 
+// Number of OpenMP threads later calls use (launchers such as torch.distributed.run export
+// OMP_NUM_THREADS=1, which would otherwise time this code on one core).
+QS3O_API void qs3o_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0)
+        omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 // ------------------------------------------------------------------ router ---
 
 // Router top-k for one block of tokens. Follows the upstream CPU checker

@@ -17,8 +17,12 @@ enum ProbeKind { PROBE_BF16 = 0, PROBE_FP8 = 1, PROBE_NVFP4 = 2 };
 // One CTA per SM: A tile 128 rows x 128 bytes, B tile n rows x 128 bytes, 128-byte swizzle
 // layout (contents are pseudo-random bytes; the result is never read). Each iteration
 // issues the MMAs that consume one 128-byte k-block: 4 instructions of K = 32 bytes.
+// cps_main / cps_side (NVFP4 only): scale-tile copies (tcgen05.cp, 512 bytes each) per
+// iteration issued by the MMA thread ahead of its four MMAs, into the scale columns those
+// MMAs read / by a second thread that runs free of the first. They measure what the scale
+// copies of a block-scaled main loop cost the tensor pipe.
 __global__ void __launch_bounds__(128, 1)
-tensor_peak_kernel(int kind, uint32_t n, uint32_t iters, uint32_t* err)
+tensor_peak_kernel(int kind, uint32_t n, uint32_t iters, uint32_t* err, uint32_t cps_main, uint32_t cps_side)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -63,10 +67,15 @@ tensor_peak_kernel(int kind, uint32_t n, uint32_t iters, uint32_t* err)
         const uint64_t db = operand_desc(smem_u32(b_tile));
         const uint32_t sfa = tmem_base + 256, sfb = tmem_base + 272;
         if (kind == PROBE_NVFP4) {
-            for (uint32_t c = 0; c < 12; ++c) // scale 1.0 everywhere the MMAs may look
+            for (uint32_t c = 0; c < 40; ++c) // scale 1.0 everywhere the MMAs may look
                 tc_cp_scales(sfa + 4 * c, scale_desc(smem_u32(sf_tile)));
         }
+        const uint64_t sdesc = scale_desc(smem_u32(sf_tile));
         for (uint32_t it = 0; it < iters; ++it) {
+            // the copies alternate between two groups of scale columns, as a main loop does
+            const uint32_t sfb_it = cps_main != 0 ? sfb + 64 * (it & 1) : sfb;
+            for (uint32_t c = 0; c < cps_main; ++c)
+                tc_cp_scales(sfb_it + 4 * c, sdesc);
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
                 const uint32_t acc = (it | j) != 0 ? 1u : 0u;
@@ -75,11 +84,17 @@ tensor_peak_kernel(int kind, uint32_t n, uint32_t iters, uint32_t* err)
                 else if (kind == PROBE_FP8)
                     tc_mma_f8(tmem_base, da + 2 * j, db + 2 * j, idesc, acc);
                 else
-                    tc_mma_nvfp4(tmem_base, da + 2 * j, db + 2 * j, idesc, acc, sfa, sfb);
+                    tc_mma_nvfp4(tmem_base, da + 2 * j, db + 2 * j, idesc, acc, sfa, sfb_it + 8 * (j & 1));
             }
         }
         tc_commit(done_bar);
         mbar_wait<true>(done_bar, 0, abort_flag, err, 0x53000001u);
+    } else if (threadIdx.x == 32 && cps_side != 0 && kind == PROBE_NVFP4) {
+        const uint64_t sdesc = scale_desc(smem_u32(sf_tile));
+        const uint32_t side = tmem_base + 416; // columns no MMA of this probe reads
+        for (uint32_t it = 0; it < iters; ++it)
+            for (uint32_t c = 0; c < cps_side; ++c)
+                tc_cp_scales(side + 4 * c, sdesc);
     }
     tc_fence_before();
     __syncthreads();
@@ -200,7 +215,10 @@ extern "C" qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, u
     if (status != QSFI_STATUS_OK)
         return status;
     const bool pair = (kind & 16u) != 0; // + 16: CTA pairs issuing cta_group::2 instructions of 256 x n
-    kind &= ~16u;
+    const uint32_t cps_main = (kind >> 8) & 15u, cps_side = (kind >> 12) & 15u;
+    kind &= 15u;
+    if ((cps_main | cps_side) != 0 && (pair || kind != 2 || cps_main > 8 || cps_side > 8))
+        return set_invalid_arg(ctx, "peak probe: scale copies go with the single-CTA NVFP4 probe, at most 8 per iteration");
     if (kind > 2 || n < 16 || n > 256 || n % 16 != 0 || iters == 0 || iters > (1u << 22) || (pair && n % 32 != 0))
         return set_invalid_arg(ctx, "peak probe: kind in {0,1,2} (+16), n a multiple of 16 in [16, 256], iters in [1, 2^22]");
     int dev = 0, sms = 0;
@@ -228,7 +246,8 @@ extern "C" qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, u
         if (pair)
             tensor_peak_pair_kernel<<<sms, 128, smem, ctx->stream>>>(static_cast<int>(kind), n, count, errw);
         else
-            tensor_peak_kernel<<<sms, 128, smem, ctx->stream>>>(static_cast<int>(kind), n, count, errw);
+            tensor_peak_kernel<<<sms, 128, smem, ctx->stream>>>(static_cast<int>(kind), n, count, errw, cps_main,
+                                                                cps_side);
     };
     launch(64); // warm-up
     cudaEventRecord(e0, ctx->stream);

@@ -325,6 +325,16 @@ class ExpertParallelLayer:
             b.finish(hidden, self.recv, out)
         return out
 
+    def routing_snapshot(self):
+        """What the last step's experts phase sorted on this rank, as numpy arrays: (ids, weights)
+        of every token row it saw, the rank's expert range, and the plan's routing tables
+        (counts, indptr, route_rows, row_tokens). For parity checks."""
+        first, count = self.data.expert_range
+        b = self.backend
+        tables = b.plan.routing_tables(b.ws_experts, self.g_ids.shape[0])
+        return (self.g_ids.cpu().numpy(), self.g_wts.cpu().numpy(), first, count,
+                [x.cpu().numpy() for x in tables[:4]])
+
     # -- measurement helpers used by bench.py --
     def profile(self, iters):
         """Mean ms of the phases, timed with CUDA events on a serialised pass."""

@@ -262,15 +262,19 @@ class HybridDecoder:
             # residual += mix; mix = norm(residual) (bf16) and its NVFP4 codes, one pass
             ops.fused_add_rmsnorm_nvfp4(ctx, mix, self.residual, blk.post_mixer_norm, cfg.eps, 1.0,
                                         packed=self.packed, tiled=self.tiled)
+            trace_logits = None
             if self.trace is not None:
                 self.trace.append(dict(normed=mix.clone(), residual_in=self.residual.clone()))
+                trace_logits = torch.empty((mix.shape[0], cfg.experts), dtype=torch.float32, device=mix.device)
             # experts + shared expert + combine; residual += out; x = norm(residual) * next layer's weight
             ops.moe_layer_execute(self.plan, mix, blk.router, blk.gate_up, blk.down, self.x, self.ws,
                                   shared=blk.shared, hidden_packed=self.packed, hidden_scale_tiled=self.tiled,
                                   residual_inout=self.residual, next_norm_weight=self.input_norm[layer + 1],
-                                  next_norm_eps=cfg.eps, topk_ids=self.ids, topk_weights=self.weights)
+                                  next_norm_eps=cfg.eps, topk_ids=self.ids, topk_weights=self.weights,
+                                  router_logits=trace_logits)
             if self.trace is not None:
                 self.trace[-1].update(ids=self.ids.clone(), weights=self.weights.clone(), x_out=self.x.clone(),
+                                      logits=trace_logits,
                                       residual_out=self.residual.clone())
         self.gemm.gemm_bf16(self.x, self.lm_head, self.logits, alpha=1.0)
         self.tokens.copy_(self.logits.argmax(dim=-1))

@@ -558,13 +558,15 @@ PEAK_KINDS = {"bf16": 0, "fp8": 1, "nvfp4": 2}
 
 
 def tensor_peak_probe(ctx: Context, kind: str = "nvfp4", n: int = 256, iters: int = 20000,
-                      pair: bool = False) -> float:
+                      pair: bool = False, cps_main: int = 0, cps_side: int = 0) -> float:
     """Dense TFLOP/s of back-to-back ``tcgen05.mma`` (128 x n tiles, operands resident in
     shared memory) on every SM: the tensor-pipe ceiling for one operand format. ``pair``:
-    CTA pairs issuing ``cta_group::2`` instructions of 256 x n instead."""
+    CTA pairs issuing ``cta_group::2`` instructions of 256 x n instead. ``cps_main`` /
+    ``cps_side``: scale-tile copies per iteration of four MMAs issued by the MMA thread / by a
+    second thread (NVFP4, single CTA)."""
     out = C.c_double(0.0)
-    ctx.check(ctx._lib.qs3_tensor_peak_probe(ctx.handle, PEAK_KINDS[kind] + (16 if pair else 0), n, iters,
-                                             C.byref(out)))
+    code = PEAK_KINDS[kind] + (16 if pair else 0) + 256 * cps_main + 4096 * cps_side
+    ctx.check(ctx._lib.qs3_tensor_peak_probe(ctx.handle, code, n, iters, C.byref(out)))
     return float(out.value)
 
 

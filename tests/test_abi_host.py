@@ -306,3 +306,16 @@ def test_header_compiles_as_c_and_cpp(tmp_path):
         r = subprocess.run([exe, *flags, "-Wall", "-Wextra", "-Werror", "-fsyntax-only",
                             "-I", os.path.join(root, "include"), str(src)], capture_output=True, text=True)
         assert r.returncode == 0, r.stderr
+
+
+def test_reference_arm_layer_shapes_equal_the_workload_constants():
+    """bench.py's reference arm imports neither torch nor the package, so it carries its own copy of
+    the benchmark layer shapes; they must stay equal to qs3_b200.workload's."""
+    import bench
+    from qs3_b200 import workload
+    ref = bench._RefConfigs.make()
+    for name in ("PREFILL_NVFP4", "EP_NVFP4", "DECODE_NVFP4", "DECODE_FP8"):
+        a, b = getattr(ref, name), getattr(workload, name)
+        for field in ("name", "tokens", "hidden", "experts", "top_k", "inter", "shared_inter", "nvfp4", "zipf_s",
+                      "fp8", "dtype_name"):
+            assert getattr(a, field) == getattr(b, field), (name, field)

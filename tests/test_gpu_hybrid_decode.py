@@ -35,7 +35,10 @@ def test_moe_blocks_match_oracle_and_graph_matches_eager(oracle):
         blk = model.blocks[layer]
         normed = to_np(tr["normed"])
         ids, w = to_np(tr["ids"]), to_np(tr["weights"])
-        assert ids.min() >= 0 and ids.max() < cfg.experts
+        # the routing of the traced step is the oracle's routing of the traced logits, bit for bit
+        ids_ref, w_ref = oracle.router_topk(to_np(tr["logits"]), cfg.top_k, 0, True, 1.0)
+        assert np.array_equal(ids, ids_ref)
+        assert np.allclose(w, w_ref, atol=1e-5, rtol=0)
         hp, hs = oracle.nvfp4_quantize_act(normed, 1.0)
         moe = oracle.moe_nvfp4(hp, hs, ids, w, _triple(blk.gate_up), _triple(blk.down),
                                shared=dict(gu=_triple(blk.shared.gate_up), d=_triple(blk.shared.down),

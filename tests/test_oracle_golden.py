@@ -130,6 +130,62 @@ def test_fp4_fp8_codecs(oracle):
     assert lib.qs3o_f32_to_e4m3(1.5 * 2.0 ** -9) == 2  # tie -> even
 
 
+def test_e4m3_codec_against_torch_float8(oracle):
+    """The oracle's e4m3 codec pinned to an implementation outside this repository:
+    torch.float8_e4m3fn decodes all 256 codes to the same values (the two NaN codes aside) and
+    rounds a dense sweep of floats, every midpoint between neighbouring e4m3 values included
+    (ties to even), to the same codes. Above 448 the oracle saturates (its quantisers never
+    produce NaN) where torch's cast does not, so the sweep stops at 448."""
+    import torch
+    lib = oracle.lib()
+    codes = np.arange(256, dtype=np.uint8)
+    want = torch.from_numpy(codes).view(torch.float8_e4m3fn).to(torch.float32).numpy()
+    got = oracle.e4m3_to_f32(codes)
+    finite = ~np.isnan(want)
+    assert finite.sum() == 254 and np.array_equal(got[finite], want[finite])
+    pos = np.sort(want[finite & (want >= 0)])
+    mids = (pos[:-1] + pos[1:]) / 2.0
+    rng = np.random.default_rng(11)
+    sweep = np.concatenate([pos, mids, np.nextafter(mids, np.float32(0)), np.nextafter(mids, np.float32(1e9)),
+                            np.exp(rng.uniform(np.log(2.0 ** -11), np.log(448.0), 20000)),
+                            rng.uniform(0.0, 448.0, 5000)]).astype(np.float32)
+    sweep = np.concatenate([sweep, -sweep])
+    t_codes = torch.from_numpy(sweep).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    o_codes = np.array([lib.qs3o_f32_to_e4m3(float(v)) for v in sweep], dtype=np.uint8)
+    # -0.0 and +0.0 encode alike up to the sign bit in both
+    assert np.array_equal(o_codes & 0x7F, t_codes & 0x7F)
+    nz = (o_codes & 0x7F) != 0
+    assert np.array_equal(o_codes[nz], t_codes[nz])
+
+
+def test_e2m1_codec_against_the_published_value_set(oracle):
+    """e2m1 (OCP microscaling FP4: 1 sign, 2 exponent, 1 mantissa bit, bias 1, no inf / NaN):
+    the sixteen values are +-{0, 0.5, 1, 1.5, 2, 3, 4, 6}, computed here from the bit fields of
+    the format definition rather than from the oracle's table; encoding rounds to nearest with
+    ties to the even mantissa and saturates at 6."""
+    lib = oracle.lib()
+
+    def decode(c):
+        sign = -1.0 if c & 8 else 1.0
+        exp, man = (c >> 1) & 3, c & 1
+        return sign * (man * 0.5 if exp == 0 else (1.0 + 0.5 * man) * 2.0 ** (exp - 1))
+
+    values = [decode(c) for c in range(16)]
+    assert sorted(set(abs(v) for v in values)) == [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+    for c in range(16):
+        assert lib.qs3o_e2m1_to_f32(c) == values[c]
+    pos = values[:8]
+    rng = np.random.default_rng(12)
+    sweep = np.concatenate([rng.uniform(0, 8, 4000), [(a + b) / 2 for a, b in zip(pos[:-1], pos[1:])]])
+    for v in sweep:
+        d = [abs(v - p) for p in pos]
+        best = min(d)
+        ties = [i for i, x in enumerate(d) if x == best]
+        want = ties[0] if len(ties) == 1 else [i for i in ties if i % 2 == 0][0]   # even mantissa bit
+        assert lib.qs3o_f32_to_e2m1(float(np.float32(v))) == want
+        assert lib.qs3o_f32_to_e2m1(-float(np.float32(v))) == want | 8
+
+
 def test_nvfp4_quantise_round_trip(oracle):
     rng = np.random.default_rng(5)
     x = bf16(rng.standard_normal((8, 64), dtype=np.float32))
