@@ -97,6 +97,13 @@ struct RouteTables {
     int32_t* tile_row0;    // [max_tiles] first padded row of the tile
     int32_t* tile_nrows;   // [max_tiles] valid rows in the tile
     int32_t* total_tiles;  // [1]
+    // 256-row "pair tiles" for the CTA-pair GEMM (128-row plans only, NULL otherwise): an expert with t
+    // row tiles gives t / 2 full pairs, listed from index 0 upwards, and t % 2 single (<= 128 rows),
+    // listed from index max_tiles - 1 downwards; pair_counts = {full pairs, singles}
+    int32_t* pair_expert;  // [max_tiles]
+    int32_t* pair_row0;    // [max_tiles] first padded row
+    int32_t* pair_nrows;   // [max_tiles] valid rows, 1..256
+    int32_t* pair_counts;  // [2]
     int32_t* block_hist;   // [route_blocks * E] scratch of the counting sort
     uint32_t max_tiles;
     uint32_t max_pad_rows;
@@ -203,6 +210,11 @@ struct GemmProblem {
     uint32_t max_tiles;
     uint32_t tile_rows;  // rows per tile of the tables: 128, or 32 (NVFP4 decode kernel, operands swapped)
     uint32_t est_tiles;  // expected number of tiles (sizes the splits of the decode kernel), 0: unknown
+    // pair tiles of the route sort (RouteTables::pair_*), NULL: no CTA-pair kernel for this problem
+    const int32_t* pair_expert;
+    const int32_t* pair_row0;
+    const int32_t* pair_nrows;
+    const int32_t* pair_counts;
     // output
     void* out;
     uint64_t out_pitch_elems;   // elements (bytes for packed NVFP4 output)
@@ -220,6 +232,9 @@ cudaError_t launch_gemm(const GemmProblem& p, cudaStream_t stream, const char** 
 // Persistent 128 x 256 kernel for dense bf16 problems with more than 64 rows (gemm_dense.cu).
 bool gemm_dense_bf16_supported(const GemmProblem& p);
 cudaError_t launch_gemm_dense_bf16(const GemmProblem& p, cudaStream_t stream, const char** why_unsupported);
+// NVFP4 GEMM on CTA pairs (256 x 256 instructions, weights cross L2 -> SM once per 256 rows; gemm_pair.cu).
+bool nvfp4_pair_gemm_supported(const GemmProblem& p);
+cudaError_t launch_nvfp4_pair_gemm(const GemmProblem& p, cudaStream_t stream, const char** why_unsupported);
 // NVFP4 grouped GEMM for 32-row token tiles (decode batches): weights are the M side of the MMA.
 cudaError_t launch_nvfp4_swap_gemm(const GemmProblem& p, cudaStream_t stream, const char** why_unsupported);
 // Rows per token tile of an NVFP4 plan: 32 (decode kernel) when experts get few rows each, else 128.

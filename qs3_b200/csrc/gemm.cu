@@ -28,6 +28,7 @@
 #include "tcgen05.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 namespace qs3 {
@@ -690,6 +691,15 @@ uint32_t sm_count()
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+bool pair_down_enabled()
+{
+    static const bool enabled = [] {
+        const char* v = std::getenv("QS3_NVFP4_PAIR_DOWN");
+        return v != nullptr && v[0] == '1';
+    }();
+    return enabled;
+}
+
 // ---- skinny bf16 GEMM for decode-sized batches ------------------------------------------------
 //
 // out[t, n] = sum_k A[t, k] * B[n, k] for a handful of rows (router logits of a decode batch):
@@ -804,6 +814,21 @@ bool make_operand_map(CUtensorMap* map, bool bytes_type, const void* base, uint6
 
 uint32_t device_sm_count() { return sm_count(); }
 
+bool make_scale_tile_map(CUtensorMap* map, const void* base, uint64_t tiles, uint32_t box_tiles)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr || tiles == 0 || box_tiles == 0 || box_tiles > 256)
+        return false;
+    const cuuint64_t dims[2] = { 128, tiles };          // 128 x u32 = one 512-byte tile per row
+    const cuuint64_t strides[1] = { 512 };
+    const cuuint32_t box[2] = { 128, box_tiles };
+    const cuuint32_t estr[2] = { 1, 1 };
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+        == CUDA_SUCCESS;
+}
+
 bool gemm_tc_supported(const GemmProblem& g)
 {
     if (!aligned16(g.a) || !aligned16(g.b) || g.a_pitch_bytes % 16 != 0 || g.b_pitch_bytes % 16 != 0)
@@ -813,6 +838,53 @@ bool gemm_tc_supported(const GemmProblem& g)
         return g.k % 256 == 0 && g.n % 64 == 0 && (g.gated || g.n % 128 == 0);
     }
     return g.k % 8 == 0;
+}
+
+bool make_scale_block_map(CUtensorMap* map, const void* base, uint64_t row_blocks, uint32_t kgroups)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr || row_blocks == 0 || kgroups < 4)
+        return false;
+    const cuuint64_t dims[3] = { 128, kgroups, row_blocks };
+    const cuuint64_t strides[2] = { 512, static_cast<cuuint64_t>(kgroups) * 512 };
+    const cuuint32_t box[3] = { 128, 4, 2 };
+    const cuuint32_t estr[3] = { 1, 1, 1 };
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+        == CUDA_SUCCESS;
+}
+
+bool make_gated_weight_map(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t inter,
+                           uint64_t groups, uint64_t pitch_bytes)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr || inter < 64 || groups == 0)
+        return false;
+    const cuuint64_t dims[3] = { inner_bytes, inter, 2 * groups };
+    const cuuint64_t strides[2] = { pitch_bytes, inter * pitch_bytes };
+    const cuuint32_t box[3] = { 128, 64, 2 };
+    const cuuint32_t estr[3] = { 1, 1, 1 };
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+        == CUDA_SUCCESS;
+}
+
+// CTA-pair kernel: grouped problems with pair tiles from the route sort, and dense problems with
+// enough 256-row tiles to be worth pairing. QS3_NVFP4_PAIR=0 in the environment keeps the
+// single-CTA kernels (for A/B measurements).
+static bool pair_kernel_wanted(const GemmProblem& g)
+{
+    static const bool enabled = [] {
+        const char* v = std::getenv("QS3_NVFP4_PAIR");
+        return v == nullptr || v[0] != '0';
+    }();
+    if (!enabled || !nvfp4_pair_gemm_supported(g))
+        return false;
+    if (g.tile_expert != nullptr)
+        return g.gated != 0 || pair_down_enabled();
+    return g.a_rows >= 1024 && (g.gated != 0 || pair_down_enabled());
 }
 
 cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** why)
@@ -836,6 +908,8 @@ cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** 
         return launch_skinny(g, stream);
     if (gemm_dense_bf16_supported(g))
         return launch_gemm_dense_bf16(g, stream, why);
+    if (pair_kernel_wanted(g))
+        return launch_nvfp4_pair_gemm(g, stream, why);
     if (gemm_tc_supported(g)) {
         const uint32_t feat = g.gated ? kBN / 2 : kBN;
         dim3 grid((g.n + feat - 1) / feat, m_tiles, 1);

@@ -308,6 +308,10 @@ GemmProblem grouped_problem(const RouteTables& rt, uint32_t groups)
     g.total_tiles = rt.total_tiles;
     g.max_tiles = rt.max_tiles;
     g.tile_rows = rt.tile_rows;
+    g.pair_expert = rt.pair_expert;
+    g.pair_row0 = rt.pair_row0;
+    g.pair_nrows = rt.pair_nrows;
+    g.pair_counts = rt.pair_counts;
     return g;
 }
 

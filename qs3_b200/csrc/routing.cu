@@ -76,10 +76,11 @@ route_hist_kernel(const int32_t* __restrict__ ids, uint32_t routes, uint32_t loc
 __device__ __forceinline__ void route_scan_body(int32_t* __restrict__ block_hist, uint32_t num_blocks,
                                                 uint32_t experts, const RouteTables& rt)
 {
-    __shared__ int s_warp[3][32];
-    __shared__ int s_carry[3];
+    constexpr int kScans = 5; // counts, padded counts, tiles, full pair tiles, single tiles
+    __shared__ int s_warp[kScans][32];
+    __shared__ int s_carry[kScans];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x < 3)
+    if (threadIdx.x < kScans)
         s_carry[threadIdx.x] = 0;
     __syncthreads();
     for (uint32_t e0 = 0; e0 < experts; e0 += blockDim.x) {
@@ -106,10 +107,11 @@ __device__ __forceinline__ void route_scan_body(int32_t* __restrict__ block_hist
         }
         const int tile_rows = static_cast<int>(rt.tile_rows);
         const int tiles = (count + tile_rows - 1) / tile_rows;
-        int v[3] = { count, tiles * tile_rows, tiles };
-        int incl[3];
+        const bool pairing = rt.pair_expert != nullptr;
+        int v[kScans] = { count, tiles * tile_rows, tiles, pairing ? tiles >> 1 : 0, pairing ? tiles & 1 : 0 };
+        int incl[kScans];
 #pragma unroll
-        for (int j = 0; j < 3; ++j) {
+        for (int j = 0; j < kScans; ++j) {
             int x = v[j];
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -126,7 +128,7 @@ __device__ __forceinline__ void route_scan_body(int32_t* __restrict__ block_hist
         __syncthreads();
         if (warp == 0) {
 #pragma unroll
-            for (int j = 0; j < 3; ++j) {
+            for (int j = 0; j < kScans; ++j) {
                 int x = s_warp[j][lane];
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
@@ -138,9 +140,9 @@ __device__ __forceinline__ void route_scan_body(int32_t* __restrict__ block_hist
             }
         }
         __syncthreads();
-        int excl[3];
+        int excl[kScans];
 #pragma unroll
-        for (int j = 0; j < 3; ++j)
+        for (int j = 0; j < kScans; ++j)
             excl[j] = s_carry[j] + (warp > 0 ? s_warp[j][warp - 1] : 0) + incl[j] - v[j];
         if (e < experts) {
             rt.indptr[e] = excl[0];
@@ -150,11 +152,24 @@ __device__ __forceinline__ void route_scan_body(int32_t* __restrict__ block_hist
                 rt.tile_row0[excl[2] + m] = excl[1] + m * tile_rows;
                 rt.tile_nrows[excl[2] + m] = min(tile_rows, count - m * tile_rows);
             }
+            if (pairing) {
+                for (int m = 0; m < (tiles >> 1); ++m) {
+                    rt.pair_expert[excl[3] + m] = static_cast<int32_t>(e);
+                    rt.pair_row0[excl[3] + m] = excl[1] + m * 2 * tile_rows;
+                    rt.pair_nrows[excl[3] + m] = min(2 * tile_rows, count - m * 2 * tile_rows);
+                }
+                if (tiles & 1) {
+                    const int at = static_cast<int>(rt.max_tiles) - 1 - excl[4];
+                    rt.pair_expert[at] = static_cast<int32_t>(e);
+                    rt.pair_row0[at] = excl[1] + (tiles - 1) * tile_rows;
+                    rt.pair_nrows[at] = count - (tiles - 1) * tile_rows;
+                }
+            }
         }
         __syncthreads();
         if (threadIdx.x == 0) {
 #pragma unroll
-            for (int j = 0; j < 3; ++j)
+            for (int j = 0; j < kScans; ++j)
                 s_carry[j] += s_warp[j][31];
         }
         __syncthreads();
@@ -163,6 +178,10 @@ __device__ __forceinline__ void route_scan_body(int32_t* __restrict__ block_hist
         rt.indptr[experts] = s_carry[0];
         rt.pad_indptr[experts] = s_carry[1];
         *rt.total_tiles = s_carry[2];
+        if (rt.pair_counts != nullptr) {
+            rt.pair_counts[0] = s_carry[3];
+            rt.pair_counts[1] = s_carry[4];
+        }
     }
 }
 
@@ -808,6 +827,12 @@ size_t route_tables_carve(char* base, uint32_t routes, uint32_t experts, RouteTa
     rt.tile_row0 = carve<int32_t>(base, off, rt.max_tiles);
     rt.tile_nrows = carve<int32_t>(base, off, rt.max_tiles);
     rt.total_tiles = carve<int32_t>(base, off, 1);
+    if (tile_rows == static_cast<uint32_t>(kTileM)) {
+        rt.pair_expert = carve<int32_t>(base, off, rt.max_tiles);
+        rt.pair_row0 = carve<int32_t>(base, off, rt.max_tiles);
+        rt.pair_nrows = carve<int32_t>(base, off, rt.max_tiles);
+        rt.pair_counts = carve<int32_t>(base, off, 2);
+    }
     rt.block_hist = carve<int32_t>(base, off, static_cast<size_t>(rt.route_blocks) * experts);
     if (out != nullptr)
         *out = rt;
