@@ -211,7 +211,7 @@ def _workload(args, module=None):
     return module.EP_NVFP4
 
 
-def _config(cfg, world, placement="balanced"):
+def _config(cfg, world, placement="balanced", hot=0):
     """The `config` object of the JSON line, identical for both arms."""
     weights_gb = cfg.experts * 3 * cfg.inter * cfg.hidden * (0.5625 if cfg.nvfp4 else 1.0 if cfg.fp8 else 2.0) / 1e9
     return {"workload": cfg.name, "tokens_per_gpu": cfg.tokens, "hidden": cfg.hidden, "experts": cfg.experts,
@@ -219,7 +219,9 @@ def _config(cfg, world, placement="balanced"):
             "router_bias": f"zipf(s={cfg.zipf_s})", "parallelism": "single" if world == 1 else f"ep{world}",
             "expert_placement": "all local" if world == 1 else
             ("contiguous blocks of expert ids" if placement == "contiguous" else
-             "even counts per rank, load-balanced on a calibration batch (longest-processing-time rule)"),
+             "even counts per rank, load-balanced on a calibration batch (longest-processing-time rule)"
+             + (f"; the {hot} hottest experts of that batch are also replicated on every rank, so their routes "
+                "are served where the token lives" if hot else "")),
             "l2_policy": f"inputs_exceed_l2 (expert weights ~{weights_gb:.1f} GB per pass)"}
 
 
@@ -266,7 +268,7 @@ def run_reference(args, rank, world):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1000.0 * dt, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": cfg.dtype_name, "data": "synthetic",
-        "config": _config(cfg, args.gpus, args.placement),
+        "config": _config(cfg, args.gpus, args.placement, 0 if args.gpus == 1 else args.hot_experts),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": f"{n} tokens per step (a prefix of the batch, or the batch repeated), whole layer "
                                    f"on the CPU oracle; inputs generated on the host, {hit} experts hit"},
@@ -336,7 +338,8 @@ def run_ours(args, rank, world, local_rank):
         cfg = workload.EP_NVFP4
         per = cfg.experts // world
         data = workload.LayerData(cfg, ctx, seed=0, expert_range=(rank * per, per), token_seed=rank + 1,
-                                  balance_world=0 if args.placement == "contiguous" else world)
+                                  balance_world=0 if args.placement == "contiguous" else world,
+                                  hot_experts=0 if args.placement == "contiguous" else args.hot_experts)
         layer = ep.ExpertParallelLayer(ctx, data, rank, world)
 
     def barrier():
@@ -423,7 +426,7 @@ def run_ours(args, rank, world, local_rank):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": block_med / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg.dtype_name,
         "data": "synthetic",
-        "config": _config(cfg, world, args.placement),
+        "config": _config(cfg, world, args.placement, 0 if world == 1 else args.hot_experts),
         "timing": {"blocks": len(blocks_ms), "steps_per_block": args.steps, "block_ms_median": block_med,
                    "block_ms_p10": block_p10, "block_ms_p90": block_p90, "timed_region_ms": total_ms,
                    "ms_per_step_p10": block_p10 / args.steps, "ms_per_step_p90": block_p90 / args.steps,
@@ -771,6 +774,8 @@ def main():
                          "batch of the NVFP4 layer instead of the headline layer")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="N > 1: how the experts are assigned to ranks")
+    ap.add_argument("--hot-experts", type=int, default=16,
+                    help="N > 1, balanced placement: replicate this many of the hottest experts on every rank")
     ap.add_argument("--no-graph", action="store_true",
                     help="N = 1: launch the resident-input steps eagerly instead of replaying one CUDA graph "
                          "(the e2e leg is always eager)")

@@ -519,6 +519,15 @@ typedef struct {
     float routed_scaling_factor;
     float act_global_scale;      /* 0 means 1 */
     uint32_t num_tokens;
+    /* Optional: placements with replicated experts. The plan then counts expert SLOTS (every rank
+       holds its own experts plus replicas of the hottest ones: num_experts = ranks * slots per rank)
+       while the router still scores the model's experts: router_weight / router_bias /
+       router_logits have expert_id_map.shape[0] rows / entries / columns instead of
+       plan.num_experts, topk_ids receives the router's expert ids, and dispatch_ids[t, k] =
+       expert_id_map[topk_ids[t, k]] the slot each route goes to (on this rank: a hot expert maps
+       to this rank's own replica). dispatch_ids is what the other phases take as topk_ids. */
+    qsfi_tensor1 expert_id_map;  /* in:  optional i32 [router experts] */
+    qsfi_tensor2 dispatch_ids;   /* out: with expert_id_map: i32 [num_tokens, top_k] */
 } qs3_moe_ep_route_desc;
 qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_ep_route_desc* desc);
 

@@ -168,7 +168,8 @@ class MoeEpRouteDesc(C.Structure):
                 ("router_logits", Tensor2), ("topk_ids", Tensor2), ("topk_weights", Tensor2),
                 ("hidden_packed", Tensor2), ("hidden_scale", Tensor2), ("score", C.c_int),
                 ("renormalize", C.c_uint32), ("routed_scaling_factor", C.c_float),
-                ("act_global_scale", C.c_float), ("num_tokens", C.c_uint32)]
+                ("act_global_scale", C.c_float), ("num_tokens", C.c_uint32),
+                ("expert_id_map", Tensor1), ("dispatch_ids", Tensor2)]
 
 
 class MoeNvfp4PreparedDesc(C.Structure):

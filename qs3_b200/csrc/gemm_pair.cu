@@ -31,8 +31,8 @@
 // has no rows; it still provides its half of the weights.
 //
 //   warps 0-7  epilogue (two per tensor-memory lane quadrant: columns [0,128) / [128,256))
-//   warp 8     TMA producer of the weight ring     warp 11  TMA producer of the A panels
-//   warp 9     MMA issuer (first CTA)              warp 10  scale copier (first CTA)
+//   warp 8     TMA producer (weight ring and A panels)
+//   warp 9     MMA issuer (first CTA)     warps 10, 11  scale copiers (first CTA)
 //
 //   TMEM  [0,256) accumulator | [256,384) A scales (k/64 x 4 columns) | [384,512) four buffers of
 //         B scales (8 columns per 64 k elements, 32 per k block)
@@ -67,7 +67,6 @@ enum : uint32_t {
     ERR_PG_PANEL_FULL = 0x54000002u,
     ERR_PG_EMPTY = 0x54000003u,
     ERR_PG_FULL = 0x54000004u,
-    ERR_PG_SF_FREE = 0x54000005u,
     ERR_PG_SF_READY = 0x54000006u,
     ERR_PG_SFA_READY = 0x54000007u,
     ERR_PG_ACC_EMPTY = 0x54000008u,
@@ -80,6 +79,17 @@ constexpr uint32_t kTraceStages = 192;
 constexpr uint32_t kTraceEvents = 4;
 constexpr uint32_t kTraceRoles = 4; // 0 producer, 1 scale copier, 2 MMA issuer, 3 epilogue warp 0 (per column tile)
 __device__ unsigned long long g_pair_trace[kTraceRoles * kTraceStages * kTraceEvents];
+// ... and every cluster's MMA thread the global timer (ns) when it starts and when it has issued its last
+// unit, and how many units it took: [cluster][start, end, units]
+constexpr uint32_t kTraceClusters = 128;
+__device__ unsigned long long g_pair_spans[kTraceClusters * 3];
+
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ void trace(bool on, uint32_t role, uint32_t stage, uint32_t event)
 {
@@ -97,6 +107,7 @@ struct PairParams {
     uint32_t stages;
     uint32_t sfa_tiles_per_block; // 512-byte A-scale tiles per 128 rows (= k / 64)
     uint32_t sfb_tiles_per_group; // 512-byte B-scale tiles per expert
+    uint32_t force_splits;        // measurement only (QS3_PAIR_SPLITS): work units per pair tile, 0 = automatic
     uint32_t dbg;                 // measurement only (QS3_PAIR_DBG): 1 no epilogue arithmetic / stores,
                                   // 2 no accumulator drain either, 4 no MMAs, 8 no weight-scale copies,
                                   // 16 no L2 prefetch, 32 record the stage trace (qs3_debug_pair_trace)
@@ -162,6 +173,17 @@ __device__ __forceinline__ void commit_pair(uint32_t bar_cluster_addr)
                  : "memory");
 }
 
+// One commit that arrives on the barrier at the same shared-memory offset in BOTH CTAs of the pair
+// (the multicast here is of the barrier arrival, not of a load): the issuing thread pays 50-100
+// cycles per tcgen05 instruction, so one commit instead of two per ring stage matters.
+__device__ __forceinline__ void commit_both(const void* local_bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::
+                     "r"(smem_u32(local_bar)),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+
 __device__ __forceinline__ void cp_scales_pair(uint32_t taddr, uint64_t sdesc)
 {
     asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
@@ -205,24 +227,68 @@ struct Unit {
     uint32_t nt_begin, nt_end;
 };
 
-// Work units per pair tile: the column tiles of a pair tile are split over 2 or 4 units when there
-// are too few pair tiles to keep every cluster busy for several rounds (a split unit reloads the
-// A panel, so no more than needed). Every thread derives the same value from the device-side counts.
-__device__ __forceinline__ uint32_t unit_splits(uint32_t pair_tiles, uint32_t n_tiles, uint32_t clusters)
+// Work units. A unit is a pair tile with a range of its column tiles; clusters take units u = cluster,
+// cluster + clusters, ... Every thread derives the same schedule from the device-side tile counts:
+//   * few pair tiles (less than four rounds of whole tiles): every tile is split into `splits` units
+//     (2 or 4), so that all clusters have work;
+//   * otherwise whole tiles, except the tiles of the last, partial round, which are split `tail_splits`
+//     ways when that shortens the tail (22 left-over tiles on 74 clusters: one half-round of
+//     half-tiles instead of one round of whole tiles). A split unit reloads its A panel.
+struct Sched {
+    uint32_t n_tiles;      // column tiles of a pair tile
+    uint32_t whole;        // leading tiles taken whole (or every tile, `splits` ways)
+    uint32_t splits;       // units per tile among the first `whole` tiles
+    uint32_t tail_splits;  // units per tile after them
+    uint32_t total_units;
+};
+
+__device__ __forceinline__ Sched make_sched(uint32_t pair_tiles, uint32_t n_tiles, uint32_t clusters, uint32_t force)
 {
-    uint32_t splits = 1;
-    while (splits * 2 <= n_tiles && n_tiles % (splits * 2) == 0 && pair_tiles * splits < 4 * clusters)
-        splits *= 2;
-    return splits;
+    Sched sc;
+    sc.n_tiles = n_tiles;
+    sc.splits = 1;
+    sc.tail_splits = 1;
+    sc.whole = pair_tiles;
+    if (force != 0) {
+        sc.splits = force;
+    } else if (pair_tiles < 4 * clusters) {
+        while (sc.splits * 2 <= n_tiles && n_tiles % (sc.splits * 2) == 0 && pair_tiles * sc.splits < 4 * clusters)
+            sc.splits *= 2;
+    } else {
+        const uint32_t rest = pair_tiles % clusters;
+        sc.whole = pair_tiles - rest;
+        // cost of the tail in sixteenths of a whole-tile round, plus one sixteenth per reload of the panel
+        uint32_t best = 0xffffffffu;
+        for (uint32_t ts = 1; ts <= 4 && ts <= n_tiles && rest != 0; ts *= 2) {
+            if (n_tiles % ts != 0)
+                continue;
+            const uint32_t cost = (rest * ts + clusters - 1) / clusters * (16 / ts) + (ts - 1);
+            if (cost < best) {
+                best = cost;
+                sc.tail_splits = ts;
+            }
+        }
+    }
+    sc.total_units = sc.whole * sc.splits + (pair_tiles - sc.whole) * sc.tail_splits;
+    return sc;
 }
 
-__device__ __forceinline__ bool load_unit(const PairParams& p, uint32_t u, uint32_t total_units, uint32_t n_tiles,
-                                          uint32_t splits, Unit* out)
+__device__ __forceinline__ bool load_unit(const PairParams& p, uint32_t u, const Sched& sc, Unit* out)
 {
-    if (u >= total_units)
+    if (u >= sc.total_units)
         return false;
-    const uint32_t tile = u / splits, split = u % splits;
-    const uint32_t nt_per_unit = n_tiles / splits;
+    uint32_t tile, split, parts;
+    if (u < sc.whole * sc.splits) {
+        parts = sc.splits;
+        tile = u / parts;
+        split = u % parts;
+    } else {
+        parts = sc.tail_splits;
+        const uint32_t v = u - sc.whole * sc.splits;
+        tile = sc.whole + v / parts;
+        split = v % parts;
+    }
+    const uint32_t nt_per_unit = sc.n_tiles / parts;
     if (p.pair_expert != nullptr) {
         const uint32_t full = static_cast<uint32_t>(p.pair_counts[0]);
         const uint32_t idx = tile < full ? tile : p.pair_cap - 1 - (tile - full);
@@ -298,7 +364,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
-            mbar_init(&sf_ready[s], 1);
+            mbar_init(&sf_ready[s], 2); // the two scale copiers
         }
         for (uint32_t kb = 0; kb < kb_count; ++kb) {
             mbar_init(&panel_full[kb], 1);
@@ -332,18 +398,65 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         : (p.dense_rows + 255) / 256;
     const uint32_t cluster_id = blockIdx.x >> 1, clusters = gridDim.x >> 1;
     const bool tr = (pp.dbg & 32u) != 0 && blockIdx.x == 0;
-    const uint32_t splits = unit_splits(pair_tiles, n_tiles, clusters);
-    const uint32_t total_units = pair_tiles * splits;
+    const Sched sc = make_sched(pair_tiles, n_tiles, clusters, pp.force_splits);
+    const uint32_t total_units = sc.total_units;
 
     if (warp == 8) {
-        // ----------------------------------------------- producer: weight ring --
-        // Runs ahead of the panel loader across unit boundaries: the ring does not depend on the panel.
+        // ------------------------------------------------------------ producer --
+        // One thread feeds two streams. The weight ring runs ahead across unit boundaries (it does not
+        // depend on the panel). The A panels go k block by k block: block kb of the next unit's panel is
+        // loaded as soon as the last column tile of the current unit is done with block kb, so a panel
+        // trails the previous unit's last column tile by one k block instead of waiting for its end. The
+        // panel stream is polled, never waited for, so that it cannot hold up the ring.
         if (lane == 0) {
+            uint32_t p_unit = cluster_id, p_no = 0, p_kb = 0;
+            Unit pu;
+            bool p_have = load_unit(pp, p_unit, sc, &pu);
+            const auto pump_panel = [&]() {
+                while (p_have && mbar_test_wait(&panel_free[p_kb], (p_no & 1) ^ 1)) {
+                    const int my_row0 = pu.row0 + static_cast<int>(rank * 128);
+                    if (rank == 0)
+                        mbar_expect_tx(&panel_full[p_kb], (pu.nrows > 128 ? 2u : 1u) * (kTileBytes + kSfBytes));
+                    if (pu.nrows > static_cast<int>(rank * 128)) {
+                        const uint32_t pbar = cluster_addr(&panel_full[p_kb], 0);
+                        tma_load_pair(a_panel + p_kb * kTileBytes, &map_a, pbar, static_cast<int>(p_kb) * 128, my_row0);
+                        tma_load_pair(sfa_stage + p_kb * kSfBytes, &map_sfa, pbar, 0,
+                                      static_cast<int>((my_row0 >> 7) * pp.sfa_tiles_per_block + 4 * p_kb));
+                    }
+                    if (++p_kb == kb_count) {
+                        p_kb = 0;
+                        ++p_no;
+                        p_unit += clusters;
+                        p_have = load_unit(pp, p_unit, sc, &pu);
+                    }
+                }
+            };
+            // bounded wait for a ring slot that keeps the panel stream going
+            const auto wait_slot = [&](uint64_t* bar, uint32_t parity) -> bool {
+                if (mbar_test_wait(bar, parity))
+                    return true;
+                const uint64_t start = clock64();
+                uint32_t spins = 0;
+                while (!mbar_test_wait(bar, parity)) {
+                    pump_panel();
+                    if ((++spins & 15u) != 0)
+                        continue;
+                    if (*abort_flag != 0)
+                        return false;
+                    if (static_cast<uint64_t>(clock64()) - start > kWaitCycles) {
+                        *abort_flag = 1;
+                        atomicCAS(p.err, 0u, static_cast<uint32_t>(ERR_PG_EMPTY));
+                        return false;
+                    }
+                }
+                return true;
+            };
             uint32_t s = 0, ph = 0, tsi = 0;
             bool ok = true;
             Unit un, next;
-            for (uint32_t u = cluster_id; ok && load_unit(pp, u, total_units, n_tiles, splits, &un); u += clusters) {
-                const bool have_next = load_unit(pp, u + clusters, total_units, n_tiles, splits, &next);
+            pump_panel();
+            for (uint32_t u = cluster_id; ok && load_unit(pp, u, sc, &un); u += clusters) {
+                const bool have_next = load_unit(pp, u + clusters, sc, &next);
                 for (uint32_t nt = un.nt_begin; ok && nt < un.nt_end; ++nt) {
                     // What this CTA streams for column tile nt: 128 of the tile's 256 weight rows
                     // ("interleaved tile" 2 nt + rank: for gated problems 64 gate rows and their 64 up rows, one
@@ -359,7 +472,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     else
                         pf = false;
                     for (uint32_t kb = 0; kb < kb_count; ++kb) {
-                        if (!mbar_wait<true>(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_PG_EMPTY)) {
+                        if (!wait_slot(&empty_bar[s], ph ^ 1)) {
                             ok = false;
                             break;
                         }
@@ -382,6 +495,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                             tma_prefetch_3d(&map_sfb, 0, static_cast<int>(4 * kb), ahead.sf2);
                         }
                         trace(tr, 0, tsi++, 1);
+                        pump_panel();
                         if (++s == stages) {
                             s = 0;
                             ph ^= 1;
@@ -391,30 +505,33 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             }
         }
     } else if (warp == 11) {
-        // ------------------------------------------------ producer: A panels --
-        // k block by k block: block kb of the next unit's panel is loaded as soon as the last column
-        // tile of the current unit is done with block kb, so a unit's panel trails the previous unit's
-        // last column tile by one k block instead of waiting for its end.
-        if (lane == 0) {
-            uint32_t unit_no = 0;
+        // ------------------------------------------- second scale copier --
+        // tcgen05.cp costs its issuing thread 50-70 cycles apiece; the eight copies of a stage's B scales
+        // (plus four of A scales in a unit's first column tile) from one thread take longer than the
+        // stage's four MMAs, so the two 128-row halves of the B scales have a copier thread each.
+        if (rank == 0 && lane == 0) {
+            uint32_t s = 0, ph = 0;
             bool ok = true;
             Unit un;
-            for (uint32_t u = cluster_id; ok && load_unit(pp, u, total_units, n_tiles, splits, &un); u += clusters, ++unit_no) {
-                const bool mine = un.nrows > static_cast<int>(rank * 128);
-                const int my_row0 = un.row0 + static_cast<int>(rank * 128);
-                const uint32_t kb_bytes = (un.nrows > 128 ? 2u : 1u) * (kTileBytes + kSfBytes);
-                for (uint32_t kb = 0; kb < kb_count; ++kb) {
-                    if (!mbar_wait<true>(&panel_free[kb], (unit_no & 1) ^ 1, abort_flag, p.err, ERR_PG_PANEL_FREE)) {
-                        ok = false;
-                        break;
-                    }
-                    if (rank == 0)
-                        mbar_expect_tx(&panel_full[kb], kb_bytes);
-                    if (mine) {
-                        const uint32_t pbar = cluster_addr(&panel_full[kb], 0);
-                        tma_load_pair(a_panel + kb * kTileBytes, &map_a, pbar, static_cast<int>(kb) * 128, my_row0);
-                        tma_load_pair(sfa_stage + kb * kSfBytes, &map_sfa, pbar, 0,
-                                      static_cast<int>((my_row0 >> 7) * pp.sfa_tiles_per_block + 4 * kb));
+            for (uint32_t u = cluster_id; ok && load_unit(pp, u, sc, &un); u += clusters) {
+                for (uint32_t nt = un.nt_begin; ok && nt < un.nt_end; ++nt) {
+                    for (uint32_t kb = 0; kb < kb_count; ++kb) {
+                        if (!mbar_wait<true>(&full_bar[s], ph, abort_flag, p.err, ERR_PG_FULL)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t sf_smem = smem_u32(ring + s * kPgStageBytes) + kTileBytes + kSfBytes;
+                        if (!(pp.dbg & 8u)) {
+#pragma unroll
+                            for (uint32_t j = 0; j < 4; ++j)
+                                cp_scales_pair(tmem_sfb + 32 * s + 8 * j + 4, scale_desc(sf_smem + j * 512));
+                        }
+                        commit_pair(cluster_addr(&sf_ready[s], 0));
+                        if (++s == stages) {
+                            s = 0;
+                            ph ^= 1;
+                        }
                     }
                 }
             }
@@ -427,7 +544,10 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             uint32_t s = 0, ph = 0, unit_no = 0, tile_no = 0, sfi = 0;
             bool ok = true;
             Unit un;
-            for (uint32_t u = cluster_id; ok && load_unit(pp, u, total_units, n_tiles, splits, &un); u += clusters, ++unit_no) {
+            const bool spans = (pp.dbg & 32u) != 0 && cluster_id < kTraceClusters;
+            if (spans)
+                g_pair_spans[cluster_id * 3] = global_ns();
+            for (uint32_t u = cluster_id; ok && load_unit(pp, u, sc, &un); u += clusters, ++unit_no) {
                 const bool more = u + clusters < total_units;
                 for (uint32_t nt = un.nt_begin; ok && nt < un.nt_end; ++nt, ++tile_no) {
                     if (!mbar_wait<true>(acc_empty, (tile_no & 1) ^ 1, abort_flag, p.err, ERR_PG_ACC_EMPTY)) {
@@ -443,11 +563,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                             ok = false;
                             break;
                         }
-                        if (!mbar_wait<true>(&full_bar[s], ph, abort_flag, p.err, ERR_PG_FULL)) {
-                            ok = false;
-                            break;
-                        }
                         trace(tr, 2, sfi, 1);
+                        // both copiers are done with the stage's B scales (they waited for the stage's loads)
                         if (!mbar_wait<true>(&sf_ready[s], ph, abort_flag, p.err, ERR_PG_SF_READY)) {
                             ok = false;
                             break;
@@ -463,23 +580,22 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                                                tmem_sfa + 16 * kb + 4 * j, tmem_sfb + 32 * s + 8 * j);
                         }
                         // the stage's shared memory and its scale buffer in tensor memory are free again
-                        commit_pair(cluster_addr(&empty_bar[s], 0));
-                        commit_pair(cluster_addr(&empty_bar[s], 1));
-                        if (last && more) {
-                            commit_pair(cluster_addr(&panel_free[kb], 0));
-                            commit_pair(cluster_addr(&panel_free[kb], 1));
-                        }
+                        commit_both(&empty_bar[s]);
+                        if (last && more)
+                            commit_both(&panel_free[kb]);
                         trace(tr, 2, sfi, 3);
                         if (++s == stages) {
                             s = 0;
                             ph ^= 1;
                         }
                     }
-                    if (ok) {
-                        commit_pair(cluster_addr(acc_full, 0));
-                        commit_pair(cluster_addr(acc_full, 1));
-                    }
+                    if (ok)
+                        commit_both(acc_full);
                 }
+            }
+            if (spans) {
+                g_pair_spans[cluster_id * 3 + 1] = global_ns();
+                g_pair_spans[cluster_id * 3 + 2] = unit_no;
             }
         }
     } else if (warp == 10) {
@@ -490,7 +606,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             uint32_t s = 0, ph = 0, unit_no = 0, sfi = 0;
             bool ok = true;
             Unit un;
-            for (uint32_t u = cluster_id; ok && load_unit(pp, u, total_units, n_tiles, splits, &un); u += clusters, ++unit_no) {
+            for (uint32_t u = cluster_id; ok && load_unit(pp, u, sc, &un); u += clusters, ++unit_no) {
                 for (uint32_t nt = un.nt_begin; ok && nt < un.nt_end; ++nt) {
                     for (uint32_t kb = 0; kb < kb_count; ++kb, ++sfi) {
                         trace(tr, 1, sfi, 0);
@@ -511,21 +627,15 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                             break;
                         }
                         trace(tr, 1, sfi, 1);
-                        // the MMAs that read this scale buffer last time round are done (they also free the stage)
-                        if (!mbar_wait<true>(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_PG_SF_FREE)) {
-                            ok = false;
-                            break;
-                        }
+                        // (the stage was refilled, so the MMAs that read its scale buffer in tensor memory last
+                        // time round are done: the buffer may be overwritten)
                         trace(tr, 1, sfi, 2);
                         tc_fence_after();
                         const uint32_t sf_smem = smem_u32(ring + s * kPgStageBytes) + kTileBytes;
                         if (!(pp.dbg & 8u)) {
 #pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j) {
+                            for (uint32_t j = 0; j < 4; ++j)
                                 cp_scales_pair(tmem_sfb + 32 * s + 8 * j, scale_desc(sf_smem + j * 512));
-                                cp_scales_pair(tmem_sfb + 32 * s + 8 * j + 4,
-                                               scale_desc(sf_smem + kSfBytes + j * 512));
-                            }
                         }
                         commit_pair(cluster_addr(&sf_ready[s], 0));
                         trace(tr, 1, sfi, 3);
@@ -547,7 +657,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         uint32_t tile_no = 0;
         Unit un;
         bool ok = true;
-        for (uint32_t u = cluster_id; ok && load_unit(pp, u, total_units, n_tiles, splits, &un); u += clusters) {
+        for (uint32_t u = cluster_id; ok && load_unit(pp, u, sc, &un); u += clusters) {
             const int my_row0 = un.row0 + static_cast<int>(rank * 128);
             const int my_nrows = min(128, un.nrows - static_cast<int>(rank * 128));
             const int r = static_cast<int>(quad * 32 + lane);
@@ -742,8 +852,13 @@ cudaError_t launch_nvfp4_pair_gemm(const GemmProblem& g, cudaStream_t stream, co
         return v != nullptr ? static_cast<uint32_t>(std::atoi(v)) : 0u;
     }();
     pp.dbg = dbg;
-
     const uint32_t n_tiles = tp.b_rows / kPgBN;
+    static const uint32_t force_splits = [] {
+        const char* v = std::getenv("QS3_PAIR_SPLITS");
+        return v != nullptr ? static_cast<uint32_t>(std::atoi(v)) : 0u;
+    }();
+    pp.force_splits = (force_splits == 1 || force_splits == 2 || force_splits == 4) && n_tiles % force_splits == 0
+        ? force_splits : 0;
 
     CUtensorMap ma, mb, msa, msb;
     const uint64_t b_total_rows = static_cast<uint64_t>(g.groups) * tp.b_rows;
@@ -778,5 +893,16 @@ extern "C" qsfi_status qs3_debug_pair_trace(uint64_t* out, uint32_t capacity, ui
         || cudaMemcpyFromSymbol(out, g_pair_trace, total * sizeof(uint64_t)) != cudaSuccess)
         return QSFI_STATUS_CUDA_ERROR;
     *count = total;
+    return QSFI_STATUS_OK;
+}
+
+extern "C" qsfi_status qs3_debug_pair_spans(uint64_t* out, uint32_t capacity)
+{
+    using namespace qs3;
+    if (out == nullptr || capacity < kTraceClusters * 3)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    if (cudaDeviceSynchronize() != cudaSuccess
+        || cudaMemcpyFromSymbol(out, g_pair_spans, kTraceClusters * 3 * sizeof(uint64_t)) != cudaSuccess)
+        return QSFI_STATUS_CUDA_ERROR;
     return QSFI_STATUS_OK;
 }

@@ -1376,6 +1376,14 @@ qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const
     if (d->num_tokens == 0)
         return set_invalid_arg(ctx, "invalid MoE num_tokens");
     const int64_t t = d->num_tokens, h = p.hidden_size;
+    const bool mapped = d->expert_id_map.data != nullptr;
+    if (mapped
+        && (d->expert_id_map.dtype != QSFI_DTYPE_I32 || !contiguous1(d->expert_id_map) || d->expert_id_map.shape[0] <= 0
+            || d->dispatch_ids.data == nullptr || d->dispatch_ids.dtype != QSFI_DTYPE_I32
+            || !contiguous2(d->dispatch_ids) || d->dispatch_ids.shape[0] != t || d->dispatch_ids.shape[1] != p.top_k))
+        return set_invalid_arg(ctx, "expert_id_map must be a contiguous i32 [router experts] tensor with an i32 "
+                                    "[num_tokens, top_k] dispatch_ids output");
+    const int64_t router_experts = mapped ? d->expert_id_map.shape[0] : static_cast<int64_t>(p.num_experts);
     status = validate_tensor(ctx, d->hidden, "hidden", QSFI_DTYPE_BF16);
     if (status == QSFI_STATUS_OK)
         status = validate_tensor(ctx, d->router_weight, "router_weight", QSFI_DTYPE_BF16);
@@ -1390,20 +1398,21 @@ qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const
     if (!contiguous2(d->hidden) || !contiguous2(d->router_weight) || !contiguous2(d->router_logits)
         || !contiguous2(d->topk_ids) || !contiguous2(d->topk_weights))
         return set_invalid_arg(ctx, "MoE route tensors must be contiguous");
-    if (d->hidden.shape[0] != t || d->hidden.shape[1] != h || d->router_weight.shape[0] != p.num_experts
+    if (d->hidden.shape[0] != t || d->hidden.shape[1] != h || d->router_weight.shape[0] != router_experts
         || d->router_weight.shape[1] != h || d->router_logits.shape[0] != t
-        || d->router_logits.shape[1] != p.num_experts || d->topk_ids.shape[0] != t
+        || d->router_logits.shape[1] != router_experts || d->topk_ids.shape[0] != t
         || d->topk_ids.shape[1] != p.top_k || d->topk_weights.shape[0] != t
         || d->topk_weights.shape[1] != p.top_k)
         return set_invalid_arg(ctx, "MoE token/top-k tensor shape mismatch");
     if (d->router_bias.data != nullptr
-        && (d->router_bias.dtype != QSFI_DTYPE_F32 || d->router_bias.shape[0] != p.num_experts
+        && (d->router_bias.dtype != QSFI_DTYPE_F32 || d->router_bias.shape[0] != router_experts
             || !contiguous1(d->router_bias)))
         return set_invalid_arg(ctx, "router_bias must be a contiguous f32 [num_experts] tensor");
-    if (p.top_k > 16 || p.num_experts > 4096 || p.top_k > p.num_experts)
+    if (p.top_k > 16 || router_experts > 4096 || p.top_k > router_experts)
         return set_unsupported(ctx, "router supports top_k <= 16 and num_experts <= 4096");
     if (!std::isfinite(d->routed_scaling_factor) || d->routed_scaling_factor <= 0.0f)
         return set_invalid_arg(ctx, "routed_scaling_factor must be finite and positive");
+    const uint32_t num_router_experts = static_cast<uint32_t>(router_experts);
     const bool quantise = d->hidden_packed.data != nullptr;
     if (quantise) {
         if (h % 16 != 0 || d->hidden_packed.dtype != QSFI_DTYPE_U8 || !contiguous2(d->hidden_packed)
@@ -1424,19 +1433,23 @@ qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const
     gl.b = d->router_weight.data;
     gl.b_pitch_bytes = static_cast<uint64_t>(h) * 2;
     gl.groups = 1;
-    gl.n = p.num_experts;
+    gl.n = num_router_experts;
     gl.k = p.hidden_size;
     gl.epilogue = EPI_STORE_F32;
     gl.out = d->router_logits.data;
-    gl.out_pitch_elems = p.num_experts;
+    gl.out_pitch_elems = num_router_experts;
     status = gemm_or_error(ctx, gl, "MoE router-logits GEMM");
     if (status != QSFI_STATUS_OK)
         return status;
     cudaError_t err = launch_router_topk(d->router_logits.data, 0, static_cast<const float*>(d->router_bias.data),
                                          static_cast<int32_t*>(d->topk_ids.data),
                                          static_cast<float*>(d->topk_weights.data), d->num_tokens,
-                                         p.num_experts, p.top_k, d->score == QSCU_ROUTER_SCORE_SIGMOID,
+                                         num_router_experts, p.top_k, d->score == QSCU_ROUTER_SCORE_SIGMOID,
                                          d->renormalize != 0, d->routed_scaling_factor, ctx->stream);
+    if (err == cudaSuccess && mapped)
+        err = launch_ep_map_ids(static_cast<const int32_t*>(d->topk_ids.data),
+                                static_cast<const int32_t*>(d->expert_id_map.data), num_router_experts,
+                                static_cast<int32_t*>(d->dispatch_ids.data), d->num_tokens * p.top_k, ctx->stream);
     if (err != cudaSuccess)
         return set_cuda_error(ctx, err, "MoE routing");
     if (quantise) {

@@ -636,6 +636,18 @@ __global__ void ep_rank_routes_kernel(int32_t* rows, float* weights, uint32_t to
     weights[i] = 1.0f;
 }
 
+// out[i] = map[ids[i]] (ids outside the map stay -1): expert ids of the router -> expert SLOTS of an
+// expert-parallel placement, where a rank's slots hold its own experts and replicas of hot ones.
+__global__ void ep_map_ids_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ map,
+                                  uint32_t map_len, int32_t* __restrict__ out, uint32_t n)
+{
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n)
+        return;
+    const int32_t id = ids[i];
+    out[i] = (id >= 0 && static_cast<uint32_t>(id) < map_len) ? map[id] : -1;
+}
+
 template <typename T> T* carve(char* base, size_t& offset, size_t count)
 {
     offset = align_up(offset, kWorkspaceAlign);
@@ -793,6 +805,16 @@ cudaError_t launch_ep_pull_tokens(const EpPullTokensParams& p, cudaStream_t stre
         largest = std::max<uint64_t>(largest, p.seg_bytes[j]);
     const uint32_t chunks = static_cast<uint32_t>(std::min<uint64_t>(64, std::max<uint64_t>(1, largest / 16 / 1024)));
     ep_pull_tokens_kernel<<<dim3(chunks, p.num_ranks, p.num_segments), 256, 0, stream>>>(p);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_map_ids(const int32_t* ids, const int32_t* map, uint32_t map_len, int32_t* out, uint32_t n,
+                              cudaStream_t stream)
+{
+    if (n == 0)
+        return cudaSuccess;
+    ep_map_ids_kernel<<<(n + 255) / 256, 256, 0, stream>>>(ids, map, map_len, out, n);
     note_launch();
     return cudaGetLastError();
 }

@@ -67,8 +67,29 @@ def balanced_placement(counts, world: int):
     return [e for r in range(world) for e in sorted(slots[r])]
 
 
+def hottest_experts(counts, hot: int):
+    """The ``hot`` experts with the most routes (descending count, ties by ascending id)."""
+    return sorted(range(len(counts)), key=lambda e: (-int(counts[e]), e))[:hot]
+
+
+def slot_id_table(num_experts: int, world: int, hot_positions, rank: int):
+    """Expert id -> expert SLOT for the tokens that live on ``rank`` when every rank holds, after its
+    own ``num_experts / world`` experts, a replica of each expert in ``hot_positions``: slot =
+    holder * slots_per_rank + index on the holder; an ordinary expert is held by its owner, a hot
+    one by ``rank`` itself (its replica), so routes to hot experts never leave the rank."""
+    per = num_experts // world
+    slots = per + len(hot_positions)
+    hot = {int(p): j for j, p in enumerate(hot_positions)}
+    return [rank * slots + per + hot[p] if p in hot else (p // per) * slots + p % per
+            for p in range(num_experts)]
+
+
 class CudaBackend:
-    """The three compute phases on this rank's GPU through the C ABI."""
+    """The three compute phases on this rank's GPU through the C ABI.
+
+    With replicated hot experts (``data.hot_positions``) the plan counts expert SLOTS: every rank
+    has ``experts / world`` slots for its own experts plus one per hot expert, and the router's
+    ids are mapped to slots (``dispatch_ids``) before the exchange; ``ids`` keeps the router's ids."""
 
     def __init__(self, ctx: ops.Context, data, world: int):
         import ctypes as C
@@ -79,12 +100,19 @@ class CudaBackend:
         dev = data.hidden.device
         t, h, k, e = cfg.tokens, cfg.hidden, cfg.top_k, cfg.experts
         first, count = data.expert_range
+        self.rank = first // count if count else 0
+        slots = count + len(getattr(data, "hot_positions", []) or [])
+        self.slot_range = (self.rank * slots, slots) if slots != count else (first, count)
+        self.id_map = data.slot_id_map(self.rank, world) if slots != count else None
         self.plan = ops.MoePlan(ctx, ops.MoePlanConfig(
-            max_num_tokens=t * world, hidden_size=h, intermediate_size=cfg.inter, num_experts=e, top_k=k,
-            local_expert_offset=first, local_num_experts=count, backend=capi.MOE_BACKEND_NVFP4))
+            max_num_tokens=t * world, hidden_size=h, intermediate_size=cfg.inter,
+            num_experts=e if self.id_map is None else world * slots, top_k=k,
+            local_expert_offset=self.slot_range[0], local_num_experts=self.slot_range[1],
+            backend=capi.MOE_BACKEND_NVFP4))
         u8, i32, f32, bf = torch.uint8, torch.int32, torch.float32, torch.bfloat16
         self.logits = torch.empty((t, e), dtype=f32, device=dev)
         self.ids = torch.empty((t, k), dtype=i32, device=dev)
+        self.dispatch_ids = self.ids if self.id_map is None else torch.empty((t, k), dtype=i32, device=dev)
         self.wts = torch.empty((t, k), dtype=f32, device=dev)
         self.packed = torch.empty((t, h // 2), dtype=u8, device=dev)
         self.scale = torch.empty((t, h // 16), dtype=u8, device=dev)
@@ -95,8 +123,10 @@ class CudaBackend:
         self.ws_finish = torch.empty(n.value, dtype=u8, device=dev)
 
     def bind_route_outputs(self, packed, scale, ids, wts):
-        """Let ``route`` write into caller-owned tensors (a peer-mapped block)."""
-        self.packed, self.scale, self.ids, self.wts = packed, scale, ids, wts
+        """Let ``route`` write what the other ranks read into caller-owned tensors (a peer-mapped block)."""
+        self.packed, self.scale, self.dispatch_ids, self.wts = packed, scale, ids, wts
+        if self.id_map is None:
+            self.ids = ids
 
     def pull_tokens(self, peer_blocks, offsets, sizes, dsts):
         """All-gather by peer loads: segment j of every rank's block -> dsts[j][rank]."""
@@ -121,8 +151,11 @@ class CudaBackend:
         d.hidden_scale = ops._desc(self.scale, 2, capi.DTYPE_FP8_E4M3)
         d.score, d.renormalize, d.routed_scaling_factor, d.act_global_scale = 0, 1, 1.0, 1.0
         d.num_tokens = hidden.shape[0]
+        if self.id_map is not None:
+            d.expert_id_map = ops._desc(self.id_map, 1)
+            d.dispatch_ids = ops._desc(self.dispatch_ids, 2)
         self.ctx.check(self.ctx._lib.qs3_moe_ep_route(self.ctx.handle, self.plan.handle, self.C.byref(d)))
-        return self.packed, self.scale, self.ids, self.wts
+        return self.packed, self.scale, self.dispatch_ids, self.wts
 
     def experts(self, packed, scale, ids, wts, out, skip_empty=False):
         d = capi.MoeNvfp4PreparedDesc()
@@ -329,8 +362,8 @@ class ExpertParallelLayer:
         """What the last step's experts phase sorted on this rank, as numpy arrays: (ids, weights)
         of every token row it saw, the rank's expert range, and the plan's routing tables
         (counts, indptr, route_rows, row_tokens). For parity checks."""
-        first, count = self.data.expert_range
         b = self.backend
+        first, count = getattr(b, "slot_range", self.data.expert_range)
         tables = b.plan.routing_tables(b.ws_experts, self.g_ids.shape[0])
         return (self.g_ids.cpu().numpy(), self.g_wts.cpu().numpy(), first, count,
                 [x.cpu().numpy() for x in tables[:4]])
@@ -392,7 +425,7 @@ class ExpertParallelLayer:
         ms = stage_ms.get("experts")
         if not ms:
             return None
-        first, count = self.data.expert_range
+        first, count = getattr(self.backend, "slot_range", self.data.expert_range)
         ids = self.g_ids.flatten().long()
         local = ids[(ids >= first) & (ids < first + count)] - first
         counts = torch.bincount(local, minlength=count)

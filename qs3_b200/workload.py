@@ -67,11 +67,18 @@ class LayerData:
     spreads hot experts over ranks. ``balance_world`` = n > 1 derives the placement here:
     the router is run on a seeded calibration batch (the same on every rank, plain tensor
     ops at set-up time) and ``ep.balanced_placement`` evens the per-rank route counts.
+    ``hot_experts`` = H > 0 (with ``balance_world``) additionally REPLICATES the H experts
+    that got the most routes on the calibration batch: every rank keeps a copy of them
+    after its own experts (``hot_positions`` lists their physical positions, the same on
+    every rank), so a token's routes to a hot expert are served where the token lives and
+    neither the token nor a partial sum crosses NVLink for them. ``slot_id_map`` turns the
+    router's ids into the expert slots of this layout.
     """
 
     def __init__(self, cfg: LayerConfig, ctx: ops.Context, seed: int = 0, expert_range=None,
                  token_seed: int | None = None, keep_bf16: bool = False, placement=None,
-                 balance_world: int = 0, calibration_tokens: int = 8192):
+                 balance_world: int = 0, calibration_tokens: int = 8192, hot_experts: int = 0,
+                 hot_positions=None):
         dev = torch.device("cuda", ctx.device)
         self.cfg = cfg
         first, count = expert_range if expert_range is not None else (0, cfg.experts)
@@ -95,7 +102,15 @@ class LayerData:
                 logits += self.bias
             ids = logits.topk(cfg.top_k, dim=1).indices
             counts = torch.bincount(ids.flatten(), minlength=cfg.experts).cpu().tolist()
+            hot_logical = []
+            if hot_experts > 0:
+                from .ep import hottest_experts
+                hot_logical = hottest_experts(counts, hot_experts)
+                counts = [0 if e in set(hot_logical) else c for e, c in enumerate(counts)]
             placement = balanced_placement(counts, balance_world)
+            if hot_logical:
+                where = {e: p for p, e in enumerate(placement)}
+                hot_positions = [where[e] for e in hot_logical]
             del x, logits, ids
         if placement is not None:
             logical = [int(e) for e in placement]
@@ -106,14 +121,18 @@ class LayerData:
             if self.bias is not None:
                 self.bias = self.bias.index_select(0, index).contiguous()
         self.placement = logical
-        # routed experts: generate every expert so that all ranks agree, keep the local slice
-        gate_up = torch.empty((count, 2 * i, h), dtype=torch.bfloat16, device=dev)
-        down = torch.empty((count, h, i), dtype=torch.bfloat16, device=dev)
-        for pos in range(first, first + count):
+        self.hot_positions = [int(p) for p in hot_positions] if hot_positions else []
+        # routed experts: every expert is generated from its own seed so that all ranks agree; this rank
+        # keeps its slice of the physical positions, followed by its replicas of the hot experts
+        local = list(range(first, first + count)) + (self.hot_positions if expert_range is not None else [])
+        self.local_positions = local
+        gate_up = torch.empty((len(local), 2 * i, h), dtype=torch.bfloat16, device=dev)
+        down = torch.empty((len(local), h, i), dtype=torch.bfloat16, device=dev)
+        for slot, pos in enumerate(local):
             ge = torch.Generator(device=dev)
             ge.manual_seed(1000 * seed + 100 + logical[pos])
-            gate_up[pos - first] = (torch.randn((2 * i, h), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
-            down[pos - first] = (torch.randn((h, i), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
+            gate_up[slot] = (torch.randn((2 * i, h), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
+            down[slot] = (torch.randn((h, i), generator=ge, device=dev) * 0.02).to(torch.bfloat16)
         self.shared = None
         if s:
             sgu = _normal_bf16((1, 2 * s, h), 0.02, gw, dev)
@@ -143,6 +162,16 @@ class LayerData:
         gt = torch.Generator(device=dev)
         gt.manual_seed(1000 * seed + 7 + (token_seed or 0))
         self.hidden = _normal_bf16((cfg.tokens, h), 1.0, gt, dev, chunk_rows=1024)
+
+    def slot_id_map(self, rank: int, world: int):
+        """i32 [experts]: the expert SLOT (rank * slots_per_rank + index on that rank) a route of a
+        token that lives on ``rank`` goes to, per physical expert id: the owner's slot for an ordinary
+        expert, this rank's own replica for a hot one. None without replicated experts."""
+        if not self.hot_positions:
+            return None
+        from .ep import slot_id_table
+        table = slot_id_table(self.cfg.experts, world, self.hot_positions, rank)
+        return torch.tensor(table, dtype=torch.int32, device=self.hidden.device)
 
     def plan(self, ctx: ops.Context, max_tokens: int | None = None) -> ops.MoePlan:
         cfg = self.cfg

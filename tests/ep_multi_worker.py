@@ -25,8 +25,10 @@ def main():
     cfg = workload.LayerConfig("ep_multi", 512, 512, 32, 4, 256, 256, True, 1.1)
     first, count = ep.expert_block(rank, world, cfg.experts)
     balance = world if os.environ.get("QS3_TEST_BALANCED") == "1" else 0
+    hot = int(os.environ.get("QS3_TEST_HOT", "0")) if balance else 0
     part = workload.LayerData(cfg, ctx, seed=9, expert_range=(first, count), token_seed=rank + 1,
-                              balance_world=balance)
+                              balance_world=balance, hot_experts=hot)
+    assert len(part.hot_positions) == hot
     layer = ep.ExpertParallelLayer(ctx, part, rank, world)
     for _ in range(3):
         out = layer.step()
@@ -53,7 +55,8 @@ def main():
     assert np.max(np.abs(f32(got) - want)) <= 2.0 ** -5 * np.max(np.abs(want))
     dist.barrier()
     if rank == 0:
-        print(f"EP_MULTI_OK world={world} rel_l2={err:.3e} combine={layer.combine_mode} balanced={bool(balance)}")
+        print(f"EP_MULTI_OK world={world} rel_l2={err:.3e} combine={layer.combine_mode} balanced={bool(balance)} "
+              f"hot={hot}")
     dist.destroy_process_group()
 
 

@@ -93,7 +93,32 @@ class OracleBackend:
         out.copy_(_bf(self.orc.f32_to_bf16(acc)))
 
 
-def _worker(rank, world, port, results):
+class ReplicatedOracleBackend(OracleBackend):
+    """As above with the experts in ``hot`` replicated on every rank: the rank's slots are its own
+    experts followed by the replicas, and routes travel as slot ids (``ep.slot_id_table``)."""
+
+    def __init__(self, orc, w, first, count, world, hot):
+        super().__init__(orc, w, first, count, world)
+        from qs3_b200 import ep
+        self.rank = first // count
+        self.slots = count + len(hot)
+        self.table = np.array(ep.slot_id_table(CFG.experts, world, hot, self.rank), np.int32)
+        local = list(range(first, first + count)) + list(hot)
+        self.gu = tuple(x[local] for x in w["gu"])
+        self.dn = tuple(x[local] for x in w["d"])
+
+    def route(self, hidden):
+        packed, scale, ids, wts = super().route(hidden)
+        self.ids = ids
+        return packed, scale, torch.from_numpy(self.table[ids.numpy()]), wts
+
+    def experts(self, packed, scale, ids, wts, out):
+        res = self.orc.moe_nvfp4(packed.numpy(), scale.numpy(), ids.numpy(), wts.numpy(), self.gu, self.dn,
+                                 local_offset=self.rank * self.slots)
+        out.copy_(_bf(res))
+
+
+def _worker(rank, world, port, results, hot=()):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -102,7 +127,9 @@ def _worker(rank, world, port, results):
         w = _weights(orc)
         first, count = ep.expert_block(rank, world, CFG.experts)
         data = SimpleNamespace(cfg=CFG, hidden=_bf(_tokens(rank)), expert_range=(first, count), shared=True)
-        layer = ep.ExpertParallelLayer(None, data, rank, world, backend=OracleBackend(orc, w, first, count, world))
+        backend = (ReplicatedOracleBackend(orc, w, first, count, world, list(hot)) if hot
+                   else OracleBackend(orc, w, first, count, world))
+        layer = ep.ExpertParallelLayer(None, data, rank, world, backend=backend)
         out1 = _np16(layer.step()).copy()
         out2 = _np16(layer.step()).copy()  # buffers are reused: a second step must give the same answer
         assert np.array_equal(out1, out2)
@@ -127,12 +154,13 @@ def _single_rank_reference(orc, world):
     return outs
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_expert_parallel_equals_single_rank(oracle, world):
+@pytest.mark.parametrize("world,hot", [(2, ()), (4, ()), (2, (5, 0)), (4, (6, 3, 1))])
+def test_expert_parallel_equals_single_rank(oracle, world, hot):
+    """`hot`: experts replicated on every rank; their routes are served by the token's own rank."""
     port = _free_port()
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, results, hot), nprocs=world, join=True)
     ref = _single_rank_reference(oracle, world)
     for rank in range(world):
         got = oracle.bf16_to_f32(results[rank]).astype(np.float64)
@@ -140,6 +168,23 @@ def test_expert_parallel_equals_single_rank(oracle, world):
         # partial sums are rounded to bf16 per rank before the ordered sum: not bit-exact by design
         assert np.linalg.norm(got - want) <= 1e-2 * np.linalg.norm(want)
         assert np.max(np.abs(got - want)) <= 2.0 ** -5 * np.max(np.abs(want))
+
+
+def test_slot_table_of_a_replicated_placement():
+    from qs3_b200.ep import hottest_experts, slot_id_table
+    counts = [5, 90, 7, 80, 3, 80, 1, 2]
+    assert hottest_experts(counts, 3) == [1, 3, 5]           # descending count, ties by id
+    world, hot = 2, [1, 5]
+    per, slots = 4, 6
+    for rank in range(world):
+        table = slot_id_table(8, world, hot, rank)
+        for e, slot in enumerate(table):
+            holder, index = divmod(slot, slots)
+            if e in hot:
+                assert holder == rank and index == per + hot.index(e)   # served where the token lives
+            else:
+                assert holder == e // per and index == e % per           # served by the owner
+        assert len(set(table)) == 8
 
 
 def test_expert_block_partition():
