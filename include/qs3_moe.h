@@ -608,6 +608,42 @@ typedef struct {
 } qs3_moe_ep_pull_tokens_desc;
 qsfi_status qs3_moe_ep_pull_tokens(qsfi_context* ctx, const qs3_moe_ep_pull_tokens_desc* desc);
 
+/* Barrier over the ranks of an expert-parallel layer, on the context's stream, without a
+ * collective library: every rank owns a signal pad of num_ranks u32 words in peer-mapped memory
+ * (zeroed once); the kernel stores `epoch` into its slot of every rank's pad and waits until every
+ * slot of its own pad has reached `epoch` (plain release stores / acquire loads at system scope
+ * over NVLink). `epoch` must grow by one with every barrier on the same pads. The wait is bounded:
+ * after timeout_cycles SM clocks (0: about two seconds) the kernel records a code in the device
+ * error word and returns, so a rank that died or never got here turns into
+ * QSFI_STATUS_BACKEND_ERROR at the next qs3_moe_check_device_error instead of a hung GPU. */
+typedef struct {
+    const qsfi_device_ptr* pads; /* [num_ranks] rank r's pad as mapped on this device */
+    uint32_t num_ranks;          /* <= 32 */
+    uint32_t my_rank;
+    uint32_t epoch;
+    uint64_t timeout_cycles;
+} qs3_moe_ep_barrier_desc;
+qsfi_status qs3_moe_ep_barrier(qsfi_context* ctx, const qs3_moe_ep_barrier_desc* desc);
+
+/* Synchronises the context's stream and turns a recorded bounded-wait expiry (see
+ * qs3_moe_read_device_error) into QSFI_STATUS_BACKEND_ERROR with the code in the last-error
+ * message; QSFI_STATUS_OK when nothing expired. Clears the error word. */
+qsfi_status qs3_moe_check_device_error(qsfi_context* ctx);
+
+/* Test aid: launches one small kernel whose threads wait on an mbarrier that nothing ever
+ * completes, with `limit_cycles` (1 .. 2e7 SM clocks) as the wait limit. The kernel must return
+ * after about that many clocks with the expiry code in the device error word. Nothing faults,
+ * traps or hangs; this exercises the path every bounded wait of the tensor-core kernels takes
+ * when its producer is lost. */
+qsfi_status qs3_debug_bounded_wait_probe(qsfi_context* ctx, uint64_t limit_cycles);
+
+/* Measurement aids of the CTA-pair GEMM (gemm_pair.cu), filled when QS3_PAIR_DBG has bit 32 set:
+ * clock64() stamps of the first cluster's producer / scale copier / MMA issuer / epilogue warp 0 at
+ * their hand-over points ([4 roles][192 stages][4 events]), and per cluster the global-timer
+ * start / end (ns) and unit count of its MMA issuer ([128][3]). */
+qsfi_status qs3_debug_pair_trace(uint64_t* out, uint32_t capacity, uint32_t* count);
+qsfi_status qs3_debug_pair_spans(uint64_t* out, uint32_t capacity);
+
 /* Routing tables of the last execute on this workspace, for parity checks:
  * copies of counts[E_local], indptr[E_local+1], route_rows[T*K] (-1: not local),
  * row_tokens[R_local], row_scales[R_local] (upstream qsfi_moe.cu:26-31). Device

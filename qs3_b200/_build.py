@@ -20,7 +20,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libqs3moe.so")
 CHECKED_LIB_PATH = os.path.join(PKG_DIR, "libqs3moe_checked.so")
 
 SOURCES = ["context.cu", "router.cu", "routing.cu", "gemm.cu", "gemm_api.cu", "nvfp4.cu", "moe.cu",
-           "peak_probe.cu", "fp8.cu", "norm.cu", "loader.cu", "nvfp4_decode.cu", "gemm_dense.cu", "gemm_pair.cu"]
+           "peak_probe.cu", "fp8.cu", "norm.cu", "loader.cu", "nvfp4_decode.cu", "gemm_dense.cu", "gemm_pair.cu", "failure.cu"]
 HEADERS = ["common.cuh", "nvfp4.cuh", "tcgen05.cuh", os.path.join("..", "..", "include", "qs3_moe.h")]
 
 NVCC_FLAGS = [

@@ -231,6 +231,11 @@ class MoeEpPullTokensDesc(C.Structure):
                 ("num_segments", C.c_uint32)]
 
 
+class MoeEpBarrierDesc(C.Structure):
+    _fields_ = [("pads", _P(C.c_void_p)), ("num_ranks", C.c_uint32), ("my_rank", C.c_uint32),
+                ("epoch", C.c_uint32), ("timeout_cycles", C.c_uint64)]
+
+
 class RmsnormDesc(C.Structure):
     _fields_ = [("x", Tensor2), ("weight", Tensor1), ("out", Tensor2), ("hidden_size", C.c_uint32),
                 ("weight_bias", C.c_float), ("eps", C.c_float)]
@@ -325,7 +330,12 @@ _SIGNATURES = {
     "qsfi_rmsnorm": (C.c_int, [C.c_void_p, _P(RmsnormDesc)]),
     "qsfi_fused_add_rmsnorm": (C.c_int, [C.c_void_p, _P(FusedAddRmsnormDesc)]),
     "qs3_fused_add_rmsnorm_nvfp4": (C.c_int, [C.c_void_p, _P(FusedAddRmsnormNvfp4Desc)]),
+    "qs3_moe_ep_barrier": (C.c_int, [C.c_void_p, _P(MoeEpBarrierDesc)]),
     "qs3_moe_read_device_error": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
+    "qs3_moe_check_device_error": (C.c_int, [C.c_void_p]),
+    "qs3_debug_bounded_wait_probe": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "qs3_debug_pair_trace": (C.c_int, [_P(C.c_uint64), C.c_uint32, _P(C.c_uint32)]),
+    "qs3_debug_pair_spans": (C.c_int, [_P(C.c_uint64), C.c_uint32]),
     "qs3_moe_launch_count": (C.c_uint64, []),
     "qs3_moe_profile_begin": (C.c_int, [C.c_void_p]),
     "qs3_moe_profile_end": (C.c_int, [C.c_void_p, _P(C.c_int32), _P(C.c_float), C.c_uint32,

@@ -175,6 +175,13 @@ struct EpPullTokensParams {
 };
 cudaError_t launch_ep_pull_tokens(const EpPullTokensParams& p, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
+struct EpBarrierParams {
+    uint32_t* pads[32];     // pads[r]: rank r's signal pad (num_ranks words) as mapped on this device
+    uint32_t num_ranks, my_rank, epoch;
+    uint64_t limit_cycles;
+    uint32_t* err;
+};
+cudaError_t launch_ep_barrier(const EpBarrierParams& p, cudaStream_t stream);
 cudaError_t launch_ep_map_ids(const int32_t* ids, const int32_t* map, uint32_t map_len, int32_t* out, uint32_t n,
                               cudaStream_t stream);
 cudaError_t launch_ep_rank_routes(int32_t* rows, float* weights, uint32_t tokens, uint32_t ranks,

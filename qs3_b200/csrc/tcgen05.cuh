@@ -110,7 +110,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity)
 // MMA threads) instead of the suspending try_wait (for whole epilogue warps).
 template <bool POLL = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* err, uint32_t code)
+                                          uint32_t* err, uint32_t code, uint64_t limit_cycles = kWaitCycles)
 {
     if (POLL ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity))
         return true;
@@ -123,7 +123,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             continue;
         if (*abort_flag != 0)
             return false;
-        if (static_cast<uint64_t>(clock64()) - start > kWaitCycles) {
+        if (static_cast<uint64_t>(clock64()) - start > limit_cycles) {
             *abort_flag = 1;
             if (err != nullptr)
                 atomicCAS(err, 0u, code);

@@ -21,9 +21,9 @@ Per layer and rank (T tokens per rank, n ranks):
   5. finish    shared expert (on a side stream while the dispatch runs) + sum of the n partials in
                ascending rank order in f32 + sigmoid-gated shared term, one bf16 rounding
 
-The barriers are those of ``torch.distributed._symmetric_memory`` (NCCL collectives through
-``torch.distributed`` on a separate communication stream when peer mapping is unavailable);
-the kernels of this library never wait on another rank themselves.
+The barriers between the phases are the library's own (``qs3_moe_ep_barrier``: signal pads in the
+peer-mapped block, bounded spin, an expiry is reported by ``check()``); NCCL collectives through
+``torch.distributed`` on a separate communication stream when peer mapping is unavailable.
 The compute steps are behind a small backend interface so that the exchange logic can
 be exercised on CPU ranks (gloo) with a stand-in backend supplied by the tests.
 """
@@ -220,6 +220,7 @@ class ExpertParallelLayer:
     def __init__(self, ctx, data, rank: int, world: int, backend=None, group=None, combine="auto",
                  dispatch="auto"):
         self.rank, self.world, self.group = rank, world, group
+        self.barrier_timeout_cycles = 0          # library default (about two seconds of SM clocks)
         self.data = data
         cfg = data.cfg
         self.cfg = cfg
@@ -243,9 +244,12 @@ class ExpertParallelLayer:
         self.token_block = None
         if self.cuda and world > 1 and combine != "nccl":
             try:
+                import os
+                # only plain peer loads and stores touch the block: no NVLink multicast object is wanted
+                os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
                 import torch.distributed._symmetric_memory as symm
-                # one peer-mapped block per rank: [partial sums | codes | scales | ids | weights]
-                sizes = [n * t * h * 2, t * (h // 2), t * (h // 16), t * k * 4, t * k * 4]
+                # one peer-mapped block per rank: [partial sums | codes | scales | ids | weights | signal pads]
+                sizes = [n * t * h * 2, t * (h // 2), t * (h // 16), t * k * 4, t * k * 4, 2 * 256]
                 offs, total = [], 0
                 for sz in sizes:
                     offs.append(total)
@@ -256,11 +260,17 @@ class ExpertParallelLayer:
                 base = [int(ptr) for ptr in hdl.buffer_ptrs]
                 self.partial = self._sym[offs[0]:offs[0] + sizes[0]].view(bf).view(n * t, h)
                 self.peer_ptrs = [b + offs[0] for b in base]
+                # signal pads of the library's own bounded barrier: two channels of n words per rank
+                self._sym[offs[5]:offs[5] + sizes[5]].zero_()
+                torch.cuda.synchronize(dev)
+                dist.barrier(group=group)        # every pad is zero before anybody signals
+                self._pads = [[b + offs[5] + 256 * ch for b in base] for ch in range(2)]
+                self._epoch = [0, 0]
                 if dispatch != "nccl" and hasattr(self.backend, "bind_route_outputs"):
                     seg = lambda j, dt, shape: self._sym[offs[j]:offs[j] + sizes[j]].view(dt).view(shape)
                     self.backend.bind_route_outputs(seg(1, u8, (t, h // 2)), seg(2, u8, (t, h // 16)),
                                                     seg(3, i32, (t, k)), seg(4, f32, (t, k)))
-                    self.token_block = dict(peers=base, offsets=offs[1:], sizes=sizes[1:])
+                    self.token_block = dict(peers=base, offsets=offs[1:5], sizes=sizes[1:5])
             except Exception as exc:  # no peer mapping on this system: exchange copies instead
                 if combine == "pull":
                     raise
@@ -280,6 +290,13 @@ class ExpertParallelLayer:
 
     # -- collectives (NCCL on the communication stream; gloo in the CPU tests) --
     def _dispatch(self, packed, scale, ids, wts):
+        try:
+            self._dispatch_collectives(packed, scale, ids, wts)
+        except RuntimeError as exc:
+            # a rank that died or never joined: the process group's timeout ends the collective
+            raise ops.Qs3Error(capi.STATUS_BACKEND_ERROR, f"expert-parallel dispatch failed: {exc}") from exc
+
+    def _dispatch_collectives(self, packed, scale, ids, wts):
         pairs = ((self.g_packed, packed), (self.g_scale, scale), (self.g_ids, ids), (self.g_wts, wts))
         if self.cuda:
             # one NCCL group for the four gathers instead of four launches
@@ -290,16 +307,30 @@ class ExpertParallelLayer:
             for dst, src in pairs:
                 dist.all_gather_into_tensor(dst, src, group=self.group)
 
+    def _barrier(self, channel: int):
+        """The library's barrier over the ranks' signal pads, on the current stream. Its wait is
+        bounded: a rank that never arrives leaves an error code that ``check()`` raises."""
+        self._epoch[channel] += 1
+        ops.ep_barrier(self.ctx, self._pads[channel], self.rank, self._epoch[channel], self.barrier_timeout_cycles)
+
+    def check(self):
+        """Synchronise and raise if a bounded device-side wait of the steps so far expired."""
+        if self.cuda and self.ctx is not None:
+            self.ctx.check_device_error()
+
     def _dispatch_pull(self):
         """Barrier over the ranks' signal pads (every rank's route outputs are in its block),
         then copy all blocks here with peer loads."""
         tb = self.token_block
-        self._symm_handle.barrier(channel=0)
+        self._barrier(0)
         self.backend.pull_tokens(tb["peers"], tb["offsets"], tb["sizes"],
                                  (self.g_packed, self.g_scale, self.g_ids, self.g_wts))
 
     def _combine(self):
-        dist.all_to_all_single(self.recv.view(self.world * self.cfg.tokens, -1), self.partial, group=self.group)
+        try:
+            dist.all_to_all_single(self.recv.view(self.world * self.cfg.tokens, -1), self.partial, group=self.group)
+        except RuntimeError as exc:
+            raise ops.Qs3Error(capi.STATUS_BACKEND_ERROR, f"expert-parallel combine failed: {exc}") from exc
 
     def step(self, hidden=None, out=None):
         hidden = self.data.hidden if hidden is None else hidden
@@ -335,7 +366,7 @@ class ExpertParallelLayer:
         if pull and self.dispatch_mode == "pull":
             # every rank's partial sums are complete once all ranks passed this barrier; the
             # barrier of the next step's dispatch keeps anyone from overwriting a buffer early
-            self._symm_handle.barrier(channel=1)
+            self._barrier(1)
             main.wait_event(self.ev[1])
             b.finish_pull(hidden, self.peer_ptrs, ids, out)
             return out
@@ -402,7 +433,7 @@ class ExpertParallelLayer:
                 for name, ms in ops.profile_end(b.ctx):
                     acc.setdefault("experts/" + name, []).append(ms)
             if pull and self.dispatch_mode == "pull":
-                self._symm_handle.barrier(channel=1)
+                self._barrier(1)
             elif pull:
                 dist.all_reduce(self.flag, group=self.group)
             else:

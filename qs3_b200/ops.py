@@ -103,6 +103,11 @@ class Context:
         self.check(self._lib.qs3_moe_read_device_error(self.handle, C.byref(code)))
         return code.value
 
+    def check_device_error(self):
+        """Synchronise the stream; raise ``Qs3Error`` (BACKEND_ERROR) if a bounded device-side wait
+        of an earlier call ran out (a lost load, tensor-core commit or peer rank)."""
+        self.check(self._lib.qs3_moe_check_device_error(self.handle))
+
 
 @dataclass
 class MoePlanConfig:
@@ -533,6 +538,20 @@ def route_sort_static(ctx: Context, topk_ids, topk_weights, local_expert_offset:
 
 STAGE_NAMES = {1: "router_logits_gemm", 2: "router_topk", 3: "route_sort", 4: "gather_quantize",
                5: "gate_up_gemm_swiglu", 6: "down_gemm", 7: "shared_expert", 8: "combine"}
+
+
+def ep_barrier(ctx: Context, pads, my_rank: int, epoch: int, timeout_cycles: int = 0):
+    """``qs3_moe_ep_barrier``: barrier over the ranks whose signal pads (device addresses as mapped
+    here, one per rank) are ``pads``; bounded wait, see ``Context.check_device_error``."""
+    d = capi.MoeEpBarrierDesc()
+    arr = (C.c_void_p * len(pads))(*[int(p) for p in pads])
+    d.pads, d.num_ranks, d.my_rank, d.epoch, d.timeout_cycles = arr, len(pads), my_rank, epoch & 0xFFFFFFFF, timeout_cycles
+    ctx.check(ctx._lib.qs3_moe_ep_barrier(ctx.handle, C.byref(d)))
+
+
+def bounded_wait_probe(ctx: Context, limit_cycles: int = 100000):
+    """``qs3_debug_bounded_wait_probe``: a kernel whose wait nothing satisfies; returns after the limit."""
+    ctx.check(ctx._lib.qs3_debug_bounded_wait_probe(ctx.handle, limit_cycles))
 
 
 def launch_count() -> int:

@@ -170,6 +170,49 @@ def test_expert_parallel_equals_single_rank(oracle, world, hot):
         assert np.max(np.abs(got - want)) <= 2.0 ** -5 * np.max(np.abs(want))
 
 
+def _failing_worker(rank, world, port, results):
+    """Rank 1 fails between steps (host side: it raises before its second dispatch and leaves);
+    rank 0 must get an error from its own step within the process group's timeout, not hang."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=6))
+    try:
+        from oracle import binding as orc
+        from qs3_b200 import ep, ops
+        w = _weights(orc)
+        first, count = ep.expert_block(rank, world, CFG.experts)
+        data = SimpleNamespace(cfg=CFG, hidden=_bf(_tokens(rank)), expert_range=(first, count), shared=True)
+        layer = ep.ExpertParallelLayer(None, data, rank, world, backend=OracleBackend(orc, w, first, count, world))
+        layer.step()                                   # a healthy step first
+        if rank == 1:
+            results[rank] = "left"
+            return                                     # the failure: this rank never dispatches again
+        t0 = time.perf_counter()
+        try:
+            layer.step()
+            results[rank] = "no error"
+        except ops.Qs3Error as exc:
+            results[rank] = ("error", exc.status, time.perf_counter() - t0)
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_a_rank_that_leaves_between_steps_is_reported_not_waited_for():
+    port = _free_port()
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_failing_worker, args=(2, port, results), nprocs=2, join=True)
+    assert results[1] == "left"
+    kind, status, seconds = results[0]
+    from qs3_b200 import capi
+    assert kind == "error" and status == capi.STATUS_BACKEND_ERROR
+    assert seconds < 30
+
+
 def test_slot_table_of_a_replicated_placement():
     from qs3_b200.ep import hottest_experts, slot_id_table
     counts = [5, 90, 7, 80, 3, 80, 1, 2]
