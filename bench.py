@@ -417,10 +417,11 @@ def run_ours(args, rank, world, local_rank):
     value = total_tokens * args.steps / (block_med / 1000.0)
     e2e_value = total_tokens * args.steps / (e2e_med / 1000.0)
 
+    hbm_gbs, peak_kind = _peaks()
+    roof = layer.roofline(stage_ms, hbm_gbs, peak_kind)   # on every rank: it may run collectives at N > 1
     if rank != 0:
         return
     graphed = getattr(layer, "graph", None) is not None
-    hbm_gbs, peak_kind = _peaks()
     line = {
         "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": block_med / args.steps,
@@ -443,7 +444,7 @@ def run_ours(args, rank, world, local_rank):
         "stage_ms": stage_ms,
     }
     line.update(extra)
-    line["roofline"] = layer.roofline(stage_ms, hbm_gbs, peak_kind)
+    line["roofline"] = roof
     if hasattr(layer, "stage_rooflines"):
         line["stages"] = layer.stage_rooflines(stage_ms, hbm_gbs)
     if parity is not None:

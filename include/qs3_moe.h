@@ -528,6 +528,11 @@ typedef struct {
        to this rank's own replica). dispatch_ids is what the other phases take as topk_ids. */
     qsfi_tensor1 expert_id_map;  /* in:  optional i32 [router experts] */
     qsfi_tensor2 dispatch_ids;   /* out: with expert_id_map: i32 [num_tokens, top_k] */
+    /* Optional: rank_mask[t] = the set of ranks token t has a route to (bit r: one of its dispatch ids
+       lies in rank r's plan.local_num_experts slots), for a dispatch that moves a token only to the
+       ranks that need it (qs3_moe_ep_pull_routed). */
+    qsfi_tensor1 rank_mask;      /* out: optional u32 (dtype I32) [num_tokens] */
+    uint32_t num_ranks;          /* with rank_mask */
 } qs3_moe_ep_route_desc;
 qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_ep_route_desc* desc);
 
@@ -607,6 +612,28 @@ typedef struct {
     uint32_t num_segments;              /* <= 4 */
 } qs3_moe_ep_pull_tokens_desc;
 qsfi_status qs3_moe_ep_pull_tokens(qsfi_context* ctx, const qs3_moe_ep_pull_tokens_desc* desc);
+
+/* De-duplicated dispatch by pulling. Every rank keeps, in one peer-mapped block, the outputs of
+ * qs3_moe_ep_route for its own tokens: codes, linear scales, dispatch ids, weights and the rank
+ * mask. This call fills the local [num_ranks * num_tokens, ...] buffers: ids and weights of every
+ * token of every rank (the route sort needs them), codes and scales only of the tokens whose mask
+ * has this rank's bit, i.e. each token row crosses NVLink once per rank that holds one of its
+ * experts and not at all otherwise. Rows that are not pulled are left as they were. Ordering
+ * against the other ranks as for qs3_moe_ep_pull_tokens (qs3_moe_ep_barrier before and after). */
+typedef struct {
+    const qsfi_device_ptr* peer_blocks; /* [num_ranks] base of rank r's block as mapped on this device */
+    uint64_t offset_codes, offset_scales, offset_ids, offset_weights, offset_mask; /* in a block, 16-byte aligned */
+    qsfi_device_ptr dst_codes;   /* u8  [num_ranks * num_tokens, hidden / 2] */
+    qsfi_device_ptr dst_scales;  /* e4m3 [num_ranks * num_tokens, hidden / 16] */
+    qsfi_device_ptr dst_ids;     /* i32 [num_ranks * num_tokens, top_k] */
+    qsfi_device_ptr dst_weights; /* f32 [num_ranks * num_tokens, top_k] */
+    uint32_t num_ranks;          /* <= 32 */
+    uint32_t my_rank;
+    uint32_t num_tokens;         /* per rank */
+    uint32_t top_k;              /* <= 16 */
+    uint32_t hidden_size;        /* multiple of 256, <= 2048 */
+} qs3_moe_ep_pull_routed_desc;
+qsfi_status qs3_moe_ep_pull_routed(qsfi_context* ctx, const qs3_moe_ep_pull_routed_desc* desc);
 
 /* Barrier over the ranks of an expert-parallel layer, on the context's stream, without a
  * collective library: every rank owns a signal pad of num_ranks u32 words in peer-mapped memory

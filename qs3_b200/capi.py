@@ -169,7 +169,8 @@ class MoeEpRouteDesc(C.Structure):
                 ("hidden_packed", Tensor2), ("hidden_scale", Tensor2), ("score", C.c_int),
                 ("renormalize", C.c_uint32), ("routed_scaling_factor", C.c_float),
                 ("act_global_scale", C.c_float), ("num_tokens", C.c_uint32),
-                ("expert_id_map", Tensor1), ("dispatch_ids", Tensor2)]
+                ("expert_id_map", Tensor1), ("dispatch_ids", Tensor2), ("rank_mask", Tensor1),
+                ("num_ranks", C.c_uint32)]
 
 
 class MoeNvfp4PreparedDesc(C.Structure):
@@ -229,6 +230,14 @@ class MoeEpPullTokensDesc(C.Structure):
     _fields_ = [("peer_blocks", _P(C.c_void_p)), ("segment_offset", C.c_uint64 * 4),
                 ("segment_bytes", C.c_uint64 * 4), ("dst", C.c_void_p * 4), ("num_ranks", C.c_uint32),
                 ("num_segments", C.c_uint32)]
+
+
+class MoeEpPullRoutedDesc(C.Structure):
+    _fields_ = [("peer_blocks", _P(C.c_void_p)), ("offset_codes", C.c_uint64), ("offset_scales", C.c_uint64),
+                ("offset_ids", C.c_uint64), ("offset_weights", C.c_uint64), ("offset_mask", C.c_uint64),
+                ("dst_codes", C.c_void_p), ("dst_scales", C.c_void_p), ("dst_ids", C.c_void_p),
+                ("dst_weights", C.c_void_p), ("num_ranks", C.c_uint32), ("my_rank", C.c_uint32),
+                ("num_tokens", C.c_uint32), ("top_k", C.c_uint32), ("hidden_size", C.c_uint32)]
 
 
 class MoeEpBarrierDesc(C.Structure):
@@ -330,6 +339,7 @@ _SIGNATURES = {
     "qsfi_rmsnorm": (C.c_int, [C.c_void_p, _P(RmsnormDesc)]),
     "qsfi_fused_add_rmsnorm": (C.c_int, [C.c_void_p, _P(FusedAddRmsnormDesc)]),
     "qs3_fused_add_rmsnorm_nvfp4": (C.c_int, [C.c_void_p, _P(FusedAddRmsnormNvfp4Desc)]),
+    "qs3_moe_ep_pull_routed": (C.c_int, [C.c_void_p, _P(MoeEpPullRoutedDesc)]),
     "qs3_moe_ep_barrier": (C.c_int, [C.c_void_p, _P(MoeEpBarrierDesc)]),
     "qs3_moe_read_device_error": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
     "qs3_moe_check_device_error": (C.c_int, [C.c_void_p]),

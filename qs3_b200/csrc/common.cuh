@@ -182,8 +182,17 @@ struct EpBarrierParams {
     uint32_t* err;
 };
 cudaError_t launch_ep_barrier(const EpBarrierParams& p, cudaStream_t stream);
-cudaError_t launch_ep_map_ids(const int32_t* ids, const int32_t* map, uint32_t map_len, int32_t* out, uint32_t n,
-                              cudaStream_t stream);
+cudaError_t launch_ep_route_targets(const int32_t* ids, const int32_t* map, uint32_t map_len, int32_t* out,
+                                    uint32_t* mask, uint32_t tokens, uint32_t top_k, uint32_t per_rank,
+                                    uint32_t ranks, cudaStream_t stream);
+struct EpPullRoutedParams {
+    const uint8_t* peer[32];   // every rank's peer-mapped token block
+    uint64_t off_codes, off_scales, off_ids, off_wts, off_mask; // byte offsets of the segments in a block
+    uint8_t *dst_codes, *dst_scales, *dst_ids, *dst_wts;        // local [num_ranks * num_tokens, ...] buffers
+    uint32_t num_ranks, my_rank, num_tokens, top_k;
+    uint32_t code_vecs, scale_vecs; // 16-byte vectors per row of codes (<= 64) / scales (<= 32)
+};
+cudaError_t launch_ep_pull_routed(const EpPullRoutedParams& p, cudaStream_t stream);
 cudaError_t launch_ep_rank_routes(int32_t* rows, float* weights, uint32_t tokens, uint32_t ranks,
                                   cudaStream_t stream);
 

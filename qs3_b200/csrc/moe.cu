@@ -1383,6 +1383,10 @@ qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const
             || !contiguous2(d->dispatch_ids) || d->dispatch_ids.shape[0] != t || d->dispatch_ids.shape[1] != p.top_k))
         return set_invalid_arg(ctx, "expert_id_map must be a contiguous i32 [router experts] tensor with an i32 "
                                     "[num_tokens, top_k] dispatch_ids output");
+    if (d->rank_mask.data != nullptr
+        && (d->rank_mask.dtype != QSFI_DTYPE_I32 || !contiguous1(d->rank_mask) || d->rank_mask.shape[0] != t
+            || d->num_ranks == 0 || d->num_ranks > 32))
+        return set_invalid_arg(ctx, "rank_mask must be a contiguous i32 [num_tokens] tensor with 1..32 ranks");
     const int64_t router_experts = mapped ? d->expert_id_map.shape[0] : static_cast<int64_t>(p.num_experts);
     status = validate_tensor(ctx, d->hidden, "hidden", QSFI_DTYPE_BF16);
     if (status == QSFI_STATUS_OK)
@@ -1446,10 +1450,12 @@ qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const
                                          static_cast<float*>(d->topk_weights.data), d->num_tokens,
                                          num_router_experts, p.top_k, d->score == QSCU_ROUTER_SCORE_SIGMOID,
                                          d->renormalize != 0, d->routed_scaling_factor, ctx->stream);
-    if (err == cudaSuccess && mapped)
-        err = launch_ep_map_ids(static_cast<const int32_t*>(d->topk_ids.data),
-                                static_cast<const int32_t*>(d->expert_id_map.data), num_router_experts,
-                                static_cast<int32_t*>(d->dispatch_ids.data), d->num_tokens * p.top_k, ctx->stream);
+    if (err == cudaSuccess && (mapped || d->rank_mask.data != nullptr))
+        err = launch_ep_route_targets(static_cast<const int32_t*>(d->topk_ids.data),
+                                      static_cast<const int32_t*>(d->expert_id_map.data), num_router_experts,
+                                      static_cast<int32_t*>(d->dispatch_ids.data),
+                                      static_cast<uint32_t*>(d->rank_mask.data), d->num_tokens, p.top_k,
+                                      p.local_num_experts, d->num_ranks, ctx->stream);
     if (err != cudaSuccess)
         return set_cuda_error(ctx, err, "MoE routing");
     if (quantise) {
@@ -1802,6 +1808,49 @@ qsfi_status qs3_moe_ep_pull_tokens(qsfi_context* ctx, const qs3_moe_ep_pull_toke
         p.dst[j] = static_cast<uint8_t*>(d->dst[j]);
     }
     return set_cuda_error(ctx, launch_ep_pull_tokens(p, ctx->stream), "qs3_moe_ep_pull_tokens");
+}
+
+qsfi_status qs3_moe_ep_pull_routed(qsfi_context* ctx, const qs3_moe_ep_pull_routed_desc* d)
+{
+    if (ctx == nullptr)
+        return QSFI_STATUS_INVALID_ARGUMENT;
+    clear_error(&ctx->last_error);
+    qsfi_status status = activate_context(ctx);
+    if (status != QSFI_STATUS_OK)
+        return status;
+    if (d == nullptr || d->peer_blocks == nullptr)
+        return set_invalid_arg(ctx, "desc/peer_blocks is null");
+    if (d->num_ranks == 0 || d->num_ranks > 32 || d->my_rank >= d->num_ranks || d->num_tokens == 0 || d->top_k == 0
+        || d->top_k > 16 || d->hidden_size == 0 || d->hidden_size % 256 != 0 || d->hidden_size > 2048)
+        return set_invalid_arg(ctx, "expert-parallel pull: 1..32 ranks, top_k <= 16, hidden a multiple of 256 up to 2048");
+    if (static_cast<uint64_t>(d->num_ranks) * d->num_tokens > 0x7fffffffull / 16)
+        return set_unsupported(ctx, "expert-parallel pull: too many token rows");
+    EpPullRoutedParams p {};
+    for (uint32_t r = 0; r < d->num_ranks; ++r) {
+        if (d->peer_blocks[r] == nullptr || !aligned16(d->peer_blocks[r]))
+            return set_invalid_arg(ctx, "expert-parallel pull: peer blocks must be non-null and 16-byte aligned");
+        p.peer[r] = static_cast<const uint8_t*>(d->peer_blocks[r]);
+    }
+    if ((d->offset_codes | d->offset_scales | d->offset_ids | d->offset_weights | d->offset_mask) % 16 != 0
+        || !aligned16(d->dst_codes) || !aligned16(d->dst_scales) || !aligned16(d->dst_ids) || !aligned16(d->dst_weights)
+        || d->dst_codes == nullptr || d->dst_scales == nullptr || d->dst_ids == nullptr || d->dst_weights == nullptr)
+        return set_invalid_arg(ctx, "expert-parallel pull: segments and destinations must be 16-byte aligned");
+    p.off_codes = d->offset_codes;
+    p.off_scales = d->offset_scales;
+    p.off_ids = d->offset_ids;
+    p.off_wts = d->offset_weights;
+    p.off_mask = d->offset_mask;
+    p.dst_codes = static_cast<uint8_t*>(d->dst_codes);
+    p.dst_scales = static_cast<uint8_t*>(d->dst_scales);
+    p.dst_ids = static_cast<uint8_t*>(d->dst_ids);
+    p.dst_wts = static_cast<uint8_t*>(d->dst_weights);
+    p.num_ranks = d->num_ranks;
+    p.my_rank = d->my_rank;
+    p.num_tokens = d->num_tokens;
+    p.top_k = d->top_k;
+    p.code_vecs = d->hidden_size / 32;
+    p.scale_vecs = d->hidden_size / 256;
+    return set_cuda_error(ctx, launch_ep_pull_routed(p, ctx->stream), "qs3_moe_ep_pull_routed");
 }
 
 // ---- FP8 block-scaled path ------------------------------------------------------------

@@ -636,16 +636,111 @@ __global__ void ep_rank_routes_kernel(int32_t* rows, float* weights, uint32_t to
     weights[i] = 1.0f;
 }
 
-// out[i] = map[ids[i]] (ids outside the map stay -1): expert ids of the router -> expert SLOTS of an
-// expert-parallel placement, where a rank's slots hold its own experts and replicas of hot ones.
-__global__ void ep_map_ids_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ map,
-                                  uint32_t map_len, int32_t* __restrict__ out, uint32_t n)
+// Per token: dispatch ids out[t, k] = map[ids[t, k]] (ids outside the map stay -1; without a map the
+// ids themselves are the dispatch ids) and mask[t] = the set of ranks the token has a route to (bit r:
+// some dispatch id lies in rank r's `per_rank` expert slots). The map turns the router's expert ids
+// into the expert SLOTS of a placement in which every rank holds its own experts and replicas of hot ones.
+__global__ void ep_route_targets_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ map,
+                                        uint32_t map_len, int32_t* __restrict__ out, uint32_t* __restrict__ mask,
+                                        uint32_t tokens, uint32_t top_k, uint32_t per_rank, uint32_t ranks)
 {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n)
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens)
         return;
-    const int32_t id = ids[i];
-    out[i] = (id >= 0 && static_cast<uint32_t>(id) < map_len) ? map[id] : -1;
+    uint32_t m = 0;
+    for (uint32_t k = 0; k < top_k; ++k) {
+        int32_t id = ids[static_cast<size_t>(t) * top_k + k];
+        if (map != nullptr) {
+            id = (id >= 0 && static_cast<uint32_t>(id) < map_len) ? map[id] : -1;
+            out[static_cast<size_t>(t) * top_k + k] = id;
+        }
+        if (id >= 0 && static_cast<uint32_t>(id) / per_rank < ranks)
+            m |= 1u << (static_cast<uint32_t>(id) / per_rank);
+    }
+    if (mask != nullptr)
+        mask[t] = m;
+}
+
+// Dispatch that pulls only what this rank needs: for every token of every rank, its dispatch ids
+// and weights always (the route sort needs them to see that a row is not local), its NVFP4 codes and
+// scales only when the token's rank mask says it has a route to an expert slot of this rank. A warp
+// takes eight consecutive tokens of one peer: eight lanes fetch the masks, then the warp issues
+// the loads of all wanted rows before storing any of them, so that the NVLink round trips overlap.
+// Rows that are not pulled keep whatever an earlier step left there; nothing reads them, because
+// none of their (fresh) ids is local. Plain peer loads; no load of this kernel is multicast.
+__global__ void __launch_bounds__(256) ep_pull_routed_kernel(EpPullRoutedParams p)
+{
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t groups_per_rank = (p.num_tokens + 7) / 8;
+    const uint32_t group = blockIdx.x * 8 + warp;
+    if (group >= groups_per_rank * p.num_ranks)
+        return;
+    const uint32_t r = group / groups_per_rank;
+    const uint32_t t0 = (group % groups_per_rank) * 8;
+    const uint8_t* peer = p.peer[r];
+    const uint32_t nrows = min(8u, p.num_tokens - t0);
+    uint32_t my_mask = 0;
+    if (lane < nrows)
+        my_mask = reinterpret_cast<const uint32_t*>(peer + p.off_mask)[t0 + lane];
+    // ids and weights of the eight tokens: 8 * top_k words each, contiguous in the peer's block
+    const uint32_t words = nrows * p.top_k;
+    const uint32_t* ids_src = reinterpret_cast<const uint32_t*>(peer + p.off_ids) + static_cast<size_t>(t0) * p.top_k;
+    const uint32_t* wts_src = reinterpret_cast<const uint32_t*>(peer + p.off_wts) + static_cast<size_t>(t0) * p.top_k;
+    const size_t row0 = static_cast<size_t>(r) * p.num_tokens + t0;
+    uint32_t* ids_dst = reinterpret_cast<uint32_t*>(p.dst_ids) + row0 * p.top_k;
+    uint32_t* wts_dst = reinterpret_cast<uint32_t*>(p.dst_wts) + row0 * p.top_k;
+    uint32_t iv[4], wv[4];
+#pragma unroll
+    for (uint32_t q = 0; q < 4; ++q) {
+        const uint32_t i = lane + 32 * q;
+        iv[q] = i < words ? ids_src[i] : 0;
+        wv[q] = i < words ? wts_src[i] : 0;
+    }
+    uint32_t wanted = 0; // bit i: row t0 + i goes to this rank
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i)
+        wanted |= ((__shfl_sync(0xffffffffu, my_mask, i) >> p.my_rank) & 1u) << i;
+    // codes: code_vecs 16-byte vectors per row (<= 64 per lane pair of loads), scales: scale_vecs (<= 32)
+    const uint4* codes = reinterpret_cast<const uint4*>(peer + p.off_codes);
+    const uint4* scales = reinterpret_cast<const uint4*>(peer + p.off_scales);
+    uint4* codes_dst = reinterpret_cast<uint4*>(p.dst_codes);
+    uint4* scales_dst = reinterpret_cast<uint4*>(p.dst_scales);
+    for (uint32_t i0 = 0; i0 < 8; i0 += 4) {
+        uint4 c[4][2], sc[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            const uint32_t i = i0 + j;
+            const bool on = (wanted >> i) & 1u;
+            const size_t src_row = t0 + i;
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h)
+                if (on && lane + 32 * h < p.code_vecs)
+                    c[j][h] = codes[src_row * p.code_vecs + lane + 32 * h];
+            if (on && lane < p.scale_vecs)
+                sc[j] = scales[src_row * p.scale_vecs + lane];
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            const uint32_t i = i0 + j;
+            if (!((wanted >> i) & 1u))
+                continue;
+            const size_t dst_row = row0 + i;
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h)
+                if (lane + 32 * h < p.code_vecs)
+                    codes_dst[dst_row * p.code_vecs + lane + 32 * h] = c[j][h];
+            if (lane < p.scale_vecs)
+                scales_dst[dst_row * p.scale_vecs + lane] = sc[j];
+        }
+    }
+#pragma unroll
+    for (uint32_t q = 0; q < 4; ++q) {
+        const uint32_t i = lane + 32 * q;
+        if (i < words) {
+            ids_dst[i] = iv[q];
+            wts_dst[i] = wv[q];
+        }
+    }
 }
 
 template <typename T> T* carve(char* base, size_t& offset, size_t count)
@@ -803,18 +898,30 @@ cudaError_t launch_ep_pull_tokens(const EpPullTokensParams& p, cudaStream_t stre
     uint64_t largest = 0;
     for (uint32_t j = 0; j < p.num_segments; ++j)
         largest = std::max<uint64_t>(largest, p.seg_bytes[j]);
-    const uint32_t chunks = static_cast<uint32_t>(std::min<uint64_t>(64, std::max<uint64_t>(1, largest / 16 / 1024)));
+    const uint32_t chunks = static_cast<uint32_t>(std::min<uint64_t>(2 * 148, std::max<uint64_t>(1, largest / 16 / 1024)));
     ep_pull_tokens_kernel<<<dim3(chunks, p.num_ranks, p.num_segments), 256, 0, stream>>>(p);
     note_launch();
     return cudaGetLastError();
 }
 
-cudaError_t launch_ep_map_ids(const int32_t* ids, const int32_t* map, uint32_t map_len, int32_t* out, uint32_t n,
-                              cudaStream_t stream)
+cudaError_t launch_ep_route_targets(const int32_t* ids, const int32_t* map, uint32_t map_len, int32_t* out,
+                                    uint32_t* mask, uint32_t tokens, uint32_t top_k, uint32_t per_rank,
+                                    uint32_t ranks, cudaStream_t stream)
 {
-    if (n == 0)
+    if (tokens == 0 || (map == nullptr && mask == nullptr))
         return cudaSuccess;
-    ep_map_ids_kernel<<<(n + 255) / 256, 256, 0, stream>>>(ids, map, map_len, out, n);
+    ep_route_targets_kernel<<<(tokens + 255) / 256, 256, 0, stream>>>(ids, map, map_len, out, mask, tokens, top_k,
+                                                                      per_rank, ranks);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_pull_routed(const EpPullRoutedParams& p, cudaStream_t stream)
+{
+    if (p.num_ranks == 0 || p.num_tokens == 0)
+        return cudaSuccess;
+    const uint32_t groups = (p.num_tokens + 7) / 8 * p.num_ranks;
+    ep_pull_routed_kernel<<<(groups + 7) / 8, 256, 0, stream>>>(p);
     note_launch();
     return cudaGetLastError();
 }

@@ -5,12 +5,12 @@ Per layer and rank (T tokens per rank, n ranks):
 
   1. route     router-logits GEMM + top-k on the rank's own tokens; tokens quantised to
                NVFP4 once (1152 B per row instead of 4096 B of bf16)
-  2. dispatch  all-gather of codes, scales, ids and weights: every rank sees all n*T tokens.
-               With top-10 routing a token already reaches 5.9 of 8 ranks on average, so
-               replicating it to all ranks costs at most 1/0.74 of a de-duplicated
-               all-to-all and needs no host-side count exchange or synchronisation.
-               "pull": the route outputs live in a peer-mapped block; after a barrier over the
-               ranks' signal pads every rank copies all blocks with plain peer loads
+  2. dispatch  "pull" (default): the route outputs live in a peer-mapped block; after a barrier over the
+               ranks' signal pads every rank copies, with plain peer loads, the ids and weights of all
+               tokens and the codes and scales of the tokens that have a route to one of ITS expert
+               slots (qs3_moe_ep_pull_routed: a de-duplicated all-to-all, one row per (token, rank)
+               pair, no host-side count exchange). With replicated hot experts (below) a token
+               reaches ~2.5 of 8 ranks instead of ~7. "gather": all blocks whole
                (qs3_moe_ep_pull_tokens). "nccl": one coalesced group of all-gathers.
   3. experts   the rank's experts over all n*T tokens; routes to other ranks' experts are
                skipped (local_expert_offset), so row t holds the rank's partial sum
@@ -114,6 +114,7 @@ class CudaBackend:
         self.ids = torch.empty((t, k), dtype=i32, device=dev)
         self.dispatch_ids = self.ids if self.id_map is None else torch.empty((t, k), dtype=i32, device=dev)
         self.wts = torch.empty((t, k), dtype=f32, device=dev)
+        self.mask = None                 # rank mask per token, bound by the layer when it dispatches by pulling
         self.packed = torch.empty((t, h // 2), dtype=u8, device=dev)
         self.scale = torch.empty((t, h // 16), dtype=u8, device=dev)
         self.ws_experts = torch.empty(self.plan.workspace_size(t * world), dtype=u8, device=dev)
@@ -122,11 +123,23 @@ class CudaBackend:
                                                             cfg.shared_inter, C.byref(n)))
         self.ws_finish = torch.empty(n.value, dtype=u8, device=dev)
 
-    def bind_route_outputs(self, packed, scale, ids, wts):
+    def bind_route_outputs(self, packed, scale, ids, wts, mask=None):
         """Let ``route`` write what the other ranks read into caller-owned tensors (a peer-mapped block)."""
-        self.packed, self.scale, self.dispatch_ids, self.wts = packed, scale, ids, wts
+        self.packed, self.scale, self.dispatch_ids, self.wts, self.mask = packed, scale, ids, wts, mask
         if self.id_map is None:
             self.ids = ids
+
+    def pull_routed(self, peer_blocks, offsets, dsts):
+        """De-duplicated dispatch: ids / weights of every token, codes / scales of the tokens routed here.
+        ``offsets`` = byte offsets of (codes, scales, ids, weights, mask) in a peer block."""
+        d = capi.MoeEpPullRoutedDesc()
+        self._peer_blocks = (self.C.c_void_p * len(peer_blocks))(*peer_blocks)
+        d.peer_blocks = self._peer_blocks
+        d.offset_codes, d.offset_scales, d.offset_ids, d.offset_weights, d.offset_mask = offsets
+        d.dst_codes, d.dst_scales, d.dst_ids, d.dst_weights = (x.data_ptr() for x in dsts)
+        d.num_ranks, d.my_rank = len(peer_blocks), self.rank
+        d.num_tokens, d.top_k, d.hidden_size = self.cfg.tokens, self.cfg.top_k, self.cfg.hidden
+        self.ctx.check(self.ctx._lib.qs3_moe_ep_pull_routed(self.ctx.handle, self.C.byref(d)))
 
     def pull_tokens(self, peer_blocks, offsets, sizes, dsts):
         """All-gather by peer loads: segment j of every rank's block -> dsts[j][rank]."""
@@ -154,6 +167,9 @@ class CudaBackend:
         if self.id_map is not None:
             d.expert_id_map = ops._desc(self.id_map, 1)
             d.dispatch_ids = ops._desc(self.dispatch_ids, 2)
+        if self.mask is not None:
+            d.rank_mask = ops._desc(self.mask, 1)
+            d.num_ranks = self.world
         self.ctx.check(self.ctx._lib.qs3_moe_ep_route(self.ctx.handle, self.plan.handle, self.C.byref(d)))
         return self.packed, self.scale, self.dispatch_ids, self.wts
 
@@ -249,7 +265,7 @@ class ExpertParallelLayer:
                 os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
                 import torch.distributed._symmetric_memory as symm
                 # one peer-mapped block per rank: [partial sums | codes | scales | ids | weights | signal pads]
-                sizes = [n * t * h * 2, t * (h // 2), t * (h // 16), t * k * 4, t * k * 4, 2 * 256]
+                sizes = [n * t * h * 2, t * (h // 2), t * (h // 16), t * k * 4, t * k * 4, 2 * 256, t * 4]
                 offs, total = [], 0
                 for sz in sizes:
                     offs.append(total)
@@ -268,9 +284,12 @@ class ExpertParallelLayer:
                 self._epoch = [0, 0]
                 if dispatch != "nccl" and hasattr(self.backend, "bind_route_outputs"):
                     seg = lambda j, dt, shape: self._sym[offs[j]:offs[j] + sizes[j]].view(dt).view(shape)
+                    routed = dispatch != "gather" and h % 256 == 0 and h <= 2048
                     self.backend.bind_route_outputs(seg(1, u8, (t, h // 2)), seg(2, u8, (t, h // 16)),
-                                                    seg(3, i32, (t, k)), seg(4, f32, (t, k)))
-                    self.token_block = dict(peers=base, offsets=offs[1:5], sizes=sizes[1:5])
+                                                    seg(3, i32, (t, k)), seg(4, f32, (t, k)),
+                                                    seg(6, i32, (t,)) if routed else None)
+                    self.token_block = dict(peers=base, offsets=offs[1:5], sizes=sizes[1:5],
+                                            routed=offs[1:5] + [offs[6]] if routed else None)
             except Exception as exc:  # no peer mapping on this system: exchange copies instead
                 if combine == "pull":
                     raise
@@ -323,8 +342,12 @@ class ExpertParallelLayer:
         then copy all blocks here with peer loads."""
         tb = self.token_block
         self._barrier(0)
-        self.backend.pull_tokens(tb["peers"], tb["offsets"], tb["sizes"],
-                                 (self.g_packed, self.g_scale, self.g_ids, self.g_wts))
+        if tb["routed"] is not None:
+            # every token row crosses NVLink once per rank that holds one of its experts
+            self.backend.pull_routed(tb["peers"], tb["routed"], (self.g_packed, self.g_scale, self.g_ids, self.g_wts))
+        else:
+            self.backend.pull_tokens(tb["peers"], tb["offsets"], tb["sizes"],
+                                     (self.g_packed, self.g_scale, self.g_ids, self.g_wts))
 
     def _combine(self):
         try:
@@ -450,10 +473,15 @@ class ExpertParallelLayer:
         return {k: statistics.mean(v) for k, v in acc.items() if v}
 
     def roofline(self, stage_ms, hbm_gbs, peak_kind):
-        """Dominant phase at n > 1: the local experts. Bytes = this rank's expert weights that
-        received rows + gathered activation rows read + partial sums written."""
+        """Dominant kernel at n > 1 as at n = 1: the grouped gate_up GEMM + SwiGLU of the local experts,
+        timed by the library's stage events inside the experts phase. Algorithmic bytes = gate_up
+        weights of this rank's expert slots that received rows + the quantised rows read and written;
+        FLOPs = 2 * local routes * 2I * H; the bound is whichever takes longer at its measured peak.
+        `nvlink` describes the combine exchange: bytes this rank pulled from its peers (one bf16 partial
+        row per (token, remote rank) pair that has a route), the time of the pulling kernel and its
+        fraction of a peer copy measured with the library's own copy kernel on a large buffer."""
         cfg = self.cfg
-        ms = stage_ms.get("experts")
+        ms = stage_ms.get("experts/gate_up_gemm_swiglu")
         if not ms:
             return None
         first, count = getattr(self.backend, "slot_range", self.data.expert_range)
@@ -462,17 +490,66 @@ class ExpertParallelLayer:
         counts = torch.bincount(local, minlength=count)
         hit = int((counts > 0).sum().item())
         routes = int(local.numel())
-        gu_b, d_b = self.data.weight_bytes_per_expert()
-        rows_all = self.world * cfg.tokens
-        algo = hit * (gu_b + d_b) + rows_all * (cfg.hidden // 2 + cfg.hidden // 16) + rows_all * cfg.hidden * 2
-        flops = 2.0 * routes * 3 * cfg.inter * cfg.hidden
-        achieved = algo / (ms * 1e-3) / 1e9
-        exch = stage_ms.get("combine_exchange", 0.0)
-        exch_bytes = (self.world - 1) * cfg.tokens * cfg.hidden * 2
-        return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
-                "kernel": "local experts phase (route sort, gather, grouped gate_up + down GEMMs, local sum)",
-                "kernel_ms": ms, "algorithmic_bytes": algo, "experts_hit": hit, "local_routes": routes,
-                "tensor_tflops": flops / (ms * 1e-3) / 1e12,
-                "combine_exchange_gbs_per_direction": (exch_bytes / (exch * 1e-3) / 1e9) if exch else None}
+        gu_b, _d_b = self.data.weight_bytes_per_expert()
+        row_in, row_out = cfg.hidden // 2 + cfg.hidden // 16, cfg.inter // 2 + cfg.inter // 16
+        algo = hit * gu_b + routes * (row_in + row_out)
+        flops = 2.0 * routes * 2 * cfg.inter * cfg.hidden
+        ceiling = ops.tensor_peak_probe(self.ctx, "nvfp4", 256, 20000)
+        t_hbm, t_tensor = algo / (hbm_gbs * 1e9), flops / (ceiling * 1e12)
+        tflops, gbs = flops / (ms * 1e-3) / 1e12, algo / (ms * 1e-3) / 1e9
+        tensor_bound = t_tensor > t_hbm
+        out = {"bound": "tensor" if tensor_bound else "hbm", "achieved": tflops if tensor_bound else gbs,
+               "peak": ceiling if tensor_bound else hbm_gbs, "unit": "TFLOP/s" if tensor_bound else "GB/s",
+               "frac": tflops / ceiling if tensor_bound else gbs / hbm_gbs, "traffic": None,
+               "peak_source": ("measured in this run: issue loop of 128 x 256 tcgen05.mma on resident tiles, every SM"
+                               if tensor_bound else f"{peak_kind} copy bandwidth"),
+               "kernel": "grouped gate_up GEMM + SwiGLU of the rank's expert slots (rank 0)", "kernel_ms": ms,
+               "algorithmic_bytes": algo, "algorithmic_flops": flops, "experts_hit": hit, "local_routes": routes,
+               "max_rows_per_expert": int(counts.max().item()) if count else 0,
+               "hbm_gbs": gbs, "hbm_frac": gbs / hbm_gbs, "tensor_tflops": tflops,
+               "tensor_ceiling_tflops": ceiling, "tensor_frac_of_measured_ceiling": tflops / ceiling,
+               "experts_phase_ms": stage_ms.get("experts")}
+        finish = stage_ms.get("finish")
+        if self.combine_mode == "pull" and finish:
+            mine = self.backend.dispatch_ids.long() // count           # rank each route goes to
+            remote = 0
+            for r in range(self.world):
+                if r != self.rank:
+                    remote += int((mine == r).any(dim=1).sum().item())
+            pulled = remote * cfg.hidden * 2
+            peak = self.measure_peer_copy()
+            out["nvlink"] = {"bytes_pulled": pulled, "finish_ms": finish,
+                             "achieved_gbs": pulled / (finish * 1e-3) / 1e9, "peak_gbs_measured": peak,
+                             "frac": (pulled / (finish * 1e-3) / 1e9 / peak) if peak else None,
+                             "partial_rows_per_token": remote / cfg.tokens,
+                             "note": "finish = pull of the partial sums over NVLink + ordered sum + shared expert "
+                                     "gate, one kernel; peak = a 256 MB copy from the next rank's memory with "
+                                     "the library's peer-copy kernel"}
+        return out
 
+    def measure_peer_copy(self, mbytes: int = 256):
+        """GB/s of copying `mbytes` MB out of the next rank's peer-mapped memory with the library's own
+        peer-copy kernel (plain 16-byte loads over NVLink), CUDA events, best of three."""
+        if not self.cuda or self.world < 2 or self.token_block is None:
+            return None
+        import torch.distributed._symmetric_memory as symm
+        nbytes = mbytes << 20
+        dev = self.data.hidden.device
+        buf = symm.empty((nbytes,), dtype=torch.uint8, device=dev)
+        hdl = symm.rendezvous(buf, dist.group.WORLD if self.group is None else self.group)
+        peers = [int(p) for p in hdl.buffer_ptrs]
+        src = peers[(self.rank + 1) % self.world]
+        dst = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        best = 0.0
+        for _ in range(4):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier(group=self.group)
+            torch.cuda.synchronize(dev)
+            a.record()
+            self.backend.pull_tokens([src], [0], [nbytes], (dst,))
+            b.record()
+            torch.cuda.synchronize(dev)
+            best = max(best, nbytes / (a.elapsed_time(b) * 1e-3) / 1e9)
+        dist.barrier(group=self.group)
+        del dst, buf, hdl
+        return best

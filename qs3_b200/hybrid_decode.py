@@ -14,8 +14,9 @@ and once per step the first norm (``qsfi_rmsnorm``) and the LM head (``qscb_gemm
 The token mixers (gated attention over a KV cache, GatedDeltaNet recurrence) are NOT part of
 this library: they are stand-ins written with torch operators, with the tensor shapes, state
 sizes and memory traffic of the real layers, so that the step time the MoE share is quoted
-against is a realistic one. The KV cache is contiguous (the page-table indirection of a paged
-cache is not modelled). One step is captured in a CUDA graph and replayed.
+against is a realistic one. The KV cache is paged: fixed-size pages in a pool, addressed through a
+CSR page table as upstream's runtime builds it (src/runtime.rs:99-181). One step is captured in a
+CUDA graph and replayed.
 
 ``python -m qs3_b200.hybrid_decode`` prints one JSON line: decode tokens/s and the share of the
 step spent in the calls of this library.
@@ -57,6 +58,7 @@ class HybridConfig:
     batch: int = 128
     context: int = 4096
     new_tokens: int = 256
+    page_size: int = 16              # tokens per KV-cache page
     eps: float = 1e-6
     seed: int = 0
 
@@ -108,7 +110,13 @@ class _MoeBlock:
 class _Attention:
     """Stand-in for a gated-attention layer (torch operators): q/k/v projections with an output
     gate, per-head RMS norm of q and k, rotary embedding on the first `rotary_dim` dimensions,
-    attention of the new token over a contiguous KV cache, output projection."""
+    attention of the new token over a PAGED KV cache, output projection.
+
+    The cache is a pool of fixed-size pages [pages, kv_heads, page_size, head_dim] addressed through a
+    CSR page table, as upstream's runtime lays it out (src/runtime.rs:99-181: `kv_indptr` [batch + 1]
+    into `kv_indices` [pages of all sequences]); pages are handed out in a shuffled order so that the
+    indirection is real. Every step looks its pages up (a gather of the sequence's pages) and writes
+    the new token's K and V into slot `pos % page_size` of page `kv_indices[kv_indptr[b] + pos // page_size]`."""
 
     def __init__(self, cfg: HybridConfig, gen, dev, max_len):
         h, qh, kvh, d = cfg.hidden, cfg.q_heads, cfg.kv_heads, cfg.head_dim
@@ -116,8 +124,17 @@ class _Attention:
         self.w_qg = _normal((2 * qh * d, h), 0.02, gen, dev)       # query and output gate
         self.w_kv = _normal((2 * kvh * d, h), 0.02, gen, dev)
         self.w_o = _normal((h, qh * d), 0.02, gen, dev)
-        self.k_cache = _normal((cfg.batch, kvh, max_len, d), 1.0, gen, dev)   # the prefilled context
-        self.v_cache = _normal((cfg.batch, kvh, max_len, d), 1.0, gen, dev)
+        self.page = cfg.page_size
+        self.pages_per_seq = (max_len + self.page - 1) // self.page
+        pages = cfg.batch * self.pages_per_seq
+        self.kv_indptr = torch.arange(cfg.batch + 1, device=dev, dtype=torch.int32) * self.pages_per_seq
+        self.kv_indices = torch.randperm(pages, generator=gen, device=dev).to(torch.int32)
+        self.k_pool = _normal((pages, kvh, self.page, d), 1.0, gen, dev)      # holds the prefilled context
+        self.v_pool = _normal((pages, kvh, self.page, d), 1.0, gen, dev)
+        self.heads = torch.arange(kvh, device=dev)
+        # the pages a decode run writes into (those that hold positions >= context), for snapshots
+        first = cfg.context // self.page
+        self.decode_pages = self.kv_indices.view(cfg.batch, self.pages_per_seq)[:, first:].reshape(-1).long()
         inv = 1.0 / (10000.0 ** (torch.arange(0, cfg.rotary_dim, 2, device=dev, dtype=torch.float32) / cfg.rotary_dim))
         ang = torch.arange(max_len, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
         self.cos, self.sin = ang.cos(), ang.sin()                   # [max_len, rotary_dim / 2]
@@ -138,12 +155,18 @@ class _Attention:
         k, v = kv[:, 0], kv[:, 1]
         norm = lambda t: (t.float() * torch.rsqrt(t.float().pow(2).mean(-1, keepdim=True) + cfg.eps)).to(t.dtype)
         q, k = self._rope(norm(q), pos), self._rope(norm(k), pos)
-        self.k_cache.index_copy_(2, pos, k.unsqueeze(2))
-        self.v_cache.index_copy_(2, pos, v.unsqueeze(2))
+        # page table of the batch (every sequence has the same length here, so the CSR rows form a matrix)
+        table = self.kv_indices.view(b, self.pages_per_seq).long()
+        page_of_pos = table.index_select(1, pos // self.page)         # [b, 1]
+        slot = (pos % self.page).view(1, 1)
+        self.k_pool.index_put_((page_of_pos, self.heads.view(1, kvh), slot), k)
+        self.v_pool.index_put_((page_of_pos, self.heads.view(1, kvh), slot), v)
         group = qh // kvh                                           # query heads per kv head share its K and V
         qv = q.reshape(b * kvh, group, d)
-        kc = self.k_cache.view(b * kvh, -1, d)
-        vc = self.v_cache.view(b * kvh, -1, d)
+        gather = lambda pool: (pool.index_select(0, table.reshape(-1))
+                               .view(b, self.pages_per_seq, kvh, self.page, d).permute(0, 2, 1, 3, 4)
+                               .reshape(b * kvh, self.pages_per_seq * self.page, d))
+        kc, vc = gather(self.k_pool), gather(self.v_pool)
         scores = torch.bmm(qv, kc.transpose(1, 2)).float() * (1.0 / math.sqrt(d)) + mask   # [b*kvh, group, L]
         probs = torch.softmax(scores, dim=-1).to(x.dtype)
         out = torch.bmm(probs, vc).view(b, qh, d) * torch.sigmoid(gate.float()).to(x.dtype)
@@ -224,7 +247,9 @@ class HybridDecoder:
             # static buffers of a step
             self.tokens = torch.randint(0, cfg.vocab, (b,), generator=gen, device=dev)
             self.pos = torch.full((1,), cfg.context, dtype=torch.long, device=dev)
-            self.mask = torch.full((1, 1, self.max_len), float("-inf"), device=dev)
+            # one entry per cache slot of a sequence's pages (the tail past max_len stays masked)
+            slots = (self.max_len + cfg.page_size - 1) // cfg.page_size * cfg.page_size
+            self.mask = torch.full((1, 1, slots), float("-inf"), device=dev)
             self.mask[..., : cfg.context] = 0.0
             self.x = torch.empty((b, h), dtype=torch.bfloat16, device=dev)
             self.residual = torch.empty((b, h), dtype=torch.bfloat16, device=dev)
@@ -314,30 +339,34 @@ class HybridDecoder:
     # ---- decode state (for repeatable runs) ---------------------------------------------
 
     def _state_tensors(self):
-        """(tensor, is_kv_cache) of everything a step changes besides its scratch buffers."""
-        out = [(self.tokens, False), (self.pos, False), (self.mask, False)]
+        """(tensor, pages) of everything a step changes besides its scratch buffers; `pages` is None
+        or, for a KV-cache page pool, the ids of the pages a decode run writes into."""
+        out = [(self.tokens, None), (self.pos, None), (self.mask, None)]
         for m in self.mixers:
             if isinstance(m, _Attention):
-                out += [(m.k_cache, True), (m.v_cache, True)]
+                out += [(m.k_pool, m.decode_pages), (m.v_pool, m.decode_pages)]
             else:
-                out += [(m.conv_state, False), (m.state, False)]
+                out += [(m.conv_state, None), (m.state, None)]
         return out
 
     def snapshot(self):
-        """Copies of the state tensors (of a KV cache only the rows a decode run writes). Runs on
+        """Copies of the state tensors (of a KV cache only the pages a decode run writes). Runs on
         the decode stream, which does not synchronise with the default stream."""
         snap = [self.position]
         with torch.cuda.stream(self.stream):
-            for t, kv in self._state_tensors():
-                snap.append(t[:, :, self.cfg.context:].clone() if kv else t.clone())
+            for t, pages in self._state_tensors():
+                snap.append(t.clone() if pages is None else t.index_select(0, pages))
         self.stream.synchronize()
         return snap
 
     def restore(self, snap):
         self.position = snap[0]
         with torch.cuda.stream(self.stream):
-            for (t, kv), s in zip(self._state_tensors(), snap[1:]):
-                (t[:, :, self.cfg.context:] if kv else t).copy_(s)
+            for (t, pages), s in zip(self._state_tensors(), snap[1:]):
+                if pages is None:
+                    t.copy_(s)
+                else:
+                    t.index_copy_(0, pages, s)
         self.stream.synchronize()
 
     # ---- measurement ------------------------------------------------------------------------
@@ -365,7 +394,7 @@ class HybridDecoder:
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=HybridConfig.new_tokens)
     ap.add_argument("--layers", type=int, default=HybridConfig.layers)
     ap.add_argument("--batch", type=int, default=HybridConfig.batch)
     ap.add_argument("--context", type=int, default=HybridConfig.context)

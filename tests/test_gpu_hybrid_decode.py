@@ -98,3 +98,36 @@ def test_library_only_graph_and_timing_helpers(oracle):
         assert torch.equal(a, b)
     assert cfg.moe_weight_bytes_per_layer() == int((cfg.experts * 3 * cfg.inter * cfg.hidden
                                                     + 3 * cfg.shared_inter * cfg.hidden) * 9 / 16)
+
+
+def test_paged_kv_cache_is_addressed_through_its_page_table():
+    """Moving every page of the pool somewhere else and updating the page table accordingly must not
+    change what the attention stand-in computes (bit for bit), and a step writes the new token's K / V
+    into exactly one slot: page `kv_indices[kv_indptr[b] + pos // page_size]`, slot `pos % page_size`."""
+    from qs3_b200.hybrid_decode import _Attention, tiny_config
+    cfg = tiny_config(new_tokens=8, page_size=16)
+    dev = torch.device("cuda", 0)
+    max_len = cfg.context + cfg.new_tokens
+    a = _Attention(cfg, torch.Generator(device=dev).manual_seed(1), dev, max_len)
+    b = _Attention(cfg, torch.Generator(device=dev).manual_seed(1), dev, max_len)
+    pages = a.k_pool.shape[0]
+    assert a.kv_indptr.tolist() == [i * a.pages_per_seq for i in range(cfg.batch + 1)]
+    assert sorted(a.kv_indices.tolist()) == list(range(pages)) and a.kv_indices.tolist() != list(range(pages))
+    move = torch.randperm(pages, generator=torch.Generator(device=dev).manual_seed(2), device=dev)
+    b.k_pool = torch.empty_like(a.k_pool).index_copy_(0, move, a.k_pool)     # page i now lives at move[i]
+    b.v_pool = torch.empty_like(a.v_pool).index_copy_(0, move, a.v_pool)
+    b.kv_indices = move[a.kv_indices.long()].to(torch.int32)
+    slots = a.pages_per_seq * a.page
+    mask = torch.full((1, 1, slots), float("-inf"), device=dev)
+    mask[..., : cfg.context + 1] = 0.0
+    x = (torch.randn((cfg.batch, cfg.hidden), device=dev) * 0.5).to(torch.bfloat16)
+    pos = torch.full((1,), cfg.context, dtype=torch.long, device=dev)
+    k_before = a.k_pool.clone()
+    out_a, out_b = a(x, pos, mask), b(x, pos, mask)
+    assert torch.equal(out_a, out_b)
+    changed = (a.k_pool != k_before).flatten(1).any(dim=1).nonzero().flatten().tolist()
+    table = a.kv_indices.view(cfg.batch, a.pages_per_seq)
+    assert sorted(changed) == sorted(table[:, cfg.context // a.page].tolist())
+    page0 = int(table[0, cfg.context // a.page])
+    diff = (a.k_pool[page0] != k_before[page0]).any(dim=-1)                  # [kv_heads, page]
+    assert diff[:, cfg.context % a.page].all() and int(diff.sum()) == cfg.kv_heads
