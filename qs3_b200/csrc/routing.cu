@@ -757,16 +757,24 @@ template <typename T> T* carve(char* base, size_t& offset, size_t count)
 // read only when one of the token's routes targets one of its experts, so pairs
 // (token, rank) without a route cost no traffic. Same summation order and roundings as
 // exchanging the partial sums first and then running combine_kernel on the copies.
-__global__ void __launch_bounds__(256) ep_pull_combine_kernel(EpPullParams p)
+// Four tokens per block, 64 threads (two warps) per token: the kernel is bound by the latency of its
+// dependent loads (ids -> which ranks -> peer rows over NVLink), so what matters is how many tokens
+// are in flight per SM; with a block per token 4096 tokens took 3.5 waves of ~8 us.
+constexpr uint32_t kEpTokensPerBlock = 4;
+
+__global__ void __launch_bounds__(64 * kEpTokensPerBlock) ep_pull_combine_kernel(EpPullParams p)
 {
-    __shared__ uint32_t s_active;
-    __shared__ float s_dot[8];
-    const uint32_t token = blockIdx.x;
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ uint32_t s_active[kEpTokensPerBlock];
+    __shared__ float s_dot[kEpTokensPerBlock][2];
+    const uint32_t slot = threadIdx.x >> 6;           // token of the block
+    const uint32_t tid = threadIdx.x & 63;            // thread of the token
+    const uint32_t lane = threadIdx.x & 31, half = tid >> 5;
+    const uint32_t token = blockIdx.x * kEpTokensPerBlock + slot;
+    const bool live = token < p.num_tokens;
     const uint32_t vec_per_row = p.hidden_size / 8;
 
     // which ranks hold a partial sum for this token
-    if (threadIdx.x < 32) {
+    if (live && half == 0) {
         uint32_t mine = 0;
         if (lane < p.top_k) {
             const int id = p.topk_ids[static_cast<size_t>(token) * p.top_k + lane];
@@ -775,13 +783,13 @@ __global__ void __launch_bounds__(256) ep_pull_combine_kernel(EpPullParams p)
         }
         const uint32_t any = __reduce_or_sync(0xffffffffu, mine);
         if (lane == 0)
-            s_active = any;
+            s_active[slot] = any;
     }
     float dot = 0.0f;
-    if (p.shared_out != nullptr) {
+    if (live && p.shared_out != nullptr) {
         const uint4* x = reinterpret_cast<const uint4*>(p.hidden) + static_cast<size_t>(token) * vec_per_row;
         const uint4* w = reinterpret_cast<const uint4*>(p.gate_w);
-        for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
+        for (uint32_t i = tid; i < vec_per_row; i += 64) {
             const uint4 xv = x[i], wv = w[i];
             const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
             const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
@@ -795,25 +803,26 @@ __global__ void __launch_bounds__(256) ep_pull_combine_kernel(EpPullParams p)
         for (int o = 16; o > 0; o >>= 1)
             dot += __shfl_xor_sync(0xffffffffu, dot, o);
         if (lane == 0)
-            s_dot[warp] = dot;
+            s_dot[slot][half] = dot;
     }
     __syncthreads();
-    const uint32_t active = s_active;
+    if (!live)
+        return;
+    const uint32_t active = s_active[slot];
     float gate = 0.0f;
-    if (p.shared_out != nullptr) {
-        dot = 0.0f;
-        for (uint32_t w = 0; w < blockDim.x / 32; ++w)
-            dot += s_dot[w];
-        gate = sigmoid_fast(dot);
-    }
+    if (p.shared_out != nullptr)
+        gate = sigmoid_fast(s_dot[slot][0] + s_dot[slot][1]);
 
     const size_t row = static_cast<size_t>(p.my_rank) * p.num_tokens + token;
     uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
-    for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
+    for (uint32_t i = tid; i < vec_per_row; i += 64) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
             acc[j] = 0.0f;
+        uint4 sh = make_uint4(0, 0, 0, 0);
+        if (p.shared_out != nullptr)
+            sh = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
         // the peer loads of up to eight ranks are issued together: NVLink latency overlaps
         for (uint32_t r0 = 0; r0 < p.num_ranks; r0 += 8) {
             uint4 v[8];
@@ -838,8 +847,7 @@ __global__ void __launch_bounds__(256) ep_pull_combine_kernel(EpPullParams p)
             }
         }
         if (p.shared_out != nullptr) {
-            const uint4 s = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
-            const uint32_t ss[4] = { s.x, s.y, s.z, s.w };
+            const uint32_t ss[4] = { sh.x, sh.y, sh.z, sh.w };
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 acc[2 * j] += gate * bf16_bits_to_f32(ss[j] & 0xffffu);
@@ -885,8 +893,8 @@ cudaError_t launch_ep_pull_combine(const EpPullParams& p, cudaStream_t stream)
 {
     if (p.num_tokens == 0)
         return cudaSuccess;
-    const uint32_t threads = std::min(256u, std::max(32u, (p.hidden_size / 8 + 31) / 32 * 32));
-    ep_pull_combine_kernel<<<p.num_tokens, threads, 0, stream>>>(p);
+    ep_pull_combine_kernel<<<(p.num_tokens + kEpTokensPerBlock - 1) / kEpTokensPerBlock, 64 * kEpTokensPerBlock, 0,
+                             stream>>>(p);
     note_launch();
     return cudaGetLastError();
 }
