@@ -355,6 +355,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         acc[G - 1][t] = fmaf(__uint_as_float(v[G - 1][t]), su * x, acc[G - 1][t]);
                 }
             }
+            if constexpr (GATED)
+                ok = group_all(1, 128, ok); // the four warps meet at barrier 1 below: stop together
             if (!ok)
                 break;
             const uint32_t f = fb * 128 + r;

@@ -424,8 +424,10 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             scale *= p.group_scale[expert];
         for (uint32_t nt = nt_begin + group; nt < nt_end; nt += 2) {
             const uint32_t use = (nt - nt_begin) >> 1;
-            const bool ready = __all_sync(
+            bool ready = __all_sync(
                 0xffffffffu, mbar_wait(&acc_full[group], use & 1, abort_flag, p.err, ERR_AS_ACC_FULL_WAIT));
+            if (!small_tile)
+                ready = group_all(1 + group, 128, ready); // the group meets at its barrier below: stop together
             if (!ready)
                 break;
             tc_fence_after();

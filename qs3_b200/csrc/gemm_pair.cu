@@ -220,6 +220,21 @@ __device__ __forceinline__ void tc_ld64(uint32_t taddr, uint32_t* r)
         : "memory");
 }
 
+// 64 accumulator values of one row -> 64 bf16 in row `r` of a 128-row x 128-byte staging sub-tile laid
+// out with the 128-byte swizzle the TMA store expects (16-byte chunk c of row r sits at chunk c ^ (r & 7)).
+__device__ __forceinline__ void stage_bf16_rows(const uint32_t (&v)[64], uint8_t* sub_tile, uint32_t r, float scale)
+{
+    uint8_t* row_smem = sub_tile + r * 128;
+#pragma unroll
+    for (uint32_t c = 0; c < 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            w[i] = pack_bf16x2(__uint_as_float(v[c * 8 + 2 * i]) * scale, __uint_as_float(v[c * 8 + 2 * i + 1]) * scale);
+        *reinterpret_cast<uint4*>(row_smem + ((c ^ (r & 7u)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 struct Unit {
     int expert;
     int row0;   // first padded row of the pair tile
@@ -332,7 +347,7 @@ template <bool GATED, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPgThreads, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                       const PairParams pp)
+                       const __grid_constant__ CUtensorMap map_o, const PairParams pp)
 {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
@@ -346,7 +361,9 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     uint8_t* a_panel = smem;
     uint8_t* sfa_stage = a_panel + kb_count * kTileBytes;
     uint8_t* ring = sfa_stage + kb_count * kSfBytes;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + stages * kPgStageBytes);
+    // bf16 output tiles leave through shared memory and TMA stores: four 128-row x 128-byte sub-tiles
+    uint8_t* staging = ring + stages * kPgStageBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + (GATED ? 0 : 4 * kTileBytes));
     uint64_t* empty_bar = full_bar + kPgSfbBufs;
     uint64_t* sf_ready = empty_bar + kPgSfbBufs;
     uint64_t* panel_full = sf_ready + kPgSfbBufs;          // per k block: A codes + A scales of both CTAs landed
@@ -356,6 +373,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     uint64_t* acc_empty = acc_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* go_flag = tmem_slot + 2; // plain tiles: the epilogue warps' common "carry on" decision
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -501,6 +519,25 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                             ph ^= 1;
                         }
                     }
+                }
+            }
+            // The ring can be issued to its end while the MMAs are still a few units behind (short
+            // units: fewer stages per unit than the ring holds); the panels of those last units are still
+            // to come, so keep feeding the panel stream until its last block is out.
+            uint64_t start = clock64();
+            uint32_t seen_no = p_no, seen_kb = p_kb;
+            while (ok && p_have) {
+                pump_panel();
+                if (p_no != seen_no || p_kb != seen_kb) { // progress: restart the clock
+                    seen_no = p_no;
+                    seen_kb = p_kb;
+                    start = clock64();
+                } else if (*abort_flag != 0) {
+                    break;
+                } else if (static_cast<uint64_t>(clock64()) - start > kWaitCycles) {
+                    *abort_flag = 1;
+                    atomicCAS(p.err, 0u, static_cast<uint32_t>(ERR_PG_PANEL_FREE));
+                    break;
                 }
             }
         }
@@ -673,7 +710,11 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 trace(tr && threadIdx.x == 0, 3, tile_no, 0);
                 const bool ready = __all_sync(
                     0xffffffffu, mbar_wait(acc_full, tile_no & 1, abort_flag, p.err, ERR_PG_ACC_FULL));
-                if (!ready) {
+                // Gated tiles use no block-wide barrier below, so a warp whose wait gave up may leave at once.
+                // Plain tiles synchronise the eight epilogue warps twice per tile: there the decision to
+                // stop is taken by one thread and read by all AFTER the first barrier, so that no warp can
+                // be left waiting at a barrier the others have walked away from.
+                if (GATED && !ready) {
                     ok = false;
                     break;
                 }
@@ -690,10 +731,14 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
                     for (int i = 0; i < 64; ++i)
                         vb[i] = va[i];
-                } else {
+                } else if (ready) {
                     tc_ld64(tmem_base + lane_base + half * 128, va);
                     tc_ld64(tmem_base + lane_base + half * 128 + 64, vb);
                     tc_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        va[i] = vb[i] = 0;
                 }
                 // the accumulator is in registers: hand it back before the arithmetic
                 tc_fence_before();
@@ -727,27 +772,45 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     *reinterpret_cast<uint32_t*>(p.out_sf + tiled_scale_offset(grow, 4ull * it, p.out_kgroups))
                         = sf_word;
                 } else {
-                    // plain tile, bf16 rows stored directly: columns [128 it, 128 it + 128)
-                    if (!row_ok)
-                        continue;
-                    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + grow * p.out_pitch + it * 128;
+                    // plain tile: bf16, staged in shared memory (128-byte swizzle) and written with TMA stores.
+                    // This warp holds columns [128 half, +128) of rows [32 quad, +32): sub-tiles 2 half and
+                    // 2 half + 1. Every row of the CTA's tile is written: rows past the segment's end are
+                    // padding rows of the same expert, rows past the tensor are clipped by the TMA unit. A CTA
+                    // without rows (the second CTA of a single) stores nothing.
+                    const bool store = my_nrows > 0;
+                    const bool issuer = warp == 0 && lane == 0;
+                    if (issuer) { // the previous tile's stores have finished reading the staging tiles
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        *go_flag = (ready && *abort_flag == 0) ? 1u : 0u;
+                    }
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (*go_flag == 0) {
+                        ok = false;
+                        break;
+                    }
+                    if (store) {
+                        stage_bf16_rows(va, staging + (2 * half) * kTileBytes, static_cast<uint32_t>(r), scale);
+                        stage_bf16_rows(vb, staging + (2 * half + 1) * kTileBytes, static_cast<uint32_t>(r), scale);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (issuer && store) {
+                        const int n0 = static_cast<int>(nt * kPgBN);
 #pragma unroll
-                    for (uint32_t c = 0; c < 8; ++c) {
-                        if (it * 128 + c * 16 >= p.n)
-                            break;
-                        const uint32_t* v = c < 4 ? va + c * 16 : vb + (c - 4) * 16;
-                        uint32_t w[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            w[i] = pack_bf16x2(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
-                        reinterpret_cast<uint4*>(o + c * 16)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        reinterpret_cast<uint4*>(o + c * 16)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        for (int sub = 0; sub < 4; ++sub)
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                             reinterpret_cast<uint64_t>(&map_o)),
+                                         "r"(smem_u32(staging + sub * kTileBytes)), "r"(n0 + sub * 64), "r"(my_row0)
+                                         : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 }
             }
         }
     }
 
+    if (!GATED && threadIdx.x == 0)
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // stores done before shared memory goes away
     tc_fence_before();
     cluster.sync(); // the pair's tensor memory is idle in both CTAs
     if (warp == 9) {
@@ -771,10 +834,10 @@ namespace {
 
 template <bool GATED, int EPI>
 cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa, const CUtensorMap& msb,
-                        PairParams pp, uint32_t max_units, cudaStream_t stream)
+                        const CUtensorMap& mo, PairParams pp, uint32_t max_units, cudaStream_t stream)
 {
     constexpr size_t kSmemBudget = 227 * 1024 - 1024 /* alignment slack */ - 512 /* barriers */;
-    const size_t panel = static_cast<size_t>(pp.tc.k_blocks) * (kTileBytes + kSfBytes);
+    const size_t panel = static_cast<size_t>(pp.tc.k_blocks) * (kTileBytes + kSfBytes) + (GATED ? 0 : 4 * kTileBytes);
     uint32_t stages = static_cast<uint32_t>((kSmemBudget - panel) / kPgStageBytes);
     stages = std::min<uint32_t>(stages, kPgSfbBufs);
     if (const char* v = std::getenv("QS3_PAIR_STAGES"))
@@ -797,7 +860,7 @@ cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUte
             configured[dev] = true;
     }
     const uint32_t clusters = std::max(1u, std::min(max_units, device_sm_count() / 2));
-    kernel<<<2 * clusters, kPgThreads, smem, stream>>>(ma, mb, msa, msb, pp);
+    kernel<<<2 * clusters, kPgThreads, smem, stream>>>(ma, mb, msa, msb, mo, pp);
     note_launch();
     return cudaGetLastError();
 }
@@ -877,8 +940,14 @@ cudaError_t launch_nvfp4_pair_gemm(const GemmProblem& g, cudaStream_t stream, co
     const uint32_t max_units = (g.tile_expert != nullptr ? g.max_tiles : static_cast<uint32_t>((g.a_rows + 255) / 256))
         * n_tiles;
     if (g.gated)
-        return launch_pair<true, EPI_SWIGLU_NVFP4>(ma, mb, msa, msb, pp, max_units, stream);
-    return launch_pair<false, EPI_STORE_BF16>(ma, mb, msa, msb, pp, max_units, stream);
+        return launch_pair<true, EPI_SWIGLU_NVFP4>(ma, mb, msa, msb, ma, pp, max_units, stream);
+    CUtensorMap mo;
+    if (!make_operand_map(&mo, false, g.out, g.n, g.a_rows, g.out_pitch_elems * 2, 128)) {
+        if (why != nullptr)
+            *why = "cuTensorMapEncodeTiled failed";
+        return cudaErrorInvalidValue;
+    }
+    return launch_pair<false, EPI_STORE_BF16>(ma, mb, msa, msb, mo, pp, max_units, stream);
 }
 
 } // namespace qs3

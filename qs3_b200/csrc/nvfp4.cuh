@@ -49,9 +49,11 @@ __device__ __forceinline__ uint8_t quantize_block16(const float* x, float g, uin
 #pragma unroll
     for (int i = 0; i < 16; ++i)
         amax = fmaxf(amax, fabsf(x[i]));
-    const uint8_t code = f32_to_e4m3_sat(__fdiv_rn(__fdiv_rn(amax, 6.0f), g));
+    // (x / 1 and 1 / s are spelled so that they cost less; both are the same correctly rounded values)
+    const float sixth = __fdiv_rn(amax, 6.0f);
+    const uint8_t code = f32_to_e4m3_sat(g == 1.0f ? sixth : __fdiv_rn(sixth, g));
     const float s = __fmul_rn(e4m3_to_f32(code), g);
-    const float inv = s > 0.0f ? __fdiv_rn(1.0f, s) : 0.0f;
+    const float inv = s > 0.0f ? __frcp_rn(s) : 0.0f;
     float q[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i)

@@ -252,8 +252,10 @@ gemm_nvfp4_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         uint32_t u = 0;
         for (uint32_t fb = fb0; fb < fb1; ++fb, ++u) {
             const uint32_t buf = u & 1;
-            const bool ready = __all_sync(
+            bool ready = __all_sync(
                 0xffffffffu, mbar_wait(&acc_full[buf], (u >> 1) & 1, abort_flag, p.err, ERR_SW_ACC_FULL_WAIT));
+            if constexpr (GATED)
+                ready = group_all(1, 128, ready); // the four warps meet at barrier 1 below: stop together
             if (!ready)
                 break;
             tc_fence_after();

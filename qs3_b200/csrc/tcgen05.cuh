@@ -132,6 +132,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// AND of `pred` over the `nthreads` threads that meet at named barrier `bar_id`, returned to all of
+// them. Epilogue warps that synchronise with each other per tile take their "stop, a wait gave up"
+// decision through this, so that no warp is left waiting at a barrier the others walked away from.
+__device__ __forceinline__ bool group_all(uint32_t bar_id, uint32_t nthreads, bool pred)
+{
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %3, 0;\n\t"
+                 "bar.red.and.pred p, %1, %2, q;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(r)
+                 : "r"(bar_id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
+                 : "memory");
+    return r != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1)
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
