@@ -207,8 +207,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // doubles the FLOP per streamed byte. Two 128-column accumulators in tensor memory
 // alternate, so the epilogue of column tile i overlaps the MMAs of tile i + 1.
 //
-//   TMEM: [0,128) acc 0 | [128,256) acc 1 | [256,384) A scales (k/64 * 4 columns) | [384,416) B scales
-//         (two 16-column buffers, alternating per k block)
+//   TMEM: [0,128) acc 0 | [128,256) acc 1 | [256,384) A scales (k/64 * 4 columns) | [384,512) B scales
+//         (16 columns per k block of every ring stage)
+//
+// The scale copies into tensor memory (tcgen05.cp) are issued by a warp of their own: as part of
+// the MMA thread's instruction stream each one stalls the tensor pipe for ~50 cycles (four of them
+// per k block cost as much as two of its four MMAs), from another thread they cost nothing. The
+// copier hands a stage's scales to the MMA thread through an mbarrier (tcgen05.commit); the scale
+// columns of a ring stage are free again when the stage itself has been refilled.
 //   smem: A panel k_blocks x 16 KB | A-scale staging k_blocks x 2 KB | ring of stages, each one or
 //         two k blocks of (16 KB B + 2 KB scales) | bf16 output: two 32 KB staging tiles
 //
@@ -221,7 +227,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 constexpr int kAsMaxKBlocks = 8;   // k <= 2048
 constexpr int kAsMaxStages = 8;
 constexpr uint32_t kSmallTileRows = 32; // bf16-output tiles with at most this many rows store them directly
-constexpr int kAsThreads = 320;    // warps 0-7 epilogue (two per TMEM lane quadrant), 8 producer, 9 MMA
+constexpr int kAsThreads = 352;    // warps 0-7 epilogue (two per TMEM lane quadrant), 8 producer, 9 MMA, 10 scale copier
 constexpr uint32_t kAsStageBytes = kTileBytes + kSfBytes;
 
 enum : uint32_t {
@@ -230,6 +236,7 @@ enum : uint32_t {
     ERR_AS_EMPTY_WAIT = 0x52000003u,
     ERR_AS_ACC_FULL_WAIT = 0x52000004u,
     ERR_AS_ACC_EMPTY_WAIT = 0x52000005u,
+    ERR_AS_SF_WAIT = 0x52000006u,
 };
 
 template <bool GATED, int EPI>
@@ -269,7 +276,9 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     uint64_t* acc_full = empty_bar + kAsMaxStages;
     uint64_t* acc_empty = acc_full + 2;
     uint64_t* panel_bar = acc_empty + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(panel_bar + 1);
+    uint64_t* sfa_ready = panel_bar + 1;
+    uint64_t* sf_ready = sfa_ready + 1;            // [kAsMaxStages]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_ready + kAsMaxStages);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5;
@@ -280,7 +289,9 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
+            mbar_init(&sf_ready[s], 1);
         }
+        mbar_init(sfa_ready, 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
             // one arrival per epilogue warp that reads the buffer (a group of four with TMA stores)
@@ -302,7 +313,7 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_sfa = tmem_base + 256;
-    const uint32_t tmem_sfb = tmem_base + 384; // two 16-column buffers, alternating per stage
+    const uint32_t tmem_sfb = tmem_base + 384; // 16 columns per k block of every ring stage
     const uint32_t stage_bytes = kbs * kAsStageBytes;   // kbs k-blocks of B codes, then their scales
     const uint32_t stages_per_tile = kb_count / kbs;
 
@@ -353,15 +364,10 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // ---------------------------------------------------------- MMA issuer --
         if (lane == 0) {
             constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
-            bool ok = mbar_wait<true>(panel_bar, 0, abort_flag, p.err, ERR_AS_PANEL_WAIT);
-            if (ok) {
-                tc_fence_after();
-                // A scales: one 512-byte tile per 64 k elements -> 4 TMEM columns each
-                for (uint32_t g = 0; g < kb_count * 4; ++g)
-                    tc_cp_scales(tmem_sfa + 4 * g, scale_desc(smem_u32(sfa_stage) + g * 512));
-            }
+            // the copier has put the A scales into tensor memory (which also means the A panel has landed)
+            bool ok = mbar_wait<true>(sfa_ready, 0, abort_flag, p.err, ERR_AS_PANEL_WAIT);
             const uint32_t a_addr = smem_u32(a_panel);
-            uint32_t s = 0, ph = 0, sf_flip = 0;
+            uint32_t s = 0, ph = 0;
             for (uint32_t nt = nt_begin; ok && nt < nt_end; ++nt) {
                 const uint32_t local = nt - nt_begin;
                 const uint32_t buf = local & 1;
@@ -373,7 +379,8 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + buf * kBN;
                 for (uint32_t st = 0; st < stages_per_tile; ++st) {
-                    if (!mbar_wait<true>(&full_bar[s], ph, abort_flag, p.err, ERR_AS_FULL_WAIT)) {
+                    // the stage's B scales are in tensor memory (the copier waited for the stage's loads)
+                    if (!mbar_wait<true>(&sf_ready[s], ph, abort_flag, p.err, ERR_AS_SF_WAIT)) {
                         ok = false;
                         break;
                     }
@@ -381,14 +388,7 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     const uint32_t sb = smem_u32(ring + s * stage_bytes);
                     for (uint32_t q = 0; q < kbs; ++q) {
                         const uint32_t kb = st * kbs + q;
-                        // B scales alternate between two TMEM buffers so that this copy does
-                        // not have to wait for the previous k-block's MMAs to finish reading
-                        const uint32_t sfb_cols = tmem_sfb + 16 * sf_flip;
-                        sf_flip ^= 1;
-                        const uint32_t sf_smem = sb + kbs * kTileBytes + q * kSfBytes;
-#pragma unroll
-                        for (uint32_t j = 0; j < 4; ++j)
-                            tc_cp_scales(sfb_cols + 4 * j, scale_desc(sf_smem + j * 512));
+                        const uint32_t sfb_cols = tmem_sfb + 16 * (s * kbs + q);
                         const uint64_t da = operand_desc(a_addr + kb * kTileBytes);
                         const uint64_t db = operand_desc(sb + q * kTileBytes);
 #pragma unroll
@@ -404,6 +404,40 @@ gemm_tc_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 }
                 if (ok)
                     tc_commit(&acc_full[buf]);
+            }
+        }
+    } else if (warp == 10) {
+        // -------------------------------------------------------- scale copier --
+        if (lane == 0) {
+            bool ok = mbar_wait<true>(panel_bar, 0, abort_flag, p.err, ERR_AS_PANEL_WAIT);
+            if (ok) {
+                tc_fence_after();
+                // A scales: one 512-byte tile per 64 k elements -> 4 TMEM columns each
+                for (uint32_t g = 0; g < kb_count * 4; ++g)
+                    tc_cp_scales(tmem_sfa + 4 * g, scale_desc(smem_u32(sfa_stage) + g * 512));
+                tc_commit(sfa_ready);
+            }
+            uint32_t s = 0, ph = 0;
+            for (uint32_t nt = nt_begin; ok && nt < nt_end; ++nt) {
+                for (uint32_t st = 0; st < stages_per_tile; ++st) {
+                    // the stage was refilled, so the MMAs that read its scale columns last time round are done
+                    if (!mbar_wait<true>(&full_bar[s], ph, abort_flag, p.err, ERR_AS_FULL_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sf_smem = smem_u32(ring + s * stage_bytes) + kbs * kTileBytes;
+                    for (uint32_t q = 0; q < kbs; ++q) {
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j)
+                            tc_cp_scales(tmem_sfb + 16 * (s * kbs + q) + 4 * j, scale_desc(sf_smem + q * kSfBytes + j * 512));
+                    }
+                    tc_commit(&sf_ready[s]);
+                    if (++s == stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
             }
         }
     } else if (EPI == EPI_STORE_BF16 && p.tma_store) {
@@ -656,7 +690,7 @@ cudaError_t launch_astat(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
     const uint32_t kbs = tp.k_blocks % 2 == 0 ? 2u : 1u;
     const size_t staging = tp.tma_store ? 4 * kTileBytes : 0;
     uint32_t stages = static_cast<uint32_t>((kSmemBudget - panel - staging) / (kbs * kAsStageBytes));
-    stages = std::min<uint32_t>(stages, kAsMaxStages);
+    stages = std::min<uint32_t>(stages, kAsMaxStages / kbs); // 16 scale columns per k block in flight, 128 in all
     const size_t smem = panel + staging + static_cast<size_t>(stages) * kbs * kAsStageBytes + 1024 + 512;
     auto kernel = gemm_tc_astat_kernel<GATED, EPI>;
     static bool configured[64] = {};
@@ -842,14 +876,15 @@ bool gemm_tc_supported(const GemmProblem& g)
     return g.k % 8 == 0;
 }
 
-bool make_scale_block_map(CUtensorMap* map, const void* base, uint64_t row_blocks, uint32_t kgroups)
+bool make_scale_block_map(CUtensorMap* map, const void* base, uint64_t row_blocks, uint32_t kgroups,
+                          uint32_t box_blocks)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr || row_blocks == 0 || kgroups < 4)
         return false;
     const cuuint64_t dims[3] = { 128, kgroups, row_blocks };
     const cuuint64_t strides[2] = { 512, static_cast<cuuint64_t>(kgroups) * 512 };
-    const cuuint32_t box[3] = { 128, 4, 2 };
+    const cuuint32_t box[3] = { 128, 4, box_blocks };
     const cuuint32_t estr[3] = { 1, 1, 1 };
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -858,14 +893,14 @@ bool make_scale_block_map(CUtensorMap* map, const void* base, uint64_t row_block
 }
 
 bool make_gated_weight_map(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t inter,
-                           uint64_t groups, uint64_t pitch_bytes)
+                           uint64_t groups, uint64_t pitch_bytes, uint32_t box_halves)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr || inter < 64 || groups == 0)
         return false;
     const cuuint64_t dims[3] = { inner_bytes, inter, 2 * groups };
     const cuuint64_t strides[2] = { pitch_bytes, inter * pitch_bytes };
-    const cuuint32_t box[3] = { 128, 64, 2 };
+    const cuuint32_t box[3] = { 128, 64, box_halves };
     const cuuint32_t estr[3] = { 1, 1, 1 };
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

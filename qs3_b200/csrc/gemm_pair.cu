@@ -820,15 +820,17 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
 }
 
+
 } // namespace
 
 // Map over a buffer of 512-byte scale tiles: [tiles, 128 x u32], box = `box_tiles` whole tiles.
 bool make_scale_tile_map(CUtensorMap* map, const void* base, uint64_t tiles, uint32_t box_tiles);
 // 3-D maps: scale tiles as [row blocks, k groups, 128 x u32] with a box of two row blocks x four k groups;
 // gated weights [groups * 2 halves, inter rows, k bytes] with a box of 64 gate rows + their 64 up rows.
-bool make_scale_block_map(CUtensorMap* map, const void* base, uint64_t row_blocks, uint32_t kgroups);
+bool make_scale_block_map(CUtensorMap* map, const void* base, uint64_t row_blocks, uint32_t kgroups,
+                          uint32_t box_blocks = 2);
 bool make_gated_weight_map(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t inter,
-                           uint64_t groups, uint64_t pitch_bytes);
+                           uint64_t groups, uint64_t pitch_bytes, uint32_t box_halves = 2);
 
 namespace {
 
