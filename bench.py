@@ -25,7 +25,8 @@ permute and combine kernels; `parity` is a sampled check of the timed layer's re
 against the CPU oracle (expert ids and permutation of all tokens bit for bit, outputs of a
 sample of tokens within tolerance), run once after the timed loops; `cpu_baseline`
 times the CPU oracle on a bounded sample of the same workload on this machine's host
-cores; `secondary` (N = 1) holds the decode workloads measured after the headline.
+cores; `secondary` (N = 1) holds the decode workloads measured after the headline: the two decode
+batches of one layer and the 48-layer hybrid decode loop (`qs3_b200/hybrid_decode.py`).
 
 `--impl reference` times the CPU oracle alone (the reference has no CPU MoE path of
 its own and its GPU path has no NVFP4 kernels, so the restated algorithm is the only
@@ -531,7 +532,26 @@ def secondary_workloads(ctx, args, hbm_gbs, peak_kind):
             torch.cuda.empty_cache()
         except Exception as exc:  # a secondary figure must not take the headline line with it
             out[key] = {"error": f"{type(exc).__name__}: {exc}"}
+    if not args.no_hybrid:
+        out["hybrid_decode"] = hybrid_decode_record()
     return out
+
+
+def hybrid_decode_record():
+    """The 48-layer hybrid decode loop around this library's MoE layer (batch 128, 4096-token context
+    in a paged KV cache, 256 generated tokens per sequence, 512 experts top-10 + shared expert, NVFP4):
+    tokens/s of the whole step and the share of it spent in this library's calls. The token mixers
+    are torch stand-ins, so the step time is not a model-speed claim; `library_ms_per_step` is."""
+    import torch
+    try:
+        from qs3_b200 import hybrid_decode
+        t0 = time.time()
+        rec = hybrid_decode.measure()
+        rec["wall_s"] = round(time.time() - t0, 1)
+        torch.cuda.empty_cache()
+        return rec
+    except Exception as exc:
+        return {"error": f"{type(exc).__name__}: {exc}"}
 
 
 class E2EPipeline:
@@ -707,9 +727,9 @@ class SingleGpuLayer:
             ceiling, ceiling_src = fallback_ceiling, "issue-loop probe of an earlier run on this pool"
         t_hbm, t_tensor = algo / (hbm_gbs * 1e9), flops / (ceiling * 1e12)
         tensor_bound = t_tensor > t_hbm
-        # DRAM bytes per launch: ncu measured dram read + write = 1.02 x the algorithmic bytes for these
-        # kernels on reduced cases of the same layer (profiles/), scaled here by the algorithmic bytes
-        traffic = 1.02 * algo
+        # DRAM bytes per launch: ncu's dram read + write over the algorithmic bytes, measured once per
+        # kernel on a reduced case of the same layer (profiles/), scaled here by the algorithmic bytes
+        traffic = TRAFFIC_RATIO[kernel] * algo
         out = {"bound": "tensor" if tensor_bound else "hbm",
                "achieved": tflops if tensor_bound else hbm_achieved,
                "peak": ceiling if tensor_bound else hbm_gbs,
@@ -761,7 +781,14 @@ class SingleGpuLayer:
         return out
 
 
-GATE_UP_KERNEL = "gemm_tc_astat_kernel<gated, swiglu_nvfp4>"
+# the library's own dispatch rule for the NVFP4 prefill gate_up GEMM (QS3_NVFP4_PAIR=0 selects the
+# single-CTA resident-A kernel); the bench workloads satisfy the pair kernel's shape rules
+GATE_UP_KERNEL = ("gemm_tc_astat_kernel<gated, swiglu_nvfp4>" if os.environ.get("QS3_NVFP4_PAIR") == "0"
+                  else "gemm_nvfp4_pair_kernel<gated, swiglu_nvfp4>")
+TRAFFIC_RATIO = {"gemm_nvfp4_pair_kernel<gated, swiglu_nvfp4>": 1.07,
+                 "gemm_tc_astat_kernel<gated, swiglu_nvfp4>": 1.02,
+                 "gemm_nvfp4_swap_kernel<gated>": 1.00,
+                 "gemm_fp8_kernel<16, gated>": 1.02}
 
 
 def main():
@@ -783,6 +810,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the sampled check against the CPU oracle")
     ap.add_argument("--no-secondary", action="store_true", help="N = 1: skip the decode workloads after the headline")
+    ap.add_argument("--no-hybrid", action="store_true",
+                    help="N = 1: skip the 48-layer hybrid decode loop among the secondary workloads (it holds "
+                         "about 50 GB of random weights and takes the longest to set up)")
     ap.add_argument("--min-seconds", type=float, default=0.5,
                     help="GPU time the back-to-back blocks of `--steps` steps must cover at least")
     ap.add_argument("--kernels-only", action="store_true",

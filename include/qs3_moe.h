@@ -414,7 +414,10 @@ qsfi_status qs3_fp8_quantize_act(qsfi_context* ctx, const qs3_fp8_quantize_act_d
 /* Routed experts on FP8 operands with precomputed routing: the FP8 sibling of
  * qsfi_moe_execute_nvfp4 (same roles of the tensors, same workspace query
  * qsfi_moe_workspace_size). SwiGLU output is re-quantised per token per 128
- * features before the down projection. */
+ * features before the down projection. No counterpart in the reference: its
+ * qsfi.h has no FP8 MoE entry (backends 1..3, qsfi.h:206-209), hence the qs3_
+ * prefix. The names qsfi_moe_execute_fp8 / qsfi_moe_fp8_execute_desc of earlier
+ * versions of this header stay as aliases. */
 typedef struct {
     qsfi_tensor2 hidden;               /* e4m3 [num_tokens, hidden] */
     qsfi_tensor2 hidden_scale;         /* f32 [num_tokens, hidden / 128] */
@@ -427,7 +430,9 @@ typedef struct {
     qsfi_tensor2 out;                  /* bf16 [num_tokens, hidden] */
     qsfi_tensor1 workspace;            /* u8 [>= qsfi_moe_workspace_size] */
     uint32_t num_tokens;
-} qsfi_moe_fp8_execute_desc;
+} qs3_moe_fp8_execute_desc;
+typedef qs3_moe_fp8_execute_desc qsfi_moe_fp8_execute_desc;
+qsfi_status qs3_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_fp8_execute_desc* desc);
 qsfi_status
 qsfi_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, const qsfi_moe_fp8_execute_desc* desc);
 

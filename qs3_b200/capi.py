@@ -352,6 +352,7 @@ _SIGNATURES = {
                                       _P(C.c_uint32)]),
     "qs3_fp8_quantize_weight": (C.c_int, [C.c_void_p, _P(Fp8QuantizeWeightDesc)]),
     "qs3_fp8_quantize_act": (C.c_int, [C.c_void_p, _P(Fp8QuantizeActDesc)]),
+    "qs3_moe_execute_fp8": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeFp8ExecuteDesc)]),
     "qsfi_moe_execute_fp8": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeFp8ExecuteDesc)]),
     "qs3_tensor_peak_probe": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, _P(C.c_double)]),
     "qs3_checkpoint_open": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_void_p)]),

@@ -1927,7 +1927,7 @@ qsfi_status qs3_fp8_quantize_act(qsfi_context* ctx, const qs3_fp8_quantize_act_d
                           "qs3_fp8_quantize_act");
 }
 
-qsfi_status qsfi_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, const qsfi_moe_fp8_execute_desc* desc)
+qsfi_status qs3_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, const qs3_moe_fp8_execute_desc* desc)
 {
     if (ctx == nullptr)
         return QSFI_STATUS_INVALID_ARGUMENT;
@@ -1936,7 +1936,7 @@ qsfi_status qsfi_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, c
         return set_invalid_arg(ctx, "plan/desc is null");
     const qsfi_moe_plan_desc& p = plan->desc;
     if (!is_fp8_plan(p))
-        return set_invalid_arg(ctx, "qsfi_moe_execute_fp8 requires an FP8 block-scaled MoE plan");
+        return set_invalid_arg(ctx, "qs3_moe_execute_fp8 requires an FP8 block-scaled MoE plan");
     qsfi_status status = activate_context(ctx);
     if (status != QSFI_STATUS_OK)
         return status;
@@ -2025,7 +2025,13 @@ qsfi_status qsfi_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, c
     cp.num_tokens = desc->num_tokens;
     cp.top_k = p.top_k;
     cp.hidden_size = p.hidden_size;
-    return set_cuda_error(ctx, launch_combine(cp, st), "qsfi_moe_execute_fp8");
+    return set_cuda_error(ctx, launch_combine(cp, st), "qs3_moe_execute_fp8");
+}
+
+// earlier name of the same entry point
+qsfi_status qsfi_moe_execute_fp8(qsfi_context* ctx, const qsfi_moe_plan* plan, const qsfi_moe_fp8_execute_desc* desc)
+{
+    return qs3_moe_execute_fp8(ctx, plan, desc);
 }
 
 } // extern "C"

@@ -392,6 +392,29 @@ class HybridDecoder:
         return ms
 
 
+def measure(steps: int | None = None, cfg: HybridConfig | None = None) -> dict:
+    """Build the decoder, time `steps` decoded tokens per sequence (default: the configuration's 256)
+    as CUDA-graph replays with and without the mixers, and return the record `main` prints."""
+    cfg = cfg or HybridConfig()
+    steps = cfg.new_tokens if steps is None else steps
+    model = HybridDecoder(cfg)
+    timed = min(steps, model.max_len - model.position - 3)
+    full = model.time_steps(steps, mixers=True)
+    lib = model.time_steps(steps, mixers=False)
+    err = model.ctx.read_device_error()
+    moe_bytes = cfg.moe_weight_bytes_per_layer() * cfg.layers
+    return {
+        "metric": "hybrid decode tokens/s (batch x steps / time), CUDA graph replay", "value": cfg.batch / (full * 1e-3),
+        "unit": "tokens/s", "ms_per_step": full, "library_ms_per_step": lib, "library_share": lib / full,
+        "library_calls": "rmsnorm, fused add+rmsnorm+NVFP4, MoE layer (+ residual add + next norm), LM head",
+        "moe_weight_bytes_per_step": moe_bytes, "moe_weight_stream_gbs": moe_bytes / (lib * 1e-3) / 1e9,
+        "mixers": f"torch stand-ins (gated attention over a paged KV cache, {cfg.page_size}-token pages behind a CSR "
+                  "page table; GatedDeltaNet recurrence)",
+        "config": {k: getattr(cfg, k) for k in ("layers", "hidden", "experts", "top_k", "inter", "shared_inter",
+                                                 "batch", "context", "vocab", "page_size")},
+        "steps": timed, "device_error": err, "data": "synthetic"}
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--steps", type=int, default=HybridConfig.new_tokens)
@@ -400,20 +423,7 @@ def main():
     ap.add_argument("--context", type=int, default=HybridConfig.context)
     args = ap.parse_args()
     cfg = HybridConfig(layers=args.layers, batch=args.batch, context=args.context)
-    model = HybridDecoder(cfg)
-    full = model.time_steps(args.steps, mixers=True)
-    lib = model.time_steps(args.steps, mixers=False)
-    err = model.ctx.read_device_error()
-    moe_bytes = cfg.moe_weight_bytes_per_layer() * cfg.layers
-    print(json.dumps({
-        "metric": "hybrid decode tokens/s (batch x steps / time), CUDA graph replay", "value": cfg.batch / (full * 1e-3),
-        "unit": "tokens/s", "ms_per_step": full, "library_ms_per_step": lib, "library_share": lib / full,
-        "library_calls": "rmsnorm, fused add+rmsnorm+NVFP4, MoE layer (+ residual add + next norm), LM head",
-        "moe_weight_bytes_per_step": moe_bytes, "moe_weight_stream_gbs": moe_bytes / (lib * 1e-3) / 1e9,
-        "mixers": "torch stand-ins (gated attention over a contiguous KV cache, GatedDeltaNet recurrence)",
-        "config": {k: getattr(cfg, k) for k in ("layers", "hidden", "experts", "top_k", "inter", "shared_inter",
-                                                 "batch", "context", "vocab")},
-        "steps": min(args.steps, cfg.new_tokens - 3), "device_error": err, "data": "synthetic"}))
+    print(json.dumps(measure(args.steps, cfg)))
 
 
 if __name__ == "__main__":

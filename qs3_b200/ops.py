@@ -423,7 +423,7 @@ def fp8_quantize_act(ctx: Context, x: torch.Tensor):
 
 def moe_execute_fp8(plan: MoePlan, hidden_codes, hidden_scale, topk_ids, topk_weights, gate_up: Fp8Weight,
                     down: Fp8Weight, out, workspace, num_tokens=None):
-    """``qsfi_moe_execute_fp8``: routed experts on FP8 block-scaled operands."""
+    """``qs3_moe_execute_fp8``: routed experts on FP8 block-scaled operands."""
     ctx = plan.ctx
     d = capi.MoeFp8ExecuteDesc()
     d.hidden = _desc(hidden_codes, 2, capi.DTYPE_FP8_E4M3)
@@ -437,7 +437,7 @@ def moe_execute_fp8(plan: MoePlan, hidden_codes, hidden_scale, topk_ids, topk_we
     d.out = _desc(out, 2)
     d.workspace = _desc(workspace, 1)
     d.num_tokens = hidden_codes.shape[0] if num_tokens is None else num_tokens
-    ctx.check(ctx._lib.qsfi_moe_execute_fp8(ctx.handle, plan.handle, C.byref(d)))
+    ctx.check(ctx._lib.qs3_moe_execute_fp8(ctx.handle, plan.handle, C.byref(d)))
 
 
 @dataclass

@@ -67,3 +67,46 @@ def test_static_route_sort_matches_existing_path_twice_in_a_row():
     with pytest.raises(ops.Qs3Error) as e:
         ops.route_sort_static(ctx, big[:4], big[:4].float(), 0, capi.ROUTE_SORT_STATIC_MAX_EXPERTS + 1)
     assert e.value.status == capi.STATUS_UNSUPPORTED and "1024 local experts" in e.value.message
+
+
+def test_static_route_sort_small_path_allocates_nothing():
+    """At most 1024 routes take the fused single-block kernel; then a larger problem follows, both
+    with caller-created outputs. Device memory as the driver reports it (free bytes) and as torch's
+    caching allocator holds it (reserved bytes) must not move across the calls: the entry point's
+    scratch lives inside the library and neither it nor the wrapper may allocate."""
+    from qs3_b200 import ops
+    ctx = ops.Context()
+    rng = np.random.default_rng(7)
+    problems = [dict(t=100, k=8, e=32, off=0, le=32), dict(t=2000, k=10, e=256, off=64, le=128)]
+    prepared = []
+    for p in problems:
+        ids = rng.integers(0, p["e"], size=(p["t"], p["k"]), dtype=np.int32)
+        w = rng.random((p["t"], p["k"]), dtype=np.float32)
+        want = _existing_tables(ops, ctx, ids, w, p["e"], p["off"], p["le"])
+        r = p["t"] * p["k"]
+        i32 = lambda n: torch.full((n,), -7, dtype=torch.int32, device="cuda")
+        out = (i32(p["le"]), i32(p["le"] + 1), i32(r), i32(r), torch.zeros(r, dtype=torch.float32, device="cuda"))
+        prepared.append((p, to_dev(ids), to_dev(w), want, out))
+    # the first call on a device resolves the scratch address (a symbol lookup, not an allocation);
+    # do it before the measurement so that the window below holds steady-state calls only
+    p, ids, w, _, out = prepared[0]
+    ops.route_sort_static(ctx, ids, w, p["off"], p["le"], out=out)
+    torch.cuda.synchronize()
+
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    for p, ids, w, _, out in prepared:
+        ops.route_sort_static(ctx, ids, w, p["off"], p["le"], out=out)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert torch.cuda.memory_reserved() == reserved_before
+    assert free_after == free_before
+
+    for p, _, _, want, out in prepared:
+        counts, indptr, route_rows, row_tokens, row_scales = (to_np(x) for x in out)
+        n = int(indptr[-1])
+        assert np.array_equal(counts, want[0])
+        assert np.array_equal(indptr, want[1])
+        assert np.array_equal(route_rows, want[2])
+        assert np.array_equal(row_tokens[:n], want[3])
+        assert np.array_equal(row_scales[:n], want[4])
