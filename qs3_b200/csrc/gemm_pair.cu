@@ -1,4 +1,4 @@
-// NVFP4 grouped GEMM on CTA pairs: D[256 rows, 256 columns] per tcgen05.mma.cta_group::2.
+// NVFP4 grouped GEMMs on CTA pairs: tcgen05.mma.cta_group::2 instructions of 256 rows.
 //
 // The resident-A kernel of gemm.cu streams all of an expert's weights through every SM
 // that holds one of its 128-row tiles, and the L2 -> SM path, not the tensor pipe, sets its
@@ -6,21 +6,29 @@
 //
 //   * each CTA keeps its own 128-row A panel (codes for the whole k <= 2048) in shared memory
 //     and its scales in tensor memory, as before;
-//   * per k block each CTA loads only HALF of the 256 weight rows of a column tile (128 rows x
-//     128 bytes) -- the instruction reads both halves, one from each CTA's shared memory -- so
-//     the weights cross L2 -> SM once per 256 token rows instead of once per 128;
-//   * the first CTA issues 256 x 256 instructions (kind::mxf4nvf4.block_scale, scale_vec::4X)
-//     for both; 256-column instructions reach a ~1.33x higher tensor-pipe ceiling than the
-//     128-column ones (6.6 vs 5.0 PFLOP/s measured with the issue-loop probe);
-//   * the weight-scale copies into tensor memory (tcgen05.cp) are issued by a thread of their
+//   * per k block each CTA loads only HALF of the weight rows of a column tile -- the instruction
+//     reads both halves, one from each CTA's shared memory -- so the weights cross L2 -> SM once
+//     per 256 token rows instead of once per 128;
+//   * the first CTA issues the instructions (kind::mxf4nvf4.block_scale, scale_vec::4X) for both;
+//   * the weight-scale copies into tensor memory (tcgen05.cp) are issued by threads of their
 //     own: issued by the MMA thread ahead of the MMAs that read them they stall the pipe for
-//     ~50 cycles each (measured: 740 -> 939 cycles per k block with four copies), issued from a
-//     second thread they cost nothing. The two threads hand scale buffers back and forth
-//     through mbarriers (tcgen05.commit);
-//   * a 256-column f32 accumulator plus resident scales leaves no room in the 512 tensor-memory
-//     columns for a second accumulator, so the epilogue warps first DRAIN the accumulator
-//     into registers (128 values per thread), hand it back to the MMA thread, and only then
-//     run SwiGLU + NVFP4 quantisation from registers while the next column tile's MMAs run.
+//     ~50 cycles each (measured: 740 -> 939 cycles per k block with four copies), issued from
+//     another thread they cost nothing. The threads hand scale buffers back and forth through
+//     mbarriers (tcgen05.commit).
+//
+// Two shapes (PairShape):
+//
+//   gated (gate_up + SwiGLU + NVFP4 re-quantisation): column tiles of 256 accumulator columns (128
+//     gate + 128 up features), 256 x 256 instructions, which reach a ~1.33x higher tensor-pipe ceiling
+//     than 128-column ones (6.6 vs 5.0 PFLOP/s measured with the issue-loop probe). A 256-column f32
+//     accumulator plus resident scales leaves no room in the 512 tensor-memory columns for a second
+//     one, so the epilogue warps first DRAIN the accumulator into registers (128 values per thread),
+//     hand it back to the MMA thread, and only then run SwiGLU + quantisation from registers while
+//     the next column tile's MMAs run.
+//   plain (down projection, bf16 out): column tiles of 128 columns and TWO accumulators. k is the
+//     intermediate size there, a column tile is eight instructions long, and the hand-over of a single
+//     accumulator would idle the pipe half of the time; the kernel is bound by its bf16 output, not by
+//     the instruction rate. Tiles leave through two shared-memory staging buffers and TMA stores.
 //
 // No load uses cluster multicast: every CTA issues plain cp.async.bulk.tensor loads into its
 // own shared memory (completion counted on the first CTA's barrier), so the kernel is fit
@@ -30,15 +38,16 @@
 // stride. An expert with an odd number of row tiles ends in a "single": the second CTA then
 // has no rows; it still provides its half of the weights.
 //
-//   warps 0-7  epilogue (two per tensor-memory lane quadrant: columns [0,128) / [128,256))
+//   warps 0-7  epilogue (two per tensor-memory lane quadrant, each half of the tile's columns)
 //   warp 8     TMA producer (weight ring and A panels)
-//   warp 9     MMA issuer (first CTA)     warps 10, 11  scale copiers (first CTA)
+//   warp 9     MMA issuer (first CTA)     warps 10, 11  scale copiers (first CTA; 11 only for 256 columns)
 //
-//   TMEM  [0,256) accumulator | [256,384) A scales (k/64 x 4 columns) | [384,512) four buffers of
-//         B scales (8 columns per 64 k elements, 32 per k block)
-//   smem  A panel k_blocks x 16 KB | A-scale staging k_blocks x 2 KB | ring of stages, each
-//         16 KB of weight codes + 4 KB of weight scales (both halves: every CTA needs the scales
-//         of all 256 columns)
+//   TMEM  gated: [0,256) accumulator | plain: [0,128) and [128,256) accumulators
+//         [256,384) A scales (k/64 x 4 columns) | [384,512) buffers of B scales, one per ring stage
+//         (4 columns per 128 weight rows and 64 k elements)
+//   smem  A panel k_blocks x 16 KB | A-scale staging k_blocks x 2 KB | ring of stages, each this CTA's
+//         half of the weight codes of a 256-element k block + the scales of ALL the tile's weight rows
+//         (gated 16 + 4 KB, plain 8 + 2 KB) | plain: two 32 KB bf16 staging buffers
 //
 // Every wait is bounded (tcgen05.cuh); on expiry the kernel records a code in the device
 // error word and leaves through the normal teardown.
@@ -56,11 +65,34 @@ namespace {
 using namespace tc;
 
 constexpr int kPgThreads = 384;
-constexpr uint32_t kPgBN = 256;
 constexpr uint32_t kPgMaxKBlocks = 8;
-constexpr uint32_t kPgSfbBufs = 4;
-constexpr uint32_t kPgStageBytes = kTileBytes + 2 * kSfBytes;
+constexpr uint32_t kPgMaxStages = 8;
 constexpr uint32_t kPgTmemCols = 512;
+
+// Shape of a column tile. Gated (gate_up) problems use 256-column instructions and ONE accumulator;
+// plain (down) problems use 128-column instructions and TWO accumulators: their k is short (the
+// intermediate size), so a column tile is only a few instructions long and the hand-over of a
+// single accumulator to the epilogue would idle the tensor pipe half of the time, while the
+// lower issue rate of the narrower instruction does not matter for a kernel bound by its output.
+template <bool GATED> struct PairShape {
+    static constexpr uint32_t kBN = GATED ? 256u : 128u;             // accumulator columns per column tile
+    static constexpr uint32_t kAccs = GATED ? 1u : 2u;               // accumulators in tensor memory
+    // k blocks (256 elements) per ring stage. Every tcgen05 instruction and every barrier wait costs the one
+    // issuing thread 50-100 cycles; with 128-column instructions (147 cycles of tensor pipe each) a stage of
+    // four instructions plus its commits and waits takes that thread longer than the pipe needs, so plain
+    // stages carry two k blocks (measured: down GEMM 0.150 -> 0.134 ms).
+    static constexpr uint32_t kKbs = GATED ? 1u : 2u;
+    // A panels in shared memory (and sets of A scales in tensor memory). Plain problems have a short k and
+    // keep two: the next unit's panel is loaded while the current unit runs. The gated panel (k = 2048:
+    // 128 KB) leaves room for one; it is refilled k block by k block behind the unit's last column tile.
+    static constexpr uint32_t kPanels = GATED ? 1u : 2u;
+    static constexpr uint32_t kKbCols = kBN / 8;                     // B-scale columns per k block (4 MMAs)
+    static constexpr uint32_t kSlotCols = kKbs * kKbCols;            // ... per ring stage
+    static constexpr uint32_t kSfbBufs = 128 / kSlotCols;            // ring stages the B-scale columns allow
+    static constexpr uint32_t kCodeBytes = kBN / 2 * 128;            // this CTA's half of the weight rows, one k block
+    static constexpr uint32_t kScaleBytes = kBN / 128 * kSfBytes;    // scales of all kBN weight rows, one k block
+    static constexpr uint32_t kStageBytes = kKbs * (kCodeBytes + kScaleBytes); // codes of all k blocks, then scales
+};
 
 enum : uint32_t {
     ERR_PG_PANEL_FREE = 0x54000001u,
@@ -110,7 +142,8 @@ struct PairParams {
     uint32_t force_splits;        // measurement only (QS3_PAIR_SPLITS): work units per pair tile, 0 = automatic
     uint32_t dbg;                 // measurement only (QS3_PAIR_DBG): 1 no epilogue arithmetic / stores,
                                   // 2 no accumulator drain either, 4 no MMAs, 8 no weight-scale copies,
-                                  // 16 no L2 prefetch, 32 record the stage trace (qs3_debug_pair_trace)
+                                  // 16 L2 prefetch of the next column tile, 32 record the stage trace
+                                  // (qs3_debug_pair_trace)
 };
 
 __device__ __forceinline__ uint32_t cluster_addr(const void* local, uint32_t cta_rank)
@@ -330,16 +363,17 @@ template <bool GATED>
 __device__ __forceinline__ Coords tile_coords(const TcParams& p, const PairParams& pp, int expert, uint32_t nt,
                                               uint32_t rank)
 {
+    using Shape = PairShape<GATED>;
     const uint32_t it = 2 * nt + rank;
     Coords c;
     if (GATED) {
         c.b1 = static_cast<int>(it * 64);
         c.b2 = 2 * expert;
     } else {
-        c.b1 = expert * static_cast<int>(p.b_rows) + static_cast<int>(it * 128);
+        c.b1 = expert * static_cast<int>(p.b_rows) + static_cast<int>(it * (Shape::kBN / 2));
         c.b2 = 0;
     }
-    c.sf2 = static_cast<int>(expert * (p.b_rows / 128) + 2 * nt);
+    c.sf2 = static_cast<int>(expert * (p.b_rows / 128) + (Shape::kBN / 128) * nt);
     return c;
 }
 
@@ -354,24 +388,31 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint32_t rank = cluster.block_rank();
     const TcParams& p = pp.tc;
     const uint32_t kb_count = p.k_blocks;
-    const uint32_t stages = pp.stages; // ring stages = weight-scale buffers in tensor memory (<= kPgSfbBufs)
+    using Shape = PairShape<GATED>;
+    constexpr uint32_t kPgBN = Shape::kBN;
+    constexpr uint32_t kAccs = Shape::kAccs;
+    constexpr uint32_t kPgStageBytes = Shape::kStageBytes;
+    constexpr uint32_t kKbs = Shape::kKbs;
+    const uint32_t stages = pp.stages; // ring stages = weight-scale buffers in tensor memory (<= Shape::kSfbBufs)
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t* a_panel = smem;
-    uint8_t* sfa_stage = a_panel + kb_count * kTileBytes;
-    uint8_t* ring = sfa_stage + kb_count * kSfBytes;
+    constexpr uint32_t nb = Shape::kPanels; // A panels in shared memory (unit i uses panel i % nb)
+    uint8_t* a_panel = smem;                                  // [nb][kb_count] 16 KB tiles
+    uint8_t* sfa_stage = a_panel + nb * kb_count * kTileBytes; // [nb][kb_count] 2 KB
+    uint8_t* ring = sfa_stage + nb * kb_count * kSfBytes;
     // bf16 output tiles leave through shared memory and TMA stores: four 128-row x 128-byte sub-tiles
     uint8_t* staging = ring + stages * kPgStageBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + (GATED ? 0 : 4 * kTileBytes));
-    uint64_t* empty_bar = full_bar + kPgSfbBufs;
-    uint64_t* sf_ready = empty_bar + kPgSfbBufs;
-    uint64_t* panel_full = sf_ready + kPgSfbBufs;          // per k block: A codes + A scales of both CTAs landed
-    uint64_t* panel_free = panel_full + kPgMaxKBlocks;     // per k block: the unit's last MMAs on it are done
-    uint64_t* sfa_ready = panel_free + kPgMaxKBlocks;      // per k block: A scales are in tensor memory
-    uint64_t* acc_full = sfa_ready + kPgMaxKBlocks;
-    uint64_t* acc_empty = acc_full + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    uint64_t* empty_bar = full_bar + kPgMaxStages;
+    uint64_t* sf_ready = empty_bar + kPgMaxStages;
+    // per panel and k block, index panel * kb_count + kb (nb * kb_count <= kPgMaxKBlocks):
+    uint64_t* panel_full = sf_ready + kPgMaxStages;        // A codes + A scales of both CTAs landed
+    uint64_t* panel_free = panel_full + kPgMaxKBlocks;     // the unit's last MMAs on it are done
+    uint64_t* sfa_ready = panel_free + kPgMaxKBlocks;      // A scales are in tensor memory
+    uint64_t* acc_full = sfa_ready + kPgMaxKBlocks;        // [kAccs]
+    uint64_t* acc_empty = acc_full + 2;                    // [kAccs]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     volatile uint32_t* go_flag = tmem_slot + 2; // plain tiles: the epilogue warps' common "carry on" decision
 
@@ -382,15 +423,17 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
-            mbar_init(&sf_ready[s], 2); // the two scale copiers
+            mbar_init(&sf_ready[s], kPgBN / 128); // one scale copier per 128 weight rows
         }
-        for (uint32_t kb = 0; kb < kb_count; ++kb) {
+        for (uint32_t kb = 0; kb < nb * kb_count; ++kb) {
             mbar_init(&panel_full[kb], 1);
             mbar_init(&panel_free[kb], 1);
             mbar_init(&sfa_ready[kb], 1);
         }
-        mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 16); // eight epilogue warps in each CTA
+        for (uint32_t b = 0; b < kAccs; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 16); // eight epilogue warps in each CTA
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -427,23 +470,31 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         // trails the previous unit's last column tile by one k block instead of waiting for its end. The
         // panel stream is polled, never waited for, so that it cannot hold up the ring.
         if (lane == 0) {
-            uint32_t p_unit = cluster_id, p_no = 0, p_kb = 0;
+            uint32_t p_unit = cluster_id, p_no = 0, p_kb = 0, p_slot0 = 0, p_par = 0;
             Unit pu;
             bool p_have = load_unit(pp, p_unit, sc, &pu);
             const auto pump_panel = [&]() {
-                while (p_have && mbar_test_wait(&panel_free[p_kb], (p_no & 1) ^ 1)) {
+                // panel p_no goes into buffer p_no % nb (first slot p_slot0), whose previous user was panel
+                // p_no - nb; p_par is the parity of (p_no / nb)
+                while (p_have && mbar_test_wait(&panel_free[p_slot0 + p_kb], p_par ^ 1)) {
                     const int my_row0 = pu.row0 + static_cast<int>(rank * 128);
+                    const uint32_t slot = p_slot0 + p_kb;
                     if (rank == 0)
-                        mbar_expect_tx(&panel_full[p_kb], (pu.nrows > 128 ? 2u : 1u) * (kTileBytes + kSfBytes));
+                        mbar_expect_tx(&panel_full[slot], (pu.nrows > 128 ? 2u : 1u) * (kTileBytes + kSfBytes));
                     if (pu.nrows > static_cast<int>(rank * 128)) {
-                        const uint32_t pbar = cluster_addr(&panel_full[p_kb], 0);
-                        tma_load_pair(a_panel + p_kb * kTileBytes, &map_a, pbar, static_cast<int>(p_kb) * 128, my_row0);
-                        tma_load_pair(sfa_stage + p_kb * kSfBytes, &map_sfa, pbar, 0,
+                        const uint32_t pbar = cluster_addr(&panel_full[slot], 0);
+                        tma_load_pair(a_panel + slot * kTileBytes, &map_a, pbar, static_cast<int>(p_kb) * 128, my_row0);
+                        tma_load_pair(sfa_stage + slot * kSfBytes, &map_sfa, pbar, 0,
                                       static_cast<int>((my_row0 >> 7) * pp.sfa_tiles_per_block + 4 * p_kb));
                     }
                     if (++p_kb == kb_count) {
                         p_kb = 0;
                         ++p_no;
+                        p_slot0 += kb_count;
+                        if (p_slot0 == nb * kb_count) {
+                            p_slot0 = 0;
+                            p_par ^= 1;
+                        }
                         p_unit += clusters;
                         p_have = load_unit(pp, p_unit, sc, &pu);
                     }
@@ -489,7 +540,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         ahead = tile_coords<GATED>(p, pp, next.expert, next.nt_begin, rank);
                     else
                         pf = false;
-                    for (uint32_t kb = 0; kb < kb_count; ++kb) {
+                    for (uint32_t kb0 = 0; kb0 < kb_count; kb0 += kKbs) {
                         if (!wait_slot(&empty_bar[s], ph ^ 1)) {
                             ok = false;
                             break;
@@ -499,18 +550,23 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         if (rank == 0)
                             mbar_expect_tx(&full_bar[s], 2 * kPgStageBytes);
                         const uint32_t fbar = cluster_addr(&full_bar[s], 0);
-                        const int c0 = static_cast<int>(kb) * 128;
-                        if (GATED)
-                            tma_load_pair_3d(sb, &map_b, fbar, c0, cur.b1, cur.b2);
-                        else
-                            tma_load_pair(sb, &map_b, fbar, c0, cur.b1);
-                        tma_load_pair_3d(sb + kTileBytes, &map_sfb, fbar, 0, static_cast<int>(4 * kb), cur.sf2);
-                        if (pf) {
+#pragma unroll
+                        for (uint32_t q = 0; q < kKbs; ++q) {
+                            const uint32_t kb = kb0 + q;
+                            const int c0 = static_cast<int>(kb) * 128;
                             if (GATED)
-                                tma_prefetch_3d(&map_b, c0, ahead.b1, ahead.b2);
+                                tma_load_pair_3d(sb + q * Shape::kCodeBytes, &map_b, fbar, c0, cur.b1, cur.b2);
                             else
-                                tma_prefetch_2d(&map_b, c0, ahead.b1);
-                            tma_prefetch_3d(&map_sfb, 0, static_cast<int>(4 * kb), ahead.sf2);
+                                tma_load_pair(sb + q * Shape::kCodeBytes, &map_b, fbar, c0, cur.b1);
+                            tma_load_pair_3d(sb + kKbs * Shape::kCodeBytes + q * Shape::kScaleBytes, &map_sfb, fbar, 0,
+                                             static_cast<int>(4 * kb), cur.sf2);
+                            if (pf) {
+                                if (GATED)
+                                    tma_prefetch_3d(&map_b, c0, ahead.b1, ahead.b2);
+                                else
+                                    tma_prefetch_2d(&map_b, c0, ahead.b1);
+                                tma_prefetch_3d(&map_sfb, 0, static_cast<int>(4 * kb), ahead.sf2);
+                            }
                         }
                         trace(tr, 0, tsi++, 1);
                         pump_panel();
@@ -546,23 +602,27 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         // tcgen05.cp costs its issuing thread 50-70 cycles apiece; the eight copies of a stage's B scales
         // (plus four of A scales in a unit's first column tile) from one thread take longer than the
         // stage's four MMAs, so the two 128-row halves of the B scales have a copier thread each.
-        if (rank == 0 && lane == 0) {
+        if (kPgBN == 256 && rank == 0 && lane == 0) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
             Unit un;
             for (uint32_t u = cluster_id; ok && load_unit(pp, u, sc, &un); u += clusters) {
                 for (uint32_t nt = un.nt_begin; ok && nt < un.nt_end; ++nt) {
-                    for (uint32_t kb = 0; kb < kb_count; ++kb) {
+                    for (uint32_t kb0 = 0; kb0 < kb_count; kb0 += kKbs) {
                         if (!mbar_wait<true>(&full_bar[s], ph, abort_flag, p.err, ERR_PG_FULL)) {
                             ok = false;
                             break;
                         }
                         tc_fence_after();
-                        const uint32_t sf_smem = smem_u32(ring + s * kPgStageBytes) + kTileBytes + kSfBytes;
+                        // the second 128 weight rows of every k block of the stage
+                        const uint32_t sf_smem = smem_u32(ring + s * kPgStageBytes) + kKbs * Shape::kCodeBytes + kSfBytes;
                         if (!(pp.dbg & 8u)) {
 #pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j)
-                                cp_scales_pair(tmem_sfb + 32 * s + 8 * j + 4, scale_desc(sf_smem + j * 512));
+                            for (uint32_t q = 0; q < kKbs; ++q)
+#pragma unroll
+                                for (uint32_t j = 0; j < 4; ++j)
+                                    cp_scales_pair(tmem_sfb + Shape::kSlotCols * s + Shape::kKbCols * q + 8 * j + 4,
+                                                   scale_desc(sf_smem + q * Shape::kScaleBytes + j * 512));
                         }
                         commit_pair(cluster_addr(&sf_ready[s], 0));
                         if (++s == stages) {
@@ -585,20 +645,26 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             if (spans)
                 g_pair_spans[cluster_id * 3] = global_ns();
             for (uint32_t u = cluster_id; ok && load_unit(pp, u, sc, &un); u += clusters, ++unit_no) {
-                const bool more = u + clusters < total_units;
+                const bool more = u + nb * clusters < total_units; // a later unit of this cluster reuses the panel
+                const uint32_t pslot = (unit_no % nb) * kb_count;   // first barrier / tile / scale slot of the panel
                 for (uint32_t nt = un.nt_begin; ok && nt < un.nt_end; ++nt, ++tile_no) {
-                    if (!mbar_wait<true>(acc_empty, (tile_no & 1) ^ 1, abort_flag, p.err, ERR_PG_ACC_EMPTY)) {
+                    const uint32_t buf = tile_no % kAccs, use = tile_no / kAccs;
+                    if (!mbar_wait<true>(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.err, ERR_PG_ACC_EMPTY)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
+                    const uint32_t tmem_acc = tmem_base + buf * kPgBN;
                     const bool first = nt == un.nt_begin, last = nt + 1 == un.nt_end;
-                    for (uint32_t kb = 0; kb < kb_count; ++kb, ++sfi) {
+                    for (uint32_t kb0 = 0; kb0 < kb_count; kb0 += kKbs, ++sfi) {
                         trace(tr, 2, sfi, 0);
-                        // A scales of this k block (first column tile of a unit; implies the A codes landed)
-                        if (first && !mbar_wait<true>(&sfa_ready[kb], unit_no & 1, abort_flag, p.err, ERR_PG_SFA_READY)) {
-                            ok = false;
-                            break;
+                        // A scales of the stage's k blocks (first column tile of a unit; implies the A codes landed)
+                        if (first) {
+                            for (uint32_t q = 0; ok && q < kKbs; ++q)
+                                ok = mbar_wait<true>(&sfa_ready[pslot + kb0 + q], (unit_no / nb) & 1, abort_flag, p.err,
+                                                     ERR_PG_SFA_READY);
+                            if (!ok)
+                                break;
                         }
                         trace(tr, 2, sfi, 1);
                         // both copiers are done with the stage's B scales (they waited for the stage's loads)
@@ -608,18 +674,26 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         }
                         trace(tr, 2, sfi, 2);
                         tc_fence_after();
-                        const uint64_t da = operand_desc(a_addr + kb * kTileBytes);
-                        const uint64_t db = operand_desc(smem_u32(ring + s * kPgStageBytes));
                         if (!(pp.dbg & 4u)) {
 #pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j)
-                                mma_nvfp4_pair(tmem_base, da + 2 * j, db + 2 * j, kIdesc, (kb > 0 || j > 0) ? 1u : 0u,
-                                               tmem_sfa + 16 * kb + 4 * j, tmem_sfb + 32 * s + 8 * j);
+                            for (uint32_t q = 0; q < kKbs; ++q) {
+                                const uint32_t kb = kb0 + q;
+                                const uint64_t da = operand_desc(a_addr + (pslot + kb) * kTileBytes);
+                                const uint64_t db = operand_desc(smem_u32(ring + s * kPgStageBytes) + q * Shape::kCodeBytes);
+#pragma unroll
+                                for (uint32_t j = 0; j < 4; ++j)
+                                    mma_nvfp4_pair(tmem_acc, da + 2 * j, db + 2 * j, kIdesc, (kb > 0 || j > 0) ? 1u : 0u,
+                                                   tmem_sfa + 16 * (pslot + kb) + 4 * j,
+                                                   tmem_sfb + Shape::kSlotCols * s + Shape::kKbCols * q + (kPgBN / 32) * j);
+                            }
                         }
                         // the stage's shared memory and its scale buffer in tensor memory are free again
                         commit_both(&empty_bar[s]);
-                        if (last && more)
-                            commit_both(&panel_free[kb]);
+                        if (last && more) {
+#pragma unroll
+                            for (uint32_t q = 0; q < kKbs; ++q)
+                                commit_both(&panel_free[pslot + kb0 + q]);
+                        }
                         trace(tr, 2, sfi, 3);
                         if (++s == stages) {
                             s = 0;
@@ -627,7 +701,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         }
                     }
                     if (ok)
-                        commit_both(acc_full);
+                        commit_both(&acc_full[buf]);
                 }
             }
             if (spans) {
@@ -645,19 +719,25 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             Unit un;
             for (uint32_t u = cluster_id; ok && load_unit(pp, u, sc, &un); u += clusters, ++unit_no) {
                 for (uint32_t nt = un.nt_begin; ok && nt < un.nt_end; ++nt) {
-                    for (uint32_t kb = 0; kb < kb_count; ++kb, ++sfi) {
+                    for (uint32_t kb0 = 0; kb0 < kb_count; kb0 += kKbs, ++sfi) {
                         trace(tr, 1, sfi, 0);
                         if (nt == un.nt_begin) {
-                            if (!mbar_wait<true>(&panel_full[kb], unit_no & 1, abort_flag, p.err, ERR_PG_PANEL_FULL)) {
-                                ok = false;
-                                break;
-                            }
-                            tc_fence_after();
+                            for (uint32_t q = 0; ok && q < kKbs; ++q) {
+                                const uint32_t slot = (unit_no % nb) * kb_count + kb0 + q;
+                                if (!mbar_wait<true>(&panel_full[slot], (unit_no / nb) & 1, abort_flag, p.err,
+                                                     ERR_PG_PANEL_FULL)) {
+                                    ok = false;
+                                    break;
+                                }
+                                tc_fence_after();
 #pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j)
-                                cp_scales_pair(tmem_sfa + 16 * kb + 4 * j,
-                                               scale_desc(smem_u32(sfa_stage) + kb * kSfBytes + j * 512));
-                            commit_pair(cluster_addr(&sfa_ready[kb], 0));
+                                for (uint32_t j = 0; j < 4; ++j)
+                                    cp_scales_pair(tmem_sfa + 16 * slot + 4 * j,
+                                                   scale_desc(smem_u32(sfa_stage) + slot * kSfBytes + j * 512));
+                                commit_pair(cluster_addr(&sfa_ready[slot], 0));
+                            }
+                            if (!ok)
+                                break;
                         }
                         if (!mbar_wait<true>(&full_bar[s], ph, abort_flag, p.err, ERR_PG_FULL)) {
                             ok = false;
@@ -668,11 +748,14 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         // time round are done: the buffer may be overwritten)
                         trace(tr, 1, sfi, 2);
                         tc_fence_after();
-                        const uint32_t sf_smem = smem_u32(ring + s * kPgStageBytes) + kTileBytes;
+                        const uint32_t sf_smem = smem_u32(ring + s * kPgStageBytes) + kKbs * Shape::kCodeBytes;
                         if (!(pp.dbg & 8u)) {
 #pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j)
-                                cp_scales_pair(tmem_sfb + 32 * s + 8 * j, scale_desc(sf_smem + j * 512));
+                            for (uint32_t q = 0; q < kKbs; ++q)
+#pragma unroll
+                                for (uint32_t j = 0; j < 4; ++j)
+                                    cp_scales_pair(tmem_sfb + Shape::kSlotCols * s + Shape::kKbCols * q + (kPgBN / 32) * j,
+                                                   scale_desc(sf_smem + q * Shape::kScaleBytes + j * 512));
                         }
                         commit_pair(cluster_addr(&sf_ready[s], 0));
                         trace(tr, 1, sfi, 3);
@@ -690,7 +773,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         // 2 nt + w / 4: 64 gate columns then their 64 up columns
         const uint32_t quad = warp & 3, half = warp >> 2;
         const uint32_t lane_base = (quad * 32) << 16;
-        const uint32_t acc_empty_leader = cluster_addr(acc_empty, 0);
+        const uint32_t acc_empty_leader0 = cluster_addr(&acc_empty[0], 0);
+        const uint32_t acc_empty_leader1 = cluster_addr(&acc_empty[kAccs - 1], 0);
         uint32_t tile_no = 0;
         Unit un;
         bool ok = true;
@@ -708,8 +792,9 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                                                     : (p.group_scale != nullptr ? p.group_scale[un.expert] : 1.0f);
             for (uint32_t nt = un.nt_begin; nt < un.nt_end; ++nt, ++tile_no) {
                 trace(tr && threadIdx.x == 0, 3, tile_no, 0);
+                const uint32_t buf = tile_no % kAccs, use = tile_no / kAccs;
                 const bool ready = __all_sync(
-                    0xffffffffu, mbar_wait(acc_full, tile_no & 1, abort_flag, p.err, ERR_PG_ACC_FULL));
+                    0xffffffffu, mbar_wait(&acc_full[buf], use & 1, abort_flag, p.err, ERR_PG_ACC_FULL));
                 // Gated tiles use no block-wide barrier below, so a warp whose wait gave up may leave at once.
                 // Plain tiles synchronise the eight epilogue warps twice per tile: there the decision to
                 // stop is taken by one thread and read by all AFTER the first barrier, so that no warp can
@@ -720,31 +805,30 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
                 trace(tr && threadIdx.x == 0, 3, tile_no, 1);
                 tc_fence_after();
-                uint32_t va[64], vb[64];
-                if ((pp.dbg & 2u) || ((pp.dbg & 64u) && half == 1) || ((pp.dbg & 128u) && half == 0)) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        va[i] = vb[i] = 0;
-                } else if (pp.dbg & 256u) {
-                    tc_ld64(tmem_base + lane_base + half * 128, va);
-                    tc_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        vb[i] = va[i];
-                } else if (ready) {
-                    tc_ld64(tmem_base + lane_base + half * 128, va);
-                    tc_ld64(tmem_base + lane_base + half * 128 + 64, vb);
+                // gated: this warp's 128 columns (64 gate, 64 up); plain: its 64 of the tile's 128 columns
+                uint32_t va[64], vb[GATED ? 64 : 1];
+                const uint32_t acc_addr = tmem_base + buf * kPgBN + lane_base;
+                if (ready && !(pp.dbg & 2u)) {
+                    if constexpr (GATED) {
+                        tc_ld64(acc_addr + half * 128, va);
+                        tc_ld64(acc_addr + half * 128 + 64, vb);
+                    } else {
+                        tc_ld64(acc_addr + half * 64, va);
+                    }
                     tc_ld_wait();
                 } else {
 #pragma unroll
                     for (int i = 0; i < 64; ++i)
-                        va[i] = vb[i] = 0;
+                        va[i] = 0;
+#pragma unroll
+                    for (int i = 0; i < (GATED ? 64 : 1); ++i)
+                        vb[i] = 0;
                 }
                 // the accumulator is in registers: hand it back before the arithmetic
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0)
-                    mbar_arrive_cluster(acc_empty_leader);
+                    mbar_arrive_cluster(buf == 0 ? acc_empty_leader0 : acc_empty_leader1);
                 trace(tr && threadIdx.x == 0, 3, tile_no, 2);
                 const uint32_t it = 2 * nt + half; // 64 output features [64 it, 64 it + 64)
                 if (pp.dbg & 1u)
@@ -773,14 +857,15 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         = sf_word;
                 } else {
                     // plain tile: bf16, staged in shared memory (128-byte swizzle) and written with TMA stores.
-                    // This warp holds columns [128 half, +128) of rows [32 quad, +32): sub-tiles 2 half and
-                    // 2 half + 1. Every row of the CTA's tile is written: rows past the segment's end are
-                    // padding rows of the same expert, rows past the tensor are clipped by the TMA unit. A CTA
-                    // without rows (the second CTA of a single) stores nothing.
+                    // This warp holds columns [64 half, +64) of rows [32 quad, +32): sub-tile `half` of the
+                    // staging buffer that belongs to this accumulator. Every row of the CTA's tile is written:
+                    // rows past the segment's end are padding rows of the same expert, rows past the tensor are
+                    // clipped by the TMA unit. A CTA without rows (the second CTA of a single) stores nothing.
                     const bool store = my_nrows > 0;
                     const bool issuer = warp == 0 && lane == 0;
-                    if (issuer) { // the previous tile's stores have finished reading the staging tiles
-                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    uint8_t* stage_buf = staging + buf * 2 * kTileBytes;
+                    if (issuer) { // the stores of the tile before last have finished reading this staging buffer
+                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                         *go_flag = (ready && *abort_flag == 0) ? 1u : 0u;
                     }
                     asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -788,19 +873,17 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         ok = false;
                         break;
                     }
-                    if (store) {
-                        stage_bf16_rows(va, staging + (2 * half) * kTileBytes, static_cast<uint32_t>(r), scale);
-                        stage_bf16_rows(vb, staging + (2 * half + 1) * kTileBytes, static_cast<uint32_t>(r), scale);
-                    }
+                    if (store)
+                        stage_bf16_rows(va, stage_buf + half * kTileBytes, static_cast<uint32_t>(r), scale);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     asm volatile("bar.sync 1, 256;" ::: "memory");
                     if (issuer && store) {
                         const int n0 = static_cast<int>(nt * kPgBN);
 #pragma unroll
-                        for (int sub = 0; sub < 4; ++sub)
+                        for (int sub = 0; sub < 2; ++sub)
                             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                                              reinterpret_cast<uint64_t>(&map_o)),
-                                         "r"(smem_u32(staging + sub * kTileBytes)), "r"(n0 + sub * 64), "r"(my_row0)
+                                         "r"(smem_u32(stage_buf + sub * kTileBytes)), "r"(n0 + sub * 64), "r"(my_row0)
                                          : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
@@ -838,16 +921,21 @@ template <bool GATED, int EPI>
 cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa, const CUtensorMap& msb,
                         const CUtensorMap& mo, PairParams pp, uint32_t max_units, cudaStream_t stream)
 {
-    constexpr size_t kSmemBudget = 227 * 1024 - 1024 /* alignment slack */ - 512 /* barriers */;
-    const size_t panel = static_cast<size_t>(pp.tc.k_blocks) * (kTileBytes + kSfBytes) + (GATED ? 0 : 4 * kTileBytes);
+    constexpr size_t kSmemBudget = 227 * 1024 - 1024 /* alignment slack */ - 1024 /* barriers */;
+    constexpr uint32_t kPgStageBytes = PairShape<GATED>::kStageBytes;
+    const size_t one_panel = static_cast<size_t>(pp.tc.k_blocks) * (kTileBytes + kSfBytes);
+    const size_t staging = GATED ? 0 : 4 * kTileBytes;
+    const size_t panel = PairShape<GATED>::kPanels * one_panel + staging;
+    if (PairShape<GATED>::kPanels * pp.tc.k_blocks > kPgMaxKBlocks || panel + 2 * kPgStageBytes > kSmemBudget)
+        return cudaErrorInvalidConfiguration;
     uint32_t stages = static_cast<uint32_t>((kSmemBudget - panel) / kPgStageBytes);
-    stages = std::min<uint32_t>(stages, kPgSfbBufs);
+    stages = std::min<uint32_t>(stages, PairShape<GATED>::kSfbBufs);
     if (const char* v = std::getenv("QS3_PAIR_STAGES"))
         stages = std::max(2u, std::min<uint32_t>(stages, static_cast<uint32_t>(std::atoi(v))));
     if (stages < 2)
         return cudaErrorInvalidConfiguration;
     pp.stages = stages;
-    const size_t smem = panel + static_cast<size_t>(stages) * kPgStageBytes + 1024 + 512;
+    const size_t smem = panel + static_cast<size_t>(stages) * kPgStageBytes + 1024 + 1024;
     auto kernel = gemm_nvfp4_pair_kernel<GATED, EPI>;
     static bool configured[64] = {};
     int dev = 0;
@@ -883,7 +971,8 @@ bool nvfp4_pair_gemm_supported(const GemmProblem& g)
         return false;
     if (g.gated)
         return g.epilogue == EPI_SWIGLU_NVFP4 && g.n % 128 == 0;
-    return g.epilogue == EPI_STORE_BF16 && g.beta == 0.0f && g.n % 256 == 0
+    return g.epilogue == EPI_STORE_BF16 && g.beta == 0.0f && g.n % 128 == 0
+        && (g.k / 256) % PairShape<false>::kKbs == 0 && g.k <= 768 /* two panels + staging + a ring of two stages */
         && (reinterpret_cast<uintptr_t>(g.out) & 15u) == 0 && (g.out_pitch_elems * 2) % 16 == 0;
 }
 
@@ -917,7 +1006,7 @@ cudaError_t launch_nvfp4_pair_gemm(const GemmProblem& g, cudaStream_t stream, co
         return v != nullptr ? static_cast<uint32_t>(std::atoi(v)) : 0u;
     }();
     pp.dbg = dbg;
-    const uint32_t n_tiles = tp.b_rows / kPgBN;
+    const uint32_t n_tiles = tp.b_rows / (g.gated ? PairShape<true>::kBN : PairShape<false>::kBN);
     static const uint32_t force_splits = [] {
         const char* v = std::getenv("QS3_PAIR_SPLITS");
         return v != nullptr ? static_cast<uint32_t>(std::atoi(v)) : 0u;
@@ -931,9 +1020,11 @@ cudaError_t launch_nvfp4_pair_gemm(const GemmProblem& g, cudaStream_t stream, co
     const uint64_t sfb_tiles = static_cast<uint64_t>(g.groups) * pp.sfb_tiles_per_group;
     if (!make_operand_map(&ma, true, g.a, g.k / 2, g.a_rows, g.a_pitch_bytes, 128)
         || !(g.gated ? make_gated_weight_map(&mb, g.b, g.k / 2, g.n, g.groups, g.b_pitch_bytes)
-                     : make_operand_map(&mb, true, g.b, g.k / 2, b_total_rows, g.b_pitch_bytes, 128))
+                     : make_operand_map(&mb, true, g.b, g.k / 2, b_total_rows, g.b_pitch_bytes,
+                                        PairShape<false>::kBN / 2))
         || !make_scale_tile_map(&msa, g.a_scale_tiled, sfa_tiles, 4)
-        || !make_scale_block_map(&msb, g.b_scale_tiled, sfb_tiles / tp.kgroups, tp.kgroups)) {
+        || !make_scale_block_map(&msb, g.b_scale_tiled, sfb_tiles / tp.kgroups, tp.kgroups,
+                                 g.gated ? PairShape<true>::kBN / 128 : PairShape<false>::kBN / 128)) {
         if (why != nullptr)
             *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;
