@@ -243,6 +243,10 @@ struct GemmProblem {
     const float* group_scale_up; // gated: optional multiplier of the up rows (NULL: group_scale)
     const float* bias;          // optional f32 [n] (EPI_STORE_F32)
     float out_global_scale;     // EPI_SWIGLU_NVFP4: global scale of the quantised output
+    // optional scratch for split-k (dense bf16 problems with f32 output, few output tiles and a long k:
+    // router logits of a decode batch); NULL: never split
+    float* splitk_scratch;
+    size_t splitk_scratch_bytes;
 };
 // Chooses the tcgen05 kernel when the shape allows it and the plain CUDA-core
 // kernel otherwise (tiny or unaligned shapes; bf16 only).

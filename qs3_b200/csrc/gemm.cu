@@ -60,6 +60,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t nt = blockIdx.x;
     constexpr uint32_t kFeat = GATED ? kBN / 2 : kBN; // output features per tile
     const uint32_t n0 = nt * kFeat;
+    // the k blocks this CTA reduces (all of them unless the launch is split over grid.z)
+    const uint32_t kb_base = p.split_kb != 0 ? blockIdx.z * p.split_kb : 0u;
+    const uint32_t kb_count = p.split_kb != 0 ? min(p.split_kb, p.k_blocks - kb_base) : p.k_blocks;
 
     // ---- shared memory carve-up ----
     extern __shared__ uint8_t smem_raw[];
@@ -109,7 +112,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ? p.sfb + static_cast<uint64_t>(expert) * p.sfb_group_stride
                     + (static_cast<uint64_t>(nt) * p.kgroups) * 512
                 : nullptr;
-            for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+            for (uint32_t kb = 0; kb < kb_count; ++kb) {
                 const uint32_t s = kb % kStages;
                 const uint32_t ph = (kb / kStages) & 1;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, ERR_EMPTY_WAIT))
@@ -118,7 +121,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint8_t* sb = sa + kTileBytes;
                 mbar_expect_tx(&full_bar[s], kStageBytes);
                 // inner coordinate in elements of the map's type (bf16 elements / bytes)
-                const int c0 = static_cast<int>(kb) * (NVFP4 ? 128 : 64);
+                const int c0 = static_cast<int>(kb_base + kb) * (NVFP4 ? 128 : 64);
                 tma_load_2d(sa, &map_a, &full_bar[s], c0, row0);
                 if (GATED) {
                     tma_load_2d(sb, &map_b, &full_bar[s], c0, b_row);
@@ -128,9 +131,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tma_load_2d(sb, &map_b, &full_bar[s], c0, b_row);
                 }
                 if (NVFP4) {
-                    bulk_load(sb + kTileBytes, sfa_src + static_cast<uint64_t>(kb) * kSfBytes, kSfBytes,
+                    bulk_load(sb + kTileBytes, sfa_src + static_cast<uint64_t>(kb_base + kb) * kSfBytes, kSfBytes,
                               &full_bar[s]);
-                    bulk_load(sb + kTileBytes + kSfBytes, sfb_src + static_cast<uint64_t>(kb) * kSfBytes,
+                    bulk_load(sb + kTileBytes + kSfBytes, sfb_src + static_cast<uint64_t>(kb_base + kb) * kSfBytes,
                               kSfBytes, &full_bar[s]);
                 }
             }
@@ -143,7 +146,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ? ((1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24))
                 : ((1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24));
             bool ok = true;
-            for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+            for (uint32_t kb = 0; kb < kb_count; ++kb) {
                 const uint32_t s = kb % kStages;
                 const uint32_t ph = (kb / kStages) & 1;
                 if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, ERR_FULL_WAIT)) {
@@ -183,7 +186,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const bool ready = __all_sync(0xffffffffu, mbar_wait(acc_bar, 0, abort_flag, p.err, ERR_ACC_WAIT));
         tc_fence_after();
         if (ready) {
-            epilogue_tile<GATED, EPI>(p, tmem_base, warp, lane, expert, row0, nrows, nt);
+            epilogue_tile<GATED, EPI>(p, tmem_base, warp, lane, expert,
+                                      row0 + static_cast<int>(blockIdx.z * p.split_row_stride), nrows, nt);
         }
     }
 
@@ -791,6 +795,39 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ a, uint64_t a_pitch, const 
     }
 }
 
+// out[r, n] = alpha * sum over slices (in slice order) of partial[slice][r, n] + beta * out[r, n] + bias[n];
+// four features per thread. `partial` is [slices][rows_pad, n] f32, slice_stride elements apart.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, uint32_t slices, uint64_t slice_stride, uint64_t rows,
+                     uint32_t n, float* __restrict__ out, uint64_t out_pitch, float alpha, float beta,
+                     const float* __restrict__ bias)
+{
+    const uint64_t q = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint32_t per_row = n / 4;
+    if (q >= rows * per_row)
+        return;
+    const uint64_t r = q / per_row;
+    const uint32_t c = static_cast<uint32_t>(q % per_row) * 4;
+    float4 acc = *reinterpret_cast<const float4*>(partial + r * n + c);
+    for (uint32_t s = 1; s < slices; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(partial + s * slice_stride + r * n + c);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+    }
+    float* o = out + r * out_pitch + c;
+    float f[4] = { acc.x * alpha, acc.y * alpha, acc.z * alpha, acc.w * alpha };
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (beta != 0.0f)
+            f[i] += beta * o[i];
+        if (bias != nullptr)
+            f[i] += bias[c + i];
+        o[i] = f[i];
+    }
+}
+
 // Dense bf16 problem with f32 output whose rows would not fill one tensor-core tile.
 bool skinny_supported(const GemmProblem& g)
 {
@@ -993,8 +1030,43 @@ cudaError_t launch_gemm(const GemmProblem& g, cudaStream_t stream, const char** 
                 return launch_tc<false, true, EPI_SWIGLU_BF16>(ma, mb, tp, grid, stream);
             if (!g.gated && g.epilogue == EPI_STORE_BF16)
                 return launch_tc<false, false, EPI_STORE_BF16>(ma, mb, tp, grid, stream);
-            if (!g.gated && g.epilogue == EPI_STORE_F32)
+            if (!g.gated && g.epilogue == EPI_STORE_F32) {
+                // A handful of output tiles with a long k (router logits of a decode batch: 128 x 512 x 2048
+                // = four tiles) would stream all of k through four SMs: split k over grid.z, partial tiles
+                // into the caller's scratch, then one pass that sums the slices in slice order (so the
+                // result does not depend on timing) and applies alpha, beta and the bias.
+                const uint32_t tiles = grid.x * grid.y;
+                uint32_t splits = 1;
+                if (g.splitk_scratch != nullptr && g.tile_expert == nullptr && 8 * tiles <= sm_count()
+                    && tp.k_blocks >= 8) {
+                    splits = std::min<uint32_t>({ 8u, tp.k_blocks / 4, sm_count() / tiles });
+                    const size_t need = static_cast<size_t>(splits) * grid.y * kBM * g.n * sizeof(float);
+                    if (splits < 2 || need > g.splitk_scratch_bytes || !aligned16(g.splitk_scratch) || g.n % 4 != 0)
+                        splits = 1;
+                }
+                if (splits > 1) {
+                    TcParams ts = tp;
+                    ts.split_kb = (tp.k_blocks + splits - 1) / splits;
+                    splits = (tp.k_blocks + ts.split_kb - 1) / ts.split_kb;
+                    ts.split_row_stride = grid.y * kBM;
+                    ts.out = g.splitk_scratch;
+                    ts.out_pitch = g.n;
+                    ts.alpha = 1.0f;
+                    ts.beta = 0.0f;
+                    ts.bias = nullptr;
+                    grid.z = splits;
+                    cudaError_t err = launch_tc<false, false, EPI_STORE_F32>(ma, mb, ts, grid, stream);
+                    if (err != cudaSuccess)
+                        return err;
+                    const uint64_t quads = g.a_rows * (g.n / 4);
+                    splitk_reduce_kernel<<<static_cast<unsigned>((quads + 255) / 256), 256, 0, stream>>>(
+                        g.splitk_scratch, splits, static_cast<uint64_t>(ts.split_row_stride) * g.n, g.a_rows, g.n,
+                        static_cast<float*>(g.out), g.out_pitch_elems, g.alpha == 0.0f ? 1.0f : g.alpha, g.beta, g.bias);
+                    note_launch();
+                    return cudaGetLastError();
+                }
                 return launch_tc<false, false, EPI_STORE_F32>(ma, mb, tp, grid, stream);
+            }
         }
         if (why != nullptr)
             *why = "no tensor-core kernel for this operand/epilogue combination";

@@ -1213,6 +1213,13 @@ qsfi_status qs3_moe_layer_execute(qsfi_context* ctx, const qsfi_moe_plan* plan, 
     gl.epilogue = EPI_STORE_F32;
     gl.out = logits;
     gl.out_pitch_elems = p.num_experts;
+    // split-k scratch for decode-sized batches: the routed experts' output buffer, which nothing touches
+    // before the down projection (the side stream works on the shared expert's own buffers)
+    {
+        __nv_bfloat16* y2_buf = fp8 ? wf.y2 : nvfp4 ? wn.y2 : wb.y2;
+        gl.splitk_scratch = reinterpret_cast<float*>(y2_buf);
+        gl.splitk_scratch_bytes = static_cast<size_t>(rt.max_pad_rows) * p.hidden_size * sizeof(__nv_bfloat16);
+    }
     status = gemm_or_error(ctx, gl, "MoE router-logits GEMM");
     if (status != QSFI_STATUS_OK)
         return status;

@@ -29,14 +29,14 @@ __device__ __forceinline__ int local_expert(const int32_t* ids, uint32_t route, 
 // which is what makes the later placement stable.
 __device__ __forceinline__ void
 warp_histogram(const int32_t* ids, uint32_t routes, uint32_t local_offset, uint32_t experts,
-               uint16_t* s_hist)
+               uint16_t* s_hist, uint32_t chunk)
 {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (uint32_t i = threadIdx.x; i < kSortWarps * experts; i += blockDim.x)
         s_hist[i] = 0;
     __syncthreads();
     uint16_t* mine = s_hist + static_cast<size_t>(warp) * experts;
-    const uint32_t base = blockIdx.x * kSortChunk + warp * (kSortRounds * 32);
+    const uint32_t base = chunk * kSortChunk + warp * (kSortRounds * 32);
 #pragma unroll
     for (int r = 0; r < kSortRounds; ++r) {
         const int e = local_expert(ids, base + r * 32 + lane, routes, local_offset, experts);
@@ -50,15 +50,15 @@ warp_histogram(const int32_t* ids, uint32_t routes, uint32_t local_offset, uint3
 
 __device__ __forceinline__ void route_hist_body(const int32_t* __restrict__ ids, uint32_t routes,
                                                 uint32_t local_offset, uint32_t experts,
-                                                int32_t* __restrict__ block_hist, uint16_t* s_hist)
+                                                int32_t* __restrict__ block_hist, uint16_t* s_hist, uint32_t chunk)
 {
-    warp_histogram(ids, routes, local_offset, experts, s_hist);
+    warp_histogram(ids, routes, local_offset, experts, s_hist, chunk);
     for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
         int total = 0;
 #pragma unroll
         for (int w = 0; w < kSortWarps; ++w)
             total += s_hist[static_cast<size_t>(w) * experts + e];
-        block_hist[static_cast<size_t>(blockIdx.x) * experts + e] = total;
+        block_hist[static_cast<size_t>(chunk) * experts + e] = total;
     }
 }
 
@@ -67,7 +67,7 @@ route_hist_kernel(const int32_t* __restrict__ ids, uint32_t routes, uint32_t loc
                   uint32_t experts, int32_t* __restrict__ block_hist)
 {
     extern __shared__ uint16_t s_hist[];
-    route_hist_body(ids, routes, local_offset, experts, block_hist, s_hist);
+    route_hist_body(ids, routes, local_offset, experts, block_hist, s_hist, blockIdx.x);
 }
 
 // Single block: per expert, exclusive scan of the block histograms (column scan),
@@ -199,7 +199,7 @@ route_scan_kernel(int32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_
 __device__ __forceinline__ void route_place_body(const int32_t* __restrict__ ids,
                                                  const float* __restrict__ weights, uint32_t routes,
                                                  uint32_t top_k, uint32_t local_offset, uint32_t experts,
-                                                 const RouteTables& rt, uint16_t* s_hist)
+                                                 const RouteTables& rt, uint16_t* s_hist, uint32_t chunk)
 {
     // exclusive prefix over the warps of the block, per expert
     for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
@@ -215,8 +215,8 @@ __device__ __forceinline__ void route_place_body(const int32_t* __restrict__ ids
     __syncthreads();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint16_t* mine = s_hist + static_cast<size_t>(warp) * experts;
-    const uint32_t base = blockIdx.x * kSortChunk + warp * (kSortRounds * 32);
-    const int32_t* block_off = rt.block_hist + static_cast<size_t>(blockIdx.x) * experts;
+    const uint32_t base = chunk * kSortChunk + warp * (kSortRounds * 32);
+    const int32_t* block_off = rt.block_hist + static_cast<size_t>(chunk) * experts;
 #pragma unroll
     for (int r = 0; r < kSortRounds; ++r) {
         const uint32_t route = base + r * 32 + lane;
@@ -251,23 +251,28 @@ route_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ we
                    RouteTables rt)
 {
     extern __shared__ uint16_t s_hist[];
-    warp_histogram(ids, routes, local_offset, experts, s_hist);
-    route_place_body(ids, weights, routes, top_k, local_offset, experts, rt, s_hist);
+    warp_histogram(ids, routes, local_offset, experts, s_hist, blockIdx.x);
+    route_place_body(ids, weights, routes, top_k, local_offset, experts, rt, s_hist, blockIdx.x);
 }
 
-// All three steps in one block when the routes fit one block's chunk (decode batches):
-// the same arithmetic as the three kernels, without two launch boundaries.
+// All three steps in one block when the routes fit a few chunks (decode batches): the same
+// arithmetic as the three kernels, chunk after chunk, without two launch boundaries. The per-warp
+// histograms of every chunk stay in shared memory between the first and the last step.
+constexpr uint32_t kSmallSortChunks = 4;
 __global__ void __launch_bounds__(kSortWarps * 32)
 route_sort_small_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weights,
                         uint32_t routes, uint32_t top_k, uint32_t local_offset, uint32_t experts,
                         RouteTables rt)
 {
     extern __shared__ uint16_t s_hist[];
-    route_hist_body(ids, routes, local_offset, experts, rt.block_hist, s_hist);
+    const size_t per_chunk = static_cast<size_t>(kSortWarps) * experts;
+    for (uint32_t c = 0; c < rt.route_blocks; ++c)
+        route_hist_body(ids, routes, local_offset, experts, rt.block_hist, s_hist + c * per_chunk, c);
     __syncthreads(); // block_hist (global) is read back by this block
-    route_scan_body(rt.block_hist, 1, experts, rt);
-    __syncthreads(); // indptr / pad_indptr (global) are read back by this block
-    route_place_body(ids, weights, routes, top_k, local_offset, experts, rt, s_hist);
+    route_scan_body(rt.block_hist, rt.route_blocks, experts, rt);
+    __syncthreads(); // indptr / pad_indptr and the scanned block_hist (global) are read back by this block
+    for (uint32_t c = 0; c < rt.route_blocks; ++c)
+        route_place_body(ids, weights, routes, top_k, local_offset, experts, rt, s_hist + c * per_chunk, c);
 }
 
 // expanded[prow, :] = hidden[route / top_k, :]; one warp per route, 16-byte copies.
@@ -999,16 +1004,17 @@ cudaError_t launch_route_sort(const int32_t* topk_ids, const float* topk_weights
         if (err != cudaSuccess)
             return err;
     }
-    if (rt.route_blocks == 1) {
-        if (smem > 48 * 1024) {
+    if (rt.route_blocks <= kSmallSortChunks && rt.route_blocks * smem <= 96 * 1024) {
+        const size_t small_smem = rt.route_blocks * smem;
+        if (small_smem > 48 * 1024) {
             cudaError_t aerr = cudaFuncSetAttribute(route_sort_small_kernel,
                                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                    static_cast<int>(smem));
+                                                    static_cast<int>(96 * 1024));
             if (aerr != cudaSuccess)
                 return aerr;
         }
-        route_sort_small_kernel<<<1, kSortWarps * 32, smem, stream>>>(topk_ids, topk_weights, routes, top_k,
-                                                                     local_offset, experts, rt);
+        route_sort_small_kernel<<<1, kSortWarps * 32, small_smem, stream>>>(topk_ids, topk_weights, routes, top_k,
+                                                                           local_offset, experts, rt);
         note_launch();
         return cudaGetLastError();
     }

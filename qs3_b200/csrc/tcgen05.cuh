@@ -47,6 +47,10 @@ struct TcParams {
     float out_global;
     uint32_t* err;
     uint32_t tma_store; // resident-A kernel, bf16 output: stage the tile in smem and store it with TMA
+    // split-k launches of gemm_tc_kernel (grid.z slices): slice z reduces k blocks [z * split_kb, +split_kb)
+    // and writes its partial tile split_row_stride * z rows further down the output; 0: no split
+    uint32_t split_kb;
+    uint32_t split_row_stride;
 };
 
 // Host helpers defined beside the GEMM launchers. make_operand_map: 2-D tensor map over a

@@ -71,3 +71,23 @@ def test_expert_parallel_rank_batch_on_one_gpu(ops, oracle):
     """4096 tokens with all 512 experts local: the single-GPU base of the weak-scaling figure."""
     from qs3_b200 import workload
     _run_and_check(ops, workload.EP_NVFP4, sample=64, seed=2)
+
+
+@pytest.mark.parametrize("env", [{"QS3_NVFP4_PAIR_DOWN": "1"}, {"QS3_NVFP4_PAIR": "0"}],
+                         ids=["down_on_cta_pairs", "gate_up_on_single_ctas"])
+def test_alternative_grouped_kernels_keep_parity(env):
+    """The library picks its grouped NVFP4 kernels once per process from the environment: the
+    down projection can run on the CTA-pair kernel (128-column tiles, two accumulators) and
+    gate_up on the single-CTA resident-A kernel. Both are kept because they are the better
+    choice at other sizes; this runs the 4096-token check above in a child process with each
+    selection so that the paths that are not the default stay parity-green."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    child_env = dict(os.environ, **env)
+    cmd = [sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+           os.path.join(root, "tests", "test_gpu_parity_full.py") + "::test_expert_parallel_rank_batch_on_one_gpu"]
+    res = subprocess.run(cmd, cwd=root, env=child_env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+    assert "1 passed" in res.stdout
