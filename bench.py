@@ -342,6 +342,8 @@ def run_ours(args, rank, world, local_rank):
                                   balance_world=0 if args.placement == "contiguous" else world,
                                   hot_experts=0 if args.placement == "contiguous" else args.hot_experts)
         layer = ep.ExpertParallelLayer(ctx, data, rank, world)
+        if not args.no_graph and not args.kernels_only:
+            layer.try_capture()
 
     def barrier():
         if world > 1:

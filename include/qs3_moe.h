@@ -644,7 +644,10 @@ qsfi_status qs3_moe_ep_pull_routed(qsfi_context* ctx, const qs3_moe_ep_pull_rout
  * collective library: every rank owns a signal pad of num_ranks u32 words in peer-mapped memory
  * (zeroed once); the kernel stores `epoch` into its slot of every rank's pad and waits until every
  * slot of its own pad has reached `epoch` (plain release stores / acquire loads at system scope
- * over NVLink). `epoch` must grow by one with every barrier on the same pads. The wait is bounded:
+ * over NVLink). `epoch` must grow by one with every barrier on the same pads. With `epoch_counter`
+ * (a u32 in this rank's own device memory, zeroed once) the kernel takes epoch = counter + 1 and
+ * stores it back, so the launch carries no per-step argument and a whole step can be replayed from
+ * a CUDA graph; every rank must then run the same sequence of barriers. The wait is bounded:
  * after timeout_cycles SM clocks (0: about two seconds) the kernel records a code in the device
  * error word and returns, so a rank that died or never got here turns into
  * QSFI_STATUS_BACKEND_ERROR at the next qs3_moe_check_device_error instead of a hung GPU. */
@@ -652,8 +655,9 @@ typedef struct {
     const qsfi_device_ptr* pads; /* [num_ranks] rank r's pad as mapped on this device */
     uint32_t num_ranks;          /* <= 32 */
     uint32_t my_rank;
-    uint32_t epoch;
+    uint32_t epoch;              /* ignored when epoch_counter is set */
     uint64_t timeout_cycles;
+    qsfi_device_ptr epoch_counter; /* optional u32 [1], 4-byte aligned */
 } qs3_moe_ep_barrier_desc;
 qsfi_status qs3_moe_ep_barrier(qsfi_context* ctx, const qs3_moe_ep_barrier_desc* desc);
 

@@ -242,7 +242,7 @@ class MoeEpPullRoutedDesc(C.Structure):
 
 class MoeEpBarrierDesc(C.Structure):
     _fields_ = [("pads", _P(C.c_void_p)), ("num_ranks", C.c_uint32), ("my_rank", C.c_uint32),
-                ("epoch", C.c_uint32), ("timeout_cycles", C.c_uint64)]
+                ("epoch", C.c_uint32), ("timeout_cycles", C.c_uint64), ("epoch_counter", C.c_void_p)]
 
 
 class RmsnormDesc(C.Structure):

@@ -164,6 +164,7 @@ struct EpPullParams {
     const __nv_bfloat16* hidden;     // [T, H]
     const __nv_bfloat16* gate_w;     // [H]
     uint32_t num_tokens, top_k, hidden_size, num_ranks, my_rank, experts_per_rank;
+    uint32_t dbg; // measurement only (QS3_EP_FINISH_DBG): 1 read the own rank's partial sums only
 };
 cudaError_t launch_ep_pull_combine(const EpPullParams& p, cudaStream_t stream);
 struct EpPullTokensParams {
@@ -178,6 +179,7 @@ cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
 struct EpBarrierParams {
     uint32_t* pads[32];     // pads[r]: rank r's signal pad (num_ranks words) as mapped on this device
     uint32_t num_ranks, my_rank, epoch;
+    uint32_t* epoch_counter; // optional: epoch = *counter + 1, stored back by the kernel
     uint64_t limit_cycles;
     uint32_t* err;
 };

@@ -30,18 +30,26 @@ enum : uint32_t {
 __global__ void ep_barrier_kernel(EpBarrierParams p)
 {
     const uint32_t q = threadIdx.x;
+    // the epoch of this barrier: the caller's, or one more than the device-resident counter (every thread
+    // reads it before thread 0, the only writer, can have stored the new value)
+    uint32_t epoch = p.epoch;
+    if (p.epoch_counter != nullptr)
+        epoch = *reinterpret_cast<volatile uint32_t*>(p.epoch_counter) + 1u;
+    __syncwarp();
+    if (q == 0 && p.epoch_counter != nullptr)
+        *reinterpret_cast<volatile uint32_t*>(p.epoch_counter) = epoch;
     if (q >= p.num_ranks)
         return;
     __threadfence_system();
     uint32_t* remote = p.pads[q] + p.my_rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.epoch) : "memory");
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
     const uint32_t* mine = p.pads[p.my_rank] + q;
     const uint64_t start = clock64();
     uint32_t spins = 0;
     while (true) {
         uint32_t seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-        if (static_cast<int32_t>(seen - p.epoch) >= 0)
+        if (static_cast<int32_t>(seen - epoch) >= 0)
             return;
         if ((++spins & 15u) != 0)
             continue;
@@ -106,6 +114,9 @@ extern "C" qsfi_status qs3_moe_ep_barrier(qsfi_context* ctx, const qs3_moe_ep_ba
     p.num_ranks = d->num_ranks;
     p.my_rank = d->my_rank;
     p.epoch = d->epoch;
+    if (d->epoch_counter != nullptr && (reinterpret_cast<uintptr_t>(d->epoch_counter) & 3u) != 0)
+        return set_invalid_arg(ctx, "expert-parallel barrier: epoch_counter must be 4-byte aligned");
+    p.epoch_counter = static_cast<uint32_t*>(d->epoch_counter);
     p.limit_cycles = d->timeout_cycles != 0 ? d->timeout_cycles : 4000000000ull; // ~2 s of SM clocks
     p.err = device_error_word();
     return set_cuda_error(ctx, launch_ep_barrier(p, ctx->stream), "qs3_moe_ep_barrier");

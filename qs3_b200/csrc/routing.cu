@@ -4,6 +4,7 @@
 #include "common.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 #include <mutex>
 
@@ -767,7 +768,7 @@ template <typename T> T* carve(char* base, size_t& offset, size_t count)
 // are in flight per SM; with a block per token 4096 tokens took 3.5 waves of ~8 us.
 constexpr uint32_t kEpTokensPerBlock = 4;
 
-__global__ void __launch_bounds__(64 * kEpTokensPerBlock) ep_pull_combine_kernel(EpPullParams p)
+__global__ void __launch_bounds__(64 * kEpTokensPerBlock, 3) ep_pull_combine_kernel(EpPullParams p)
 {
     __shared__ uint32_t s_active[kEpTokensPerBlock];
     __shared__ float s_dot[kEpTokensPerBlock][2];
@@ -792,16 +793,26 @@ __global__ void __launch_bounds__(64 * kEpTokensPerBlock) ep_pull_combine_kernel
     }
     float dot = 0.0f;
     if (live && p.shared_out != nullptr) {
+        // gate logit: the row's loads are issued together (four chunks per thread and pass)
         const uint4* x = reinterpret_cast<const uint4*>(p.hidden) + static_cast<size_t>(token) * vec_per_row;
         const uint4* w = reinterpret_cast<const uint4*>(p.gate_w);
-        for (uint32_t i = tid; i < vec_per_row; i += 64) {
-            const uint4 xv = x[i], wv = w[i];
-            const uint32_t xs[4] = { xv.x, xv.y, xv.z, xv.w };
-            const uint32_t ws[4] = { wv.x, wv.y, wv.z, wv.w };
+        for (uint32_t i0 = tid; i0 < vec_per_row; i0 += 256) {
+            uint4 xv[4], wv[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                dot += bf16_bits_to_f32(xs[j] & 0xffffu) * bf16_bits_to_f32(ws[j] & 0xffffu);
-                dot += bf16_bits_to_f32(xs[j] >> 16) * bf16_bits_to_f32(ws[j] >> 16);
+            for (uint32_t c = 0; c < 4; ++c) {
+                const uint32_t i = i0 + 64 * c;
+                xv[c] = i < vec_per_row ? x[i] : make_uint4(0, 0, 0, 0);
+                wv[c] = i < vec_per_row ? w[i] : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) {
+                const uint32_t xs[4] = { xv[c].x, xv[c].y, xv[c].z, xv[c].w };
+                const uint32_t ws[4] = { wv[c].x, wv[c].y, wv[c].z, wv[c].w };
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    dot += bf16_bits_to_f32(xs[j] & 0xffffu) * bf16_bits_to_f32(ws[j] & 0xffffu);
+                    dot += bf16_bits_to_f32(xs[j] >> 16) * bf16_bits_to_f32(ws[j] >> 16);
+                }
             }
         }
 #pragma unroll
@@ -813,59 +824,89 @@ __global__ void __launch_bounds__(64 * kEpTokensPerBlock) ep_pull_combine_kernel
     __syncthreads();
     if (!live)
         return;
-    const uint32_t active = s_active[slot];
+    const uint32_t active = (p.dbg & 1u) ? (s_active[slot] & (1u << p.my_rank)) : s_active[slot];
     float gate = 0.0f;
     if (p.shared_out != nullptr)
         gate = sigmoid_fast(s_dot[slot][0] + s_dot[slot][1]);
 
     const size_t row = static_cast<size_t>(p.my_rank) * p.num_tokens + token;
     uint4* out = reinterpret_cast<uint4*>(p.out) + static_cast<size_t>(token) * vec_per_row;
-    for (uint32_t i = tid; i < vec_per_row; i += 64) {
-        float acc[8];
+    // A thread owns up to four 16-byte chunks of the row (hidden <= 2048) and keeps the loads of all of
+    // them, for two ranks at a time, in flight together: what bounds this kernel is the latency of the
+    // peer loads, so the number of dependent rounds (ranks / 2), not the bytes, sets its time. Ranks are
+    // added in ascending order.
+    constexpr uint32_t kChunks = 4;
+    for (uint32_t i0 = tid; i0 < vec_per_row; i0 += 64 * kChunks) {
+        float acc[kChunks][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            acc[j] = 0.0f;
-        uint4 sh = make_uint4(0, 0, 0, 0);
-        if (p.shared_out != nullptr)
-            sh = reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i];
-        // the peer loads of up to eight ranks are issued together: NVLink latency overlaps
-        for (uint32_t r0 = 0; r0 < p.num_ranks; r0 += 8) {
-            uint4 v[8];
+        for (uint32_t c = 0; c < kChunks; ++c)
 #pragma unroll
-            for (uint32_t q = 0; q < 8; ++q) {
-                const uint32_t r = r0 + q;
-                v[q] = (r < p.num_ranks && ((active >> r) & 1u))
-                    ? reinterpret_cast<const uint4*>(p.peer[r])[row * vec_per_row + i]
-                    : make_uint4(0, 0, 0, 0);
+            for (int j = 0; j < 8; ++j)
+                acc[c][j] = 0.0f;
+        // the shared expert's rows travel with the first round of partial sums
+        uint4 sh[kChunks];
+#pragma unroll
+        for (uint32_t c = 0; c < kChunks; ++c) {
+            const uint32_t i = i0 + 64 * c;
+            sh[c] = (p.shared_out != nullptr && i < vec_per_row)
+                ? reinterpret_cast<const uint4*>(p.shared_out)[static_cast<size_t>(token) * vec_per_row + i]
+                : make_uint4(0, 0, 0, 0);
+        }
+        uint32_t todo = active & (p.num_ranks >= 32 ? 0xffffffffu : (1u << p.num_ranks) - 1u);
+        while (todo != 0) {
+            const uint32_t ra = static_cast<uint32_t>(__ffs(static_cast<int>(todo))) - 1u;
+            todo &= todo - 1u;
+            const bool two = todo != 0;
+            const uint32_t rb = two ? static_cast<uint32_t>(__ffs(static_cast<int>(todo))) - 1u : ra;
+            todo &= todo - 1u; // no-op on zero
+            const uint4* pa = reinterpret_cast<const uint4*>(p.peer[ra]) + row * vec_per_row;
+            const uint4* pb = reinterpret_cast<const uint4*>(p.peer[rb]) + row * vec_per_row;
+            uint4 va[kChunks], vb[kChunks];
+#pragma unroll
+            for (uint32_t c = 0; c < kChunks; ++c) {
+                const uint32_t i = i0 + 64 * c;
+                va[c] = i < vec_per_row ? pa[i] : make_uint4(0, 0, 0, 0);
+                vb[c] = (two && i < vec_per_row) ? pb[i] : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
-            for (uint32_t q = 0; q < 8; ++q) {
-                const uint32_t r = r0 + q;
-                if (r >= p.num_ranks || !((active >> r) & 1u))
-                    continue;
-                const uint32_t vs[4] = { v[q].x, v[q].y, v[q].z, v[q].w };
+            for (uint32_t c = 0; c < kChunks; ++c) {
+                const uint32_t as[4] = { va[c].x, va[c].y, va[c].z, va[c].w };
+                const uint32_t bs[4] = { vb[c].x, vb[c].y, vb[c].z, vb[c].w };
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[2 * j] += bf16_bits_to_f32(vs[j] & 0xffffu);
-                    acc[2 * j + 1] += bf16_bits_to_f32(vs[j] >> 16);
+                    acc[c][2 * j] += bf16_bits_to_f32(as[j] & 0xffffu);
+                    acc[c][2 * j + 1] += bf16_bits_to_f32(as[j] >> 16);
+                }
+                if (two) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[c][2 * j] += bf16_bits_to_f32(bs[j] & 0xffffu);
+                        acc[c][2 * j + 1] += bf16_bits_to_f32(bs[j] >> 16);
+                    }
                 }
             }
         }
-        if (p.shared_out != nullptr) {
-            const uint32_t ss[4] = { sh.x, sh.y, sh.z, sh.w };
+#pragma unroll
+        for (uint32_t c = 0; c < kChunks; ++c) {
+            const uint32_t i = i0 + 64 * c;
+            if (i >= vec_per_row)
+                break;
+            if (p.shared_out != nullptr) {
+                const uint32_t ss[4] = { sh[c].x, sh[c].y, sh[c].z, sh[c].w };
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[c][2 * j] += gate * bf16_bits_to_f32(ss[j] & 0xffffu);
+                    acc[c][2 * j + 1] += gate * bf16_bits_to_f32(ss[j] >> 16);
+                }
+            }
+            uint32_t o[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                acc[2 * j] += gate * bf16_bits_to_f32(ss[j] & 0xffffu);
-                acc[2 * j + 1] += gate * bf16_bits_to_f32(ss[j] >> 16);
+                const __nv_bfloat162 r2 = __floats2bfloat162_rn(acc[c][2 * j], acc[c][2 * j + 1]);
+                o[j] = *reinterpret_cast<const uint32_t*>(&r2);
             }
+            out[i] = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        uint32_t o[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const __nv_bfloat162 r2 = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-            o[j] = *reinterpret_cast<const uint32_t*>(&r2);
-        }
-        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -894,10 +935,16 @@ __global__ void __launch_bounds__(256) ep_pull_tokens_kernel(EpPullTokensParams 
 
 } // namespace
 
-cudaError_t launch_ep_pull_combine(const EpPullParams& p, cudaStream_t stream)
+cudaError_t launch_ep_pull_combine(const EpPullParams& params, cudaStream_t stream)
 {
-    if (p.num_tokens == 0)
+    if (params.num_tokens == 0)
         return cudaSuccess;
+    EpPullParams p = params;
+    static const uint32_t dbg = [] {
+        const char* v = std::getenv("QS3_EP_FINISH_DBG");
+        return v != nullptr ? static_cast<uint32_t>(std::atoi(v)) : 0u;
+    }();
+    p.dbg = dbg;
     ep_pull_combine_kernel<<<(p.num_tokens + kEpTokensPerBlock - 1) / kEpTokensPerBlock, 64 * kEpTokensPerBlock, 0,
                              stream>>>(p);
     note_launch();

@@ -237,6 +237,8 @@ class ExpertParallelLayer:
                  dispatch="auto"):
         self.rank, self.world, self.group = rank, world, group
         self.barrier_timeout_cycles = 0          # library default (about two seconds of SM clocks)
+        self.graph = None                        # CUDA graph of one resident-input step (capture())
+        self.launches_per_step = 0
         self.data = data
         cfg = data.cfg
         self.cfg = cfg
@@ -281,7 +283,9 @@ class ExpertParallelLayer:
                 torch.cuda.synchronize(dev)
                 dist.barrier(group=group)        # every pad is zero before anybody signals
                 self._pads = [[b + offs[5] + 256 * ch for b in base] for ch in range(2)]
-                self._epoch = [0, 0]
+                # epochs are counted on the device (one word per channel), so a barrier launch has no
+                # per-step argument and the whole step can be replayed from a CUDA graph
+                self._epoch_dev = torch.zeros(2, dtype=torch.int32, device=dev)
                 if dispatch != "nccl" and hasattr(self.backend, "bind_route_outputs"):
                     seg = lambda j, dt, shape: self._sym[offs[j]:offs[j] + sizes[j]].view(dt).view(shape)
                     routed = dispatch != "gather" and h % 256 == 0 and h <= 2048
@@ -329,8 +333,8 @@ class ExpertParallelLayer:
     def _barrier(self, channel: int):
         """The library's barrier over the ranks' signal pads, on the current stream. Its wait is
         bounded: a rank that never arrives leaves an error code that ``check()`` raises."""
-        self._epoch[channel] += 1
-        ops.ep_barrier(self.ctx, self._pads[channel], self.rank, self._epoch[channel], self.barrier_timeout_cycles)
+        ops.ep_barrier(self.ctx, self._pads[channel], self.rank, 0, self.barrier_timeout_cycles,
+                       epoch_counter=self._epoch_dev[channel:channel + 1])
 
     def check(self):
         """Synchronise and raise if a bounded device-side wait of the steps so far expired."""
@@ -355,10 +359,58 @@ class ExpertParallelLayer:
         except RuntimeError as exc:
             raise ops.Qs3Error(capi.STATUS_BACKEND_ERROR, f"expert-parallel combine failed: {exc}") from exc
 
+    def capture(self):
+        """Record one resident-input step (this rank's share of it: its kernels, the peer loads and the
+        two barriers) in a CUDA graph. Eager, a step is about ten library calls of 30-40 us of host time
+        each, which is as long as the GPU work of a rank at 4 or 8 GPUs. Every rank must capture, and
+        every rank must then replay the same number of steps (the barriers count their epochs on the
+        device). Only the peer-load paths are capturable; with NCCL in the step this is a no-op."""
+        if not (self.cuda and self.combine_mode == "pull" and self.dispatch_mode == "pull") or self.graph is not None:
+            return
+        for _ in range(2):
+            self.step()
+        torch.cuda.synchronize()
+        before = ops.launch_count()
+        self.step()
+        self.launches_per_step = ops.launch_count() - before
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        graph = torch.cuda.CUDAGraph()
+        # thread-local capture mode: the process group's watchdog thread keeps querying its own events
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            self._step_eager(self.data.hidden, self.out)
+        self.ctx.use_current_stream()
+        self.graph = graph
+
+    def try_capture(self):
+        """``capture`` on every rank; falls back to eager launches on all ranks if any rank failed."""
+        ok = 1.0
+        try:
+            self.capture()
+        except Exception as exc:
+            import sys
+            print(f"rank {self.rank}: CUDA graph capture failed ({exc}); eager launches", file=sys.stderr)
+            ok = 0.0
+            torch.cuda.synchronize()
+        if self.cuda and self.world > 1:
+            flag = torch.tensor([ok], device=self.data.hidden.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            ok = float(flag.item())
+        if ok == 0.0:
+            self.graph = None
+            if self.ctx is not None and self.cuda:
+                self.ctx.use_current_stream()
+
     def step(self, hidden=None, out=None):
-        hidden = self.data.hidden if hidden is None else hidden
-        out = self.out if out is None else out
+        if self.graph is not None and hidden is None and out is None:
+            self.graph.replay()
+            return self.out
+        return self._step_eager(self.data.hidden if hidden is None else hidden, self.out if out is None else out)
+
+    def _step_eager(self, hidden, out):
         b = self.backend
+        if self.cuda and self.ctx is not None:
+            self.ctx.use_current_stream()
         packed, scale, ids, wts = b.route(hidden)
         if not self.cuda:
             self._dispatch(packed, scale, ids, wts)

@@ -540,12 +540,16 @@ STAGE_NAMES = {1: "router_logits_gemm", 2: "router_topk", 3: "route_sort", 4: "g
                5: "gate_up_gemm_swiglu", 6: "down_gemm", 7: "shared_expert", 8: "combine"}
 
 
-def ep_barrier(ctx: Context, pads, my_rank: int, epoch: int, timeout_cycles: int = 0):
+def ep_barrier(ctx: Context, pads, my_rank: int, epoch: int, timeout_cycles: int = 0, epoch_counter=None):
     """``qs3_moe_ep_barrier``: barrier over the ranks whose signal pads (device addresses as mapped
-    here, one per rank) are ``pads``; bounded wait, see ``Context.check_device_error``."""
+    here, one per rank) are ``pads``; bounded wait, see ``Context.check_device_error``. With
+    ``epoch_counter`` (an int32 / uint32 device tensor of one element, zeroed once) the kernel counts
+    the epochs itself, which makes the launch replayable from a CUDA graph."""
     d = capi.MoeEpBarrierDesc()
     arr = (C.c_void_p * len(pads))(*[int(p) for p in pads])
     d.pads, d.num_ranks, d.my_rank, d.epoch, d.timeout_cycles = arr, len(pads), my_rank, epoch & 0xFFFFFFFF, timeout_cycles
+    if epoch_counter is not None:
+        d.epoch_counter = epoch_counter.data_ptr()
     ctx.check(ctx._lib.qs3_moe_ep_barrier(ctx.handle, C.byref(d)))
 
 
