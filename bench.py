@@ -414,6 +414,10 @@ def run_ours(args, rank, world, local_rank):
         extra["efficiency_note"] = ("weak_base_ms = the single-GPU layer (all 512 experts local) on one rank's "
                                     "4096 tokens, max over ranks, same run; efficiency_same_tokens = weak_base_ms / "
                                     "ms_per_step")
+        extra["stage_ms_note"] = ("phases of a serialised pass of eager launches on rank 0 (ranks aligned by a "
+                                  "barrier before each pass): they include the host's launch gaps, which the "
+                                  "timed steps, replayed from a CUDA graph, do not have; 'experts/...' are the "
+                                  "library's own stage events inside the experts phase")
         del single, full
 
     total_tokens = cfg.tokens * world
@@ -804,7 +808,7 @@ def main():
                          "batch of the NVFP4 layer instead of the headline layer")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="N > 1: how the experts are assigned to ranks")
-    ap.add_argument("--hot-experts", type=int, default=16,
+    ap.add_argument("--hot-experts", type=int, default=32,
                     help="N > 1, balanced placement: replicate this many of the hottest experts on every rank")
     ap.add_argument("--no-graph", action="store_true",
                     help="N = 1: launch the resident-input steps eagerly instead of replaying one CUDA graph "

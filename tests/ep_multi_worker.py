@@ -53,10 +53,20 @@ def main():
     err = np.linalg.norm(f32(got) - want) / np.linalg.norm(want)
     assert err <= 1e-2, err
     assert np.max(np.abs(f32(got) - want)) <= 2.0 ** -5 * np.max(np.abs(want))
+    # the same step replayed from a CUDA graph (barrier epochs counted on the device): bit-identical
+    layer.try_capture()
+    graphed = layer.graph is not None
+    if layer.combine_mode == "pull" and layer.dispatch_mode == "pull":
+        assert graphed, "the peer-load step must be capturable"
+        for _ in range(3):
+            replayed = layer.step()
+        torch.cuda.synchronize()
+        layer.check()
+        assert np.array_equal(to_np(replayed), got), "graph replay differs from eager launches"
     dist.barrier()
     if rank == 0:
         print(f"EP_MULTI_OK world={world} rel_l2={err:.3e} combine={layer.combine_mode} balanced={bool(balance)} "
-              f"hot={hot}")
+              f"hot={hot} graph={graphed}")
     dist.destroy_process_group()
 
 
