@@ -1437,6 +1437,32 @@ qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const
         || (quantise && !aligned16(d->hidden_packed.data)))
         return set_invalid_arg(ctx, "MoE tensors must be 16-byte aligned");
 
+    // The token quantiser depends on the tokens only: it runs on the plan's side stream beside the
+    // router GEMM and the top-k and joins before the call returns its stream to the caller.
+    qs3_nvfp4_quantize_act_desc q {};
+    q.x = d->hidden;
+    q.packed = d->hidden_packed;
+    q.scale_linear = d->hidden_scale;
+    q.global_scale = d->act_global_scale;
+    q.rows = d->num_tokens;
+    cudaStream_t main_stream = ctx->stream;
+    const bool fork = quantise && !stage_recording() && plan_side_stream(plan);
+    if (fork) {
+        cudaError_t ferr = cudaEventRecord(plan->ev_fork, main_stream);
+        if (ferr == cudaSuccess)
+            ferr = cudaStreamWaitEvent(plan->side_stream, plan->ev_fork, 0);
+        if (ferr != cudaSuccess)
+            return set_cuda_error(ctx, ferr, "MoE route fork");
+        ctx->stream = plan->side_stream;
+        status = qs3_nvfp4_quantize_act(ctx, &q);
+        ctx->stream = main_stream;
+        if (status != QSFI_STATUS_OK)
+            return status;
+        ferr = cudaEventRecord(plan->ev_quant, plan->side_stream);
+        if (ferr != cudaSuccess)
+            return set_cuda_error(ctx, ferr, "MoE route fork");
+    }
+
     GemmProblem gl {};
     gl.a = d->hidden.data;
     gl.a_rows = d->num_tokens;
@@ -1465,15 +1491,10 @@ qsfi_status qs3_moe_ep_route(qsfi_context* ctx, const qsfi_moe_plan* plan, const
                                       p.local_num_experts, d->num_ranks, ctx->stream);
     if (err != cudaSuccess)
         return set_cuda_error(ctx, err, "MoE routing");
-    if (quantise) {
-        qs3_nvfp4_quantize_act_desc q {};
-        q.x = d->hidden;
-        q.packed = d->hidden_packed;
-        q.scale_linear = d->hidden_scale;
-        q.global_scale = d->act_global_scale;
-        q.rows = d->num_tokens;
+    if (fork)
+        return set_cuda_error(ctx, cudaStreamWaitEvent(main_stream, plan->ev_quant, 0), "MoE route join");
+    if (quantise)
         return qs3_nvfp4_quantize_act(ctx, &q);
-    }
     return QSFI_STATUS_OK;
 }
 
