@@ -765,6 +765,18 @@ qsfi_status qs3_moe_profile_end(
  * tensor-pipe fractions. */
 qsfi_status qs3_tensor_peak_probe(qsfi_context* ctx, uint32_t kind, uint32_t n, uint32_t iters, double* tflops);
 
+/* Operand-delivery ceiling (L2 -> shared memory) on the context's device, no counterpart upstream:
+ * every SM streams `tiles` tiles of `tile_bytes` out of `buffer` into its shared memory with bulk
+ * copies (cp.async.bulk, the path the GEMM operands take), `stages` of them in flight, and discards
+ * them; a first untimed pass fills the L2 when the buffer fits it. pattern 0: tiles are contiguous
+ * (operands stored as shared-memory images); pattern 1: a tile is a 128-row x 128-byte swizzled box
+ * of a matrix with 1 KiB rows (tile_bytes 16384, cp.async.bulk.tensor). Returns GB/s over all SMs. The
+ * grouped NVFP4 GEMMs stream their weights once per pair of row tiles; this is the rate that stream
+ * can reach for a given number of bytes in flight. */
+qsfi_status qs3_operand_stream_probe(qsfi_context* ctx, qsfi_device_ptr buffer, uint64_t buffer_bytes,
+                                     uint32_t tile_bytes, uint32_t stages, uint32_t tiles, uint32_t pattern,
+                                     double* gbs);
+
 /* ================================================= checkpoint loader ======
  * Upstream has the loader only as a trait (src/weight_loader.rs:33-38: alloc_tensor,
  * read_exact, zero_fill, seal) with its contract in prose (src/weight_loader.rs:9-32,

@@ -355,6 +355,8 @@ _SIGNATURES = {
     "qs3_moe_execute_fp8": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeFp8ExecuteDesc)]),
     "qsfi_moe_execute_fp8": (C.c_int, [C.c_void_p, C.c_void_p, _P(MoeFp8ExecuteDesc)]),
     "qs3_tensor_peak_probe": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, _P(C.c_double)]),
+    "qs3_operand_stream_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32,
+                                           C.c_uint32, _P(C.c_double)]),
     "qs3_checkpoint_open": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_void_p)]),
     "qs3_checkpoint_close": (None, [C.c_void_p]),
     "qs3_checkpoint_num_tensors": (C.c_uint64, [C.c_void_p]),

@@ -593,6 +593,18 @@ def tensor_peak_probe(ctx: Context, kind: str = "nvfp4", n: int = 256, iters: in
     return float(out.value)
 
 
+def operand_stream_probe(ctx: Context, buffer, tile_bytes: int = 16384, stages: int = 4, tiles: int = 2000,
+                         boxes: bool = False) -> float:
+    """``qs3_operand_stream_probe``: GB/s at which all SMs together stream ``buffer`` (a device tensor;
+    L2-resident when it is smaller than the L2) into shared memory with bulk copies, ``stages`` tiles of
+    ``tile_bytes`` in flight per SM: the operand-delivery ceiling of the streaming GEMMs. ``boxes``: every
+    tile is a 128-row x 128-byte swizzled box of a matrix with 1 KiB rows instead of contiguous bytes."""
+    out = C.c_double(0.0)
+    ctx.check(ctx._lib.qs3_operand_stream_probe(ctx.handle, buffer.data_ptr(), buffer.numel() * buffer.element_size(),
+                                                tile_bytes, stages, tiles, 1 if boxes else 0, C.byref(out)))
+    return float(out.value)
+
+
 def rmsnorm(ctx: Context, x, weight, out, eps: float = 1e-6, weight_bias: float = 0.0):
     """``qsfi_rmsnorm`` (upstream qsfi.h:160-167, 330)."""
     d = capi.RmsnormDesc()
