@@ -8,7 +8,8 @@ includes the two qsfi files, plus `qscu.cu`, for sm_100a against the FlashInfer 
 the installed `flashinfer` Python package (the reference's own `3pty/flashinfer` submodule is empty and
 its pin unrecorded, so this is a stand-in revision: good for an A/B check, not a source to port).
 Everything is written to ``oracle/_ref/`` (git-ignored); no reference source is copied. The recipe needs
-the reference tree (``QS3_REFERENCE_DIR``, default ``/root/reference``); machines without it use the
+the reference tree (its directory is ``REF_DIR`` below, overridable with ``QS3_REFERENCE_DIR``); machines
+without it use the
 prebuilt ``oracle/_ref/libqs3ref.so`` if present.
 
 ``load()`` binds the upstream subset of the C ABI with the ctypes structures of ``qs3_b200.capi`` (the

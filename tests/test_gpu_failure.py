@@ -69,3 +69,49 @@ def test_rank_barrier_times_out_when_a_peer_never_signals(ops):
     _still_usable(ops, ctx)
     with pytest.raises(ops.Qs3Error):
         ops.ep_barrier(ctx, ptrs, my_rank=2, epoch=1)
+
+
+def test_rank_barrier_counts_its_epochs_on_the_device(ops):
+    """With an epoch counter in device memory the launch has no per-step argument (that is what lets a
+    rank's step be replayed from a CUDA graph): every launch signals counter + 1 and stores it back."""
+    ctx = ops.Context()
+    solo = torch.zeros(64, dtype=torch.int32, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        ops.ep_barrier(ctx, [solo.data_ptr()], my_rank=0, epoch=0, timeout_cycles=300_000, epoch_counter=counter)
+    ctx.check_device_error()
+    assert int(counter.item()) == 3 and int(solo[0].item()) == 3
+    # replayed from a graph: three more epochs, nothing expires
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ctx.use_current_stream()
+        with torch.cuda.graph(graph, stream=stream):
+            ops.ep_barrier(ctx, [solo.data_ptr()], my_rank=0, epoch=0, timeout_cycles=300_000, epoch_counter=counter)
+        for _ in range(3):
+            graph.replay()
+        stream.synchronize()
+    ctx.use_current_stream()
+    ctx.check_device_error()
+    assert int(counter.item()) == 6 and int(solo[0].item()) == 6
+    # a peer that never signals still ends in an error code, not a hang
+    pads = torch.zeros((2, 64), dtype=torch.int32, device="cuda")
+    ops.ep_barrier(ctx, [pads[0].data_ptr(), pads[1].data_ptr()], my_rank=0, epoch=0, timeout_cycles=300_000,
+                   epoch_counter=counter)
+    with pytest.raises(ops.Qs3Error) as e:
+        ctx.check_device_error()
+    assert "0x55000001" in e.value.message
+    _still_usable(ops, ctx)
+
+
+def test_operand_stream_probe_reports_a_plausible_rate(ops):
+    """The L2 -> shared-memory probe behind the operand-delivery figures: both tile patterns run to the
+    end (no bounded wait expires) and report terabytes per second on an L2-resident buffer."""
+    ctx = ops.Context()
+    buf = torch.zeros(32 << 20, dtype=torch.uint8, device="cuda")
+    for boxes in (False, True):
+        gbs = ops.operand_stream_probe(ctx, buf, 16384, 4, 500, boxes=boxes)
+        assert 1000.0 < gbs < 40000.0, gbs
+    ctx.check_device_error()
+    with pytest.raises(ops.Qs3Error):
+        ops.operand_stream_probe(ctx, buf, 1000, 4, 10)
