@@ -208,7 +208,74 @@ router_topk_reg_kernel(const LogitT* __restrict__ logits, const float* __restric
 
     float my_weight = 0.0f;
     int my_id = 0;
-    for (uint32_t pos = 0; pos < top_k; ++pos) {
+
+    // Fast path. The arg-max rounds below cost ~3 * ITEMS integer instructions each, and the integer pipe,
+    // not memory, bounds this kernel (ncu: 1800 instructions per token, ALU pipe 70 % busy). Most of that
+    // work is spent on keys that cannot win: tau, the top_k-th largest of the 32 lane maxima, is a lower
+    // bound of the top_k-th largest key (top_k different lanes hold a key >= tau), so every winner is
+    // among the keys >= tau. Those are usually a dozen or two; they are compacted to one per lane and the
+    // rounds run on them. Ties keep upstream's rule (equal keys: lowest id), because all keys equal to
+    // the boundary value are candidates too. Falls back to the full rounds when fewer than top_k lanes
+    // hold a valid key (tau == 0) or more than 32 keys reach tau.
+    __shared__ uint32_t s_ck[kRouterWarps][32];
+    __shared__ uint32_t s_cid[kRouterWarps][32];
+    bool fast = top_k <= 32;
+    uint32_t tau = 0;
+    if (fast) {
+        uint32_t t = 0;
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j)
+            t = max(t, key[j]);
+        for (uint32_t pos = 0; pos < top_k; ++pos) {
+            tau = __reduce_max_sync(0xffffffffu, t);
+            const uint32_t holders = __ballot_sync(0xffffffffu, t == tau);
+            if (lane == static_cast<uint32_t>(__ffs(static_cast<int>(holders)) - 1))
+                t = 0; // one lane per step, so that equal maxima count once each
+        }
+        fast = tau != 0u;
+    }
+    if (fast) {
+        uint32_t cnt = 0;
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j)
+            cnt += key[j] >= tau ? 1u : 0u;
+        uint32_t incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= static_cast<uint32_t>(o))
+                incl += v;
+        }
+        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+        fast = total <= 32u;
+        if (fast) {
+            const uint32_t wslot = threadIdx.x >> 5;
+            uint32_t at = incl - cnt;
+#pragma unroll
+            for (int j = 0; j < ITEMS; ++j)
+                if (key[j] >= tau) {
+                    s_ck[wslot][at] = key[j];
+                    s_cid[wslot][at] = lane + 32u * static_cast<uint32_t>(j);
+                    ++at;
+                }
+            __syncwarp();
+            uint32_t ck = lane < total ? s_ck[wslot][lane] : 0u;
+            const uint32_t cid = lane < total ? s_cid[wslot][lane] : 0xffffffffu;
+            for (uint32_t pos = 0; pos < top_k; ++pos) {
+                const uint32_t top = __reduce_max_sync(0xffffffffu, ck); // never 0: total >= top_k candidates
+                const uint32_t win = __reduce_min_sync(0xffffffffu, ck == top ? cid : 0xffffffffu);
+                const float sc = key_score(top);
+                const float w = sigmoid_score ? sc : (denom > 0.0f ? expf(sc - vmax) / denom : 0.0f);
+                if (cid == win)
+                    ck = 0u;
+                if (lane == pos) {
+                    my_weight = w;
+                    my_id = static_cast<int>(win);
+                }
+            }
+        }
+    }
+    for (uint32_t pos = 0; !fast && pos < top_k; ++pos) {
         uint32_t best = 0;
         int bj = 0;
 #pragma unroll
