@@ -10,7 +10,11 @@
 // restate this repository's own quantisation convention (upstream has no NVFP4
 // arithmetic: qsfi_moe.cu:807-821 returns UNSUPPORTED), so for those outputs
 // parity is unpinned: the oracle and the kernels agree with each other, and no
-// upstream value exists to compare against.
+// upstream value exists to compare against. What IS pinned to a third party is the
+// NVFP4 operand format itself: cuBLASLt's block-scaled FP4 GEMM, run on the codes
+// and tiled scales the quantisers write, reproduces this file's decode-and-multiply
+// (tests/test_gpu_nvfp4_thirdparty.py), and the e4m3 / e2m1 decoders agree with
+// torch's dtypes (tests/test_oracle_golden.py).
 //
 // Parity pins (checked by tests/test_oracle_golden.py): the router known-answer
 // cases with ties and non-finite logits (tests_cuda_qscu_gdn_router.inc:966-968,
